@@ -1,0 +1,109 @@
+/*
+ * b200attn — causal grouped-query attention for NVIDIA B200 (sm_100a), C ABI.
+ *
+ * Drop-in boundary for the flash-attention entry points of AlsoTheZv3n/modern-llm-v1
+ * (paths relative to that project's root).  Every function returns an int status
+ * (0 = B200ATTN_OK), never throws and never aborts; kernels are enqueued on the
+ * given CUDA stream and the call returns without synchronising.
+ *
+ * Data types: q, k, v, o, dout, dq, dk, dv are device pointers to BF16 stored as
+ * 16-bit words (the reference's BF16 storage, llm/src/core/dtype.h:34-49); lse is
+ * FP32.  All accumulation is FP32.
+ *
+ * Layouts (element strides, unit stride on the head dimension D):
+ *   B200ATTN_LAYOUT_BHTD  [B, H, T, D] — the reference's "split" layout
+ *                         [B*H, T, D] (llm/src/model/attention.h:39-46)
+ *   B200ATTN_LAYOUT_BTHD  [B, T, H, D] — the projection output [B, T, H*D]
+ *                         read in place, so split_heads / merge_heads
+ *                         (llm/src/model/attention.cu:344-386) are not needed.
+ * q, o, dout, dq have H = Hq heads; k, v, dk, dv have H = Hkv heads.  Query head h
+ * reads KV head h / (Hq / Hkv) (llm/src/model/attention.cu:406); nothing is
+ * replicated, which replaces repeat_kv_heads / accumulate_kv_grads
+ * (llm/src/model/attention.cu:481-543).
+ *
+ * Constraints (checked, B200ATTN_ERR_* otherwise): D in {64, 128}; Hq % Hkv == 0;
+ * all sizes > 0; base pointers 16-byte aligned.
+ */
+#ifndef B200ATTN_H_
+#define B200ATTN_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    B200ATTN_OK = 0,
+    B200ATTN_ERR_INVALID_ARG = 1,  /* null pointer, non-positive size, Hq % Hkv != 0, bad layout */
+    B200ATTN_ERR_UNSUPPORTED = 2,  /* head dimension other than 64 / 128 */
+    B200ATTN_ERR_ALIGNMENT = 3,    /* a base pointer is not 16-byte aligned */
+    B200ATTN_ERR_WORKSPACE = 4,    /* workspace missing or too small */
+    B200ATTN_ERR_CUDA = 5,         /* a CUDA runtime call or a launch failed */
+    B200ATTN_ERR_TENSOR_MAP = 6,   /* the driver refused a TMA tensor map */
+    B200ATTN_ERR_DEVICE_WAIT = 7,  /* a kernel gave up on a bounded wait (see b200attn_last_device_status) */
+    B200ATTN_ERR_NO_DEVICE = 8     /* no sm_100 device is current */
+};
+
+enum { B200ATTN_LAYOUT_BHTD = 0, B200ATTN_LAYOUT_BTHD = 1 };
+
+/*
+ * Forward: o = softmax(softmax_scale * q k^T, causal) v and lse[b, h, t] = logsumexp of
+ * the scaled scores of row t (natural log), lse laid out [B, Hq, T] contiguous.
+ * Replaces flash_attn_forward (llm/src/model/flash_attn.h:25-28,
+ * llm/src/model/flash_attn.cu:383-426); the reference fixes
+ * softmax_scale = 1/sqrt(D) (llm/src/model/flash_attn.cu:418) — pass 0 to get that.
+ */
+int b200attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T, int Hq, int Hkv, int D,
+                 int layout, float softmax_scale, void* stream);
+
+/*
+ * Backward: dq, dk, dv (overwritten, not accumulated) from q, k, v, o, lse, dout.
+ * Replaces flash_attn_backward (llm/src/model/flash_attn.h:47-52,
+ * llm/src/model/flash_attn.cu:428-504): D = rowsum(o * dout), a dQ pass and a dK/dV
+ * pass.  dk/dv are already summed over the query heads of each KV group (what
+ * accumulate_kv_grads does in the reference, llm/src/model/attention.cu:510-543),
+ * in a fixed order, so results are bit-reproducible.  The reference allocates its
+ * D vector per call (llm/src/model/flash_attn.cu:463); here the caller passes a
+ * workspace of at least b200attn_bwd_workspace_bytes(...) bytes, 256-byte aligned.
+ */
+int b200attn_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* dout,
+                 void* dq, void* dk, void* dv, int B, int T, int Hq, int Hkv, int D, int layout, float softmax_scale,
+                 void* workspace, size_t workspace_bytes, void* stream);
+size_t b200attn_bwd_workspace_bytes(int B, int T, int Hq, int Hkv, int D);
+
+/*
+ * Decode: one query token per sequence against a KV cache of L tokens (the cache
+ * already holds the current token), split over the cache length.  q, o: [B, Hq, D]
+ * contiguous BF16; kcache, vcache: [B, Hkv, L, D] contiguous BF16; lse [B, Hq] FP32 or
+ * NULL.  Equals row L-1 of b200attn_fwd with T = L.  The reference has no such
+ * path: infer_modern_gpt re-runs the full forward per token
+ * (llm/apps/infer_modern_gpt.cu:253-255); this is the kernel its KV cache would call.
+ * n_splits <= 0 lets the library choose.  workspace: at least
+ * b200attn_decode_workspace_bytes(...) bytes, 256-byte aligned.
+ */
+int b200attn_decode(const void* q, const void* kcache, const void* vcache, void* o, float* lse, int B, int L, int Hq,
+                    int Hkv, int D, float softmax_scale, int n_splits, void* workspace, size_t workspace_bytes,
+                    void* stream);
+size_t b200attn_decode_workspace_bytes(int B, int L, int Hq, int Hkv, int D, int n_splits);
+/* The split count b200attn_decode uses for n_splits <= 0. */
+int b200attn_decode_default_splits(int B, int L, int Hq, int Hkv, int D);
+
+/*
+ * Synchronises `stream` and returns the device status word of the current device:
+ * 0, or the code of the first bounded wait that gave up since the last call (the
+ * word is then cleared).  The reference surfaces execution errors at a later
+ * synchronisation too (llm/src/core/cuda_check.h:31-45).
+ */
+int b200attn_last_device_status(void* stream);
+
+/* Human-readable text for a status returned by this library. */
+const char* b200attn_strerror(int status);
+
+/* Library version, major * 100 + minor. */
+int b200attn_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200ATTN_H_ */

@@ -1,0 +1,177 @@
+// C-ABI launcher for the sm_100a attention kernels (see include/b200attn.h for
+// the contract).  Host side only validates, builds TMA tensor maps and enqueues.
+#include "../../include/b200attn.h"
+
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "attn_fwd.cuh"
+#include "tmap.h"
+
+using namespace b200attn;
+
+namespace {
+
+// One status word per device, living in the library's device image.
+__device__ int g_status_word;
+
+constexpr int kMaxDevices = 64;
+int* g_status_ptr[kMaxDevices] = {nullptr};
+
+// Returns the device address of the status word of the current device (resolved once per device).
+int* status_ptr(int* err) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        *err = B200ATTN_ERR_NO_DEVICE;
+        return nullptr;
+    }
+    if (!g_status_ptr[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) {
+            cudaGetLastError();
+            *err = B200ATTN_ERR_NO_DEVICE;
+            return nullptr;
+        }
+        if (cudaMemset(p, 0, sizeof(int)) != cudaSuccess) {
+            cudaGetLastError();
+            *err = B200ATTN_ERR_CUDA;
+            return nullptr;
+        }
+        g_status_ptr[dev] = static_cast<int*>(p);
+    }
+    return g_status_ptr[dev];
+}
+
+struct Strides {
+    long long t, h, b;  // element strides
+};
+
+inline Strides strides_for(int layout, int H, int T, int D) {
+    Strides s;
+    if (layout == B200ATTN_LAYOUT_BHTD) {
+        s.t = D;
+        s.h = (long long)T * D;
+        s.b = (long long)H * T * D;
+    } else {
+        s.t = (long long)H * D;
+        s.h = D;
+        s.b = (long long)T * H * D;
+    }
+    return s;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_common(int B, int T, int Hq, int Hkv, int D, int layout) {
+    if (B <= 0 || T <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0) return B200ATTN_ERR_INVALID_ARG;
+    if (Hq % Hkv != 0) return B200ATTN_ERR_INVALID_ARG;
+    if (layout != B200ATTN_LAYOUT_BHTD && layout != B200ATTN_LAYOUT_BTHD) return B200ATTN_ERR_INVALID_ARG;
+    if (D != 64 && D != 128) return B200ATTN_ERR_UNSUPPORTED;
+    return B200ATTN_OK;
+}
+
+template <int D>
+int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to,
+               const FwdParams& p, cudaStream_t st) {
+    using Cfg = FwdCfg<D>;
+    static bool attr_set[kMaxDevices] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev]) {
+        if (cudaFuncSetAttribute(attn_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) !=
+            cudaSuccess) {
+            cudaGetLastError();
+            return B200ATTN_ERR_CUDA;
+        }
+        attr_set[dev] = true;
+    }
+    dim3 grid(p.n_qtiles, p.Hq, p.B);
+    attn_fwd_kernel<D><<<grid, 256, Cfg::kSmemBytes, st>>>(tq, tk, tv, to, p);
+    return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
+}
+
+}  // namespace
+
+extern "C" int b200attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T, int Hq,
+                            int Hkv, int D, int layout, float softmax_scale, void* stream) {
+    int rc = check_common(B, T, Hq, Hkv, D, layout);
+    if (rc) return rc;
+    if (!q || !k || !v || !o || !lse) return B200ATTN_ERR_INVALID_ARG;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return B200ATTN_ERR_ALIGNMENT;
+    int* status = status_ptr(&rc);
+    if (!status) return rc;
+    const Strides sq = strides_for(layout, Hq, T, D), sk = strides_for(layout, Hkv, T, D);
+    CUtensorMap tq, tk, tv, to;
+    if (!make_tmap_bf16_4d(&tq, q, D, T, Hq, B, sq.t, sq.h, sq.b, 128) ||
+        !make_tmap_bf16_4d(&tk, k, D, T, Hkv, B, sk.t, sk.h, sk.b, 128) ||
+        !make_tmap_bf16_4d(&tv, v, D, T, Hkv, B, sk.t, sk.h, sk.b, 128) ||
+        !make_tmap_bf16_4d(&to, o, D, T, Hq, B, sq.t, sq.h, sq.b, 128))
+        return B200ATTN_ERR_TENSOR_MAP;
+    FwdParams p;
+    p.B = B;
+    p.T = T;
+    p.Hq = Hq;
+    p.Hkv = Hkv;
+    p.group = Hq / Hkv;
+    p.n_qtiles = (T + 127) / 128;
+    p.scale = softmax_scale > 0.f ? softmax_scale : 1.f / sqrtf((float)D);
+    p.scale_log2 = p.scale * 1.4426950408889634f;
+    p.lse = lse;
+    p.status = status;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return D == 64 ? launch_fwd<64>(tq, tk, tv, to, p, st) : launch_fwd<128>(tq, tk, tv, to, p, st);
+}
+
+extern "C" int b200attn_bwd(const void*, const void*, const void*, const void*, const float*, const void*, void*,
+                            void*, void*, int, int, int, int, int, int, float, void*, size_t, void*) {
+    return B200ATTN_ERR_UNSUPPORTED;
+}
+extern "C" size_t b200attn_bwd_workspace_bytes(int B, int T, int Hq, int, int) {
+    return (size_t)B * Hq * T * sizeof(float);
+}
+extern "C" int b200attn_decode(const void*, const void*, const void*, void*, float*, int, int, int, int, int, float,
+                               int, void*, size_t, void*) {
+    return B200ATTN_ERR_UNSUPPORTED;
+}
+extern "C" size_t b200attn_decode_workspace_bytes(int, int, int, int, int, int) { return 0; }
+extern "C" int b200attn_decode_default_splits(int, int, int, int, int) { return 1; }
+
+extern "C" int b200attn_last_device_status(void* stream) {
+    int rc = 0;
+    int* status = status_ptr(&rc);
+    if (!status) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cudaStreamSynchronize(st) != cudaSuccess) {
+        cudaGetLastError();
+        return B200ATTN_ERR_CUDA;
+    }
+    int host = 0;
+    if (cudaMemcpy(&host, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return B200ATTN_ERR_CUDA;
+    if (host != 0) {
+        cudaMemset(status, 0, sizeof(int));
+        return host;
+    }
+    return B200ATTN_OK;
+}
+
+extern "C" const char* b200attn_strerror(int status) {
+    switch (status) {
+        case B200ATTN_OK: return "ok";
+        case B200ATTN_ERR_INVALID_ARG: return "invalid argument (null pointer, non-positive size, Hq % Hkv != 0 or bad layout)";
+        case B200ATTN_ERR_UNSUPPORTED: return "unsupported head dimension (only 64 and 128)";
+        case B200ATTN_ERR_ALIGNMENT: return "a base pointer is not 16-byte aligned";
+        case B200ATTN_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+        case B200ATTN_ERR_CUDA: return "a CUDA runtime call or kernel launch failed";
+        case B200ATTN_ERR_TENSOR_MAP: return "the driver refused a TMA tensor map";
+        case B200ATTN_ERR_DEVICE_WAIT: return "a kernel gave up on a bounded wait";
+        case B200ATTN_ERR_NO_DEVICE: return "no usable CUDA device is current";
+        case DEV_WAIT_TIMEOUT_LOAD: return "device: a TMA load barrier never completed";
+        case DEV_WAIT_TIMEOUT_MMA: return "device: a tensor-core completion barrier never completed";
+        case DEV_WAIT_TIMEOUT_SOFTMAX: return "device: a softmax hand-off barrier never completed";
+        case DEV_WAIT_TIMEOUT_FREE: return "device: a buffer-free barrier never completed";
+        default: return "unknown status";
+    }
+}
+
+extern "C" int b200attn_version(void) { return 1; }

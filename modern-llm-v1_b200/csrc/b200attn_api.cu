@@ -6,6 +6,7 @@
 #include <math.h>
 #include <stdint.h>
 
+#include "attn_bwd.cuh"
 #include "attn_fwd.cuh"
 #include "tmap.h"
 
@@ -123,13 +124,109 @@ extern "C" int b200attn_fwd(const void* q, const void* k, const void* v, void* o
     return D == 64 ? launch_fwd<64>(tq, tk, tv, to, p, st) : launch_fwd<128>(tq, tk, tv, to, p, st);
 }
 
-extern "C" int b200attn_bwd(const void*, const void*, const void*, const void*, const float*, const void*, void*,
-                            void*, void*, int, int, int, int, int, int, float, void*, size_t, void*) {
-    return B200ATTN_ERR_UNSUPPORTED;
+namespace {
+
+inline size_t bwd_vec_elems(int B, int T, int Hq) { return (size_t)B * Hq * (size_t)((T + 127) / 128 * 128); }
+
+template <typename K>
+int set_smem_once(K kernel, int bytes, bool* done) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!done[dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
+            cudaGetLastError();
+            return B200ATTN_ERR_CUDA;
+        }
+        done[dev] = true;
+    }
+    return B200ATTN_OK;
 }
-extern "C" size_t b200attn_bwd_workspace_bytes(int B, int T, int Hq, int, int) {
-    return (size_t)B * Hq * T * sizeof(float);
+
+template <int D>
+int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+               const CUtensorMap& tdq, const CUtensorMap& tdk, const CUtensorMap& tdv, const PreParams& pre,
+               const BwdParams& p, cudaStream_t st) {
+    using Cfg = BwdCfg<D>;
+    static bool dq_set[kMaxDevices] = {false}, dkdv_set[kMaxDevices] = {false};
+    int rc = set_smem_once(attn_bwd_dq_kernel<D>, Cfg::kSmemBytes, dq_set);
+    if (rc) return rc;
+    rc = set_smem_once(attn_bwd_dkdv_kernel<D>, Cfg::kSmemBytes, dkdv_set);
+    if (rc) return rc;
+    const long long pre_threads = (long long)p.B * p.Hq * p.Tpad * (D / 8);
+    attn_bwd_preprocess_kernel<D><<<(unsigned)((pre_threads + 255) / 256), 256, 0, st>>>(pre);
+    if (cudaGetLastError() != cudaSuccess) return B200ATTN_ERR_CUDA;
+    attn_bwd_dkdv_kernel<D><<<dim3(p.n_tiles, p.Hkv, p.B), 320, Cfg::kSmemBytes, st>>>(tk, tv, tq, tdo, tdk, tdv, p);
+    if (cudaGetLastError() != cudaSuccess) return B200ATTN_ERR_CUDA;
+    attn_bwd_dq_kernel<D><<<dim3(p.n_tiles, p.Hq, p.B), 320, Cfg::kSmemBytes, st>>>(tq, tk, tv, tdo, tdq, p);
+    return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
 }
+
+}  // namespace
+
+extern "C" size_t b200attn_bwd_workspace_bytes(int B, int T, int Hq, int Hkv, int D) {
+    (void)Hkv;
+    (void)D;
+    if (B <= 0 || T <= 0 || Hq <= 0) return 0;
+    return 2 * bwd_vec_elems(B, T, Hq) * sizeof(float);
+}
+
+extern "C" int b200attn_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                            const void* dout, void* dq, void* dk, void* dv, int B, int T, int Hq, int Hkv, int D,
+                            int layout, float softmax_scale, void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = check_common(B, T, Hq, Hkv, D, layout);
+    if (rc) return rc;
+    if (!q || !k || !v || !o || !lse || !dout || !dq || !dk || !dv) return B200ATTN_ERR_INVALID_ARG;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(dout) || !aligned16(dq) ||
+        !aligned16(dk) || !aligned16(dv))
+        return B200ATTN_ERR_ALIGNMENT;
+    if (!workspace || workspace_bytes < b200attn_bwd_workspace_bytes(B, T, Hq, Hkv, D) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+        return B200ATTN_ERR_WORKSPACE;
+    int* status = status_ptr(&rc);
+    if (!status) return rc;
+    const Strides sq = strides_for(layout, Hq, T, D), sk = strides_for(layout, Hkv, T, D);
+    CUtensorMap tq, tk, tv, tdo, tdq, tdk, tdv;
+    if (!make_tmap_bf16_4d(&tq, q, D, T, Hq, B, sq.t, sq.h, sq.b, 128) ||
+        !make_tmap_bf16_4d(&tk, k, D, T, Hkv, B, sk.t, sk.h, sk.b, 128) ||
+        !make_tmap_bf16_4d(&tv, v, D, T, Hkv, B, sk.t, sk.h, sk.b, 128) ||
+        !make_tmap_bf16_4d(&tdo, dout, D, T, Hq, B, sq.t, sq.h, sq.b, 128) ||
+        !make_tmap_bf16_4d(&tdq, dq, D, T, Hq, B, sq.t, sq.h, sq.b, 128) ||
+        !make_tmap_bf16_4d(&tdk, dk, D, T, Hkv, B, sk.t, sk.h, sk.b, 128) ||
+        !make_tmap_bf16_4d(&tdv, dv, D, T, Hkv, B, sk.t, sk.h, sk.b, 128))
+        return B200ATTN_ERR_TENSOR_MAP;
+    float* ws = static_cast<float*>(workspace);
+    const size_t nvec = bwd_vec_elems(B, T, Hq);
+    PreParams pre;
+    pre.o = static_cast<const uint16_t*>(o);
+    pre.dout = static_cast<const uint16_t*>(dout);
+    pre.lse = lse;
+    pre.lse2 = ws;
+    pre.dvec = ws + nvec;
+    pre.B = B;
+    pre.T = T;
+    pre.Tpad = (T + 127) / 128 * 128;
+    pre.Hq = Hq;
+    pre.st = sq.t;
+    pre.sh = sq.h;
+    pre.sb = sq.b;
+    BwdParams p;
+    p.B = B;
+    p.T = T;
+    p.Tpad = pre.Tpad;
+    p.Hq = Hq;
+    p.Hkv = Hkv;
+    p.group = Hq / Hkv;
+    p.n_tiles = (T + 127) / 128;
+    p.scale = softmax_scale > 0.f ? softmax_scale : 1.f / sqrtf((float)D);
+    p.scale_log2 = p.scale * 1.4426950408889634f;
+    p.lse2 = pre.lse2;
+    p.dvec = pre.dvec;
+    p.status = status;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return D == 64 ? launch_bwd<64>(tq, tk, tv, tdo, tdq, tdk, tdv, pre, p, st)
+                   : launch_bwd<128>(tq, tk, tv, tdo, tdq, tdk, tdv, pre, p, st);
+}
+
 extern "C" int b200attn_decode(const void*, const void*, const void*, void*, float*, int, int, int, int, int, float,
                                int, void*, size_t, void*) {
     return B200ATTN_ERR_UNSUPPORTED;

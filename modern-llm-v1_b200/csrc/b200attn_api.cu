@@ -7,6 +7,7 @@
 #include <stdint.h>
 
 #include "attn_bwd.cuh"
+#include "attn_decode.cuh"
 #include "attn_fwd.cuh"
 #include "tmap.h"
 
@@ -227,12 +228,117 @@ extern "C" int b200attn_bwd(const void* q, const void* k, const void* v, const v
                    : launch_bwd<128>(tq, tk, tv, tdo, tdq, tdk, tdv, pre, p, st);
 }
 
-extern "C" int b200attn_decode(const void*, const void*, const void*, void*, float*, int, int, int, int, int, float,
-                               int, void*, size_t, void*) {
-    return B200ATTN_ERR_UNSUPPORTED;
+namespace {
+
+// Query heads served per decode CTA: the largest divisor of the group size that is <= 8.
+inline int decode_heads_per_cta(int group) {
+    for (int g = 8; g >= 1; --g)
+        if (group % g == 0) return g;
+    return 1;
 }
-extern "C" size_t b200attn_decode_workspace_bytes(int, int, int, int, int, int) { return 0; }
-extern "C" int b200attn_decode_default_splits(int, int, int, int, int) { return 1; }
+
+inline int decode_pick_splits(int B, int L, int Hq, int Hkv, int n_splits) {
+    const int n_all = (L + 127) / 128;
+    if (n_splits <= 0) {
+        const int group = Hq / Hkv;
+        const long long units = (long long)B * Hkv * (group / decode_heads_per_cta(group));
+        // aim at four CTAs per SM of a 148-SM part so that the tail is short
+        long long want = (4 * 148 + units - 1) / units;
+        n_splits = (int)(want < 1 ? 1 : want);
+    }
+    if (n_splits > n_all) n_splits = n_all;
+    if (n_splits > 64) n_splits = 64;
+    const int tps = (n_all + n_splits - 1) / n_splits;
+    return (n_all + tps - 1) / tps;  // drop splits that would be empty
+}
+
+template <int D, int G>
+int launch_decode_g(const CUtensorMap& tk, const CUtensorMap& tv, const DecodeParams& p, cudaStream_t st) {
+    using Cfg = DecodeCfg<D>;
+    static bool set[kMaxDevices] = {false};
+    int rc = set_smem_once(attn_decode_kernel<D, G>, Cfg::kSmemBytes, set);
+    if (rc) return rc;
+    attn_decode_kernel<D, G><<<dim3(p.n_splits, p.Hkv * p.n_chunks, p.B), 160, Cfg::kSmemBytes, st>>>(tk, tv, p);
+    return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
+}
+
+template <int D>
+int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, const DecodeParams& p, cudaStream_t st) {
+    switch (p.G) {
+        case 1: return launch_decode_g<D, 1>(tk, tv, p, st);
+        case 2: return launch_decode_g<D, 2>(tk, tv, p, st);
+        case 3: return launch_decode_g<D, 3>(tk, tv, p, st);
+        case 4: return launch_decode_g<D, 4>(tk, tv, p, st);
+        case 5: return launch_decode_g<D, 5>(tk, tv, p, st);
+        case 6: return launch_decode_g<D, 6>(tk, tv, p, st);
+        case 7: return launch_decode_g<D, 7>(tk, tv, p, st);
+        default: return launch_decode_g<D, 8>(tk, tv, p, st);
+    }
+}
+
+}  // namespace
+
+extern "C" int b200attn_decode_default_splits(int B, int L, int Hq, int Hkv, int D) {
+    (void)D;
+    if (B <= 0 || L <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0) return 0;
+    return decode_pick_splits(B, L, Hq, Hkv, 0);
+}
+
+extern "C" size_t b200attn_decode_workspace_bytes(int B, int L, int Hq, int Hkv, int D, int n_splits) {
+    if (B <= 0 || L <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || Hq % Hkv != 0) return 0;
+    const int s = decode_pick_splits(B, L, Hq, Hkv, n_splits);
+    return (size_t)B * Hq * s * (size_t)(D + 2) * sizeof(float);
+}
+
+extern "C" int b200attn_decode(const void* q, const void* kcache, const void* vcache, void* o, float* lse, int B, int L,
+                               int Hq, int Hkv, int D, float softmax_scale, int n_splits, void* workspace,
+                               size_t workspace_bytes, void* stream) {
+    int rc = check_common(B, L, Hq, Hkv, D, B200ATTN_LAYOUT_BHTD);
+    if (rc) return rc;
+    if (!q || !kcache || !vcache || !o) return B200ATTN_ERR_INVALID_ARG;
+    if (!aligned16(q) || !aligned16(kcache) || !aligned16(vcache) || !aligned16(o)) return B200ATTN_ERR_ALIGNMENT;
+    if (!workspace || workspace_bytes < b200attn_decode_workspace_bytes(B, L, Hq, Hkv, D, n_splits) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+        return B200ATTN_ERR_WORKSPACE;
+    int* status = status_ptr(&rc);
+    if (!status) return rc;
+    const Strides sk = strides_for(B200ATTN_LAYOUT_BHTD, Hkv, L, D);
+    CUtensorMap tk, tv;
+    if (!make_tmap_bf16_4d(&tk, kcache, D, L, Hkv, B, sk.t, sk.h, sk.b, 128) ||
+        !make_tmap_bf16_4d(&tv, vcache, D, L, Hkv, B, sk.t, sk.h, sk.b, 128))
+        return B200ATTN_ERR_TENSOR_MAP;
+    DecodeParams p;
+    p.B = B;
+    p.L = L;
+    p.Hq = Hq;
+    p.Hkv = Hkv;
+    p.group = Hq / Hkv;
+    p.G = decode_heads_per_cta(p.group);
+    p.n_chunks = p.group / p.G;
+    p.n_splits = decode_pick_splits(B, L, Hq, Hkv, n_splits);
+    p.tiles_per_split = ((L + 127) / 128 + p.n_splits - 1) / p.n_splits;
+    p.scale = softmax_scale > 0.f ? softmax_scale : 1.f / sqrtf((float)D);
+    p.scale_log2 = p.scale * 1.4426950408889634f;
+    p.q = static_cast<const uint16_t*>(q);
+    float* ws = static_cast<float*>(workspace);
+    const size_t rows = (size_t)B * Hq;
+    p.part_o = ws;
+    p.part_m = ws + rows * p.n_splits * D;
+    p.part_l = p.part_m + rows * p.n_splits;
+    p.status = status;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    rc = D == 64 ? launch_decode<64>(tk, tv, p, st) : launch_decode<128>(tk, tv, p, st);
+    if (rc) return rc;
+    const unsigned blocks = (unsigned)((rows + 3) / 4);
+    if (D == 64)
+        attn_decode_combine_kernel<64><<<blocks, 128, 0, st>>>(p.part_o, p.part_m, p.part_l, static_cast<uint16_t*>(o),
+                                                              lse, (int)rows, p.n_splits, p.scale, p.scale_log2);
+    else
+        attn_decode_combine_kernel<128><<<blocks, 128, 0, st>>>(p.part_o, p.part_m, p.part_l,
+                                                               static_cast<uint16_t*>(o), lse, (int)rows, p.n_splits,
+                                                               p.scale, p.scale_log2);
+    return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
+}
 
 extern "C" int b200attn_last_device_status(void* stream) {
     int rc = 0;

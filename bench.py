@@ -1,0 +1,312 @@
+#!/usr/bin/env python3
+"""Benchmark of the causal GQA attention hot path (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config NAME]
+
+One "step" is one forward (O + logsumexp) and one backward (dQ, dK, dV) over one batch of
+seeded synthetic activations of the named configuration (default: the 50M training shape,
+B=32, T=512, Hq=6, Hkv=2, D=64, BF16 I/O, FP32 accumulation).  Prints ONE JSON line.
+
+* value      whole-job TFLOP/s with inputs resident in HBM (4*B*Hq*T^2*D/2 forward FLOPs,
+             2.5x that for backward), device-timed, max over ranks.
+* e2e        the same metric through the public operator API with HOST buffers: every step
+             copies its inputs from pinned host memory and reads its results back.
+* roofline   the dominant kernel's tensor throughput against the measured BF16 peak.
+* cpu_baseline  the CPU oracle (a port of the reference's host attention) on the box's cores.
+
+Multi-GPU (launched by torchrun, one rank per GPU): every rank runs the full configuration on
+its own seed — (batch, KV head) shards are independent, no collective is on the data path —
+so scaling is "weak"; NCCL only carries the timing reduction and a checksum gather.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+
+# DRAM traffic of the dominant kernel per launch at the default workload, from the committed ncu
+# summary (profiles/); None until a capture exists for the current kernel.
+NCU_TRAFFIC_BYTES = {"c2_50m_train": None}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        d["_source"] = "measured"
+        return d
+    d = dict(FALLBACK_PEAKS)
+    d["_source"] = "fallback"
+    return d
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="c2_50m_train")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+# ------------------------------------------------------------------------------------------
+# clocks: sampled through NVML while the timed region runs
+# ------------------------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {
+        0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+        0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+        0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting",
+    }
+
+    def __init__(self, index: int, period_s: float = 0.01):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self._h = None
+        self.period = period_s
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._h = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if r & bit and name != "gpu_idle":
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def start(self):
+        if self._h is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU side: the oracle port timed on the host cores (cpu_baseline leg and --impl reference)
+# ------------------------------------------------------------------------------------------
+def cpu_prepare(cfg, seed, n_units, one_head=False):
+    """FP32 copies of the BF16-rounded inputs of the first `n_units` (batch, KV head) units; with
+    one_head only the first query head of the first unit (the smallest sample there is)."""
+    from modern_llm_v1_b200 import inputs
+
+    q, k, v, do, hq, hkv = inputs.make_train_inputs(cfg, seed, 0, n_units, bf16=True)
+    arrs = [t.float().numpy() for t in (q, k, v, do)]
+    frac = n_units / cfg.units
+    if one_head:
+        arrs = [arrs[0][:1, :1].copy(), arrs[1][:1, :1].copy(), arrs[2][:1, :1].copy(), arrs[3][:1, :1].copy()]
+        frac = 1.0 / (cfg.units * cfg.group)
+    return arrs, cfg.fwd_bwd_flops() * frac
+
+
+def cpu_time_units(cfg, seed, n_units, repeats=1):
+    """Seconds for one forward+backward of `n_units` (batch, KV head) units on the CPU oracle
+    (all host threads), and the FLOPs those units stand for."""
+    from oracle import attn_oracle as ao
+
+    arrs, flops = cpu_prepare(cfg, seed, n_units)
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        ao.attn_fwd_bwd_c(*arrs)
+        best = min(best, time.perf_counter() - t0)
+    return best, flops
+
+
+def cpu_baseline(cfg, seed):
+    from oracle import attn_oracle as ao
+
+    cores = ao.num_threads()
+    # about 20 core-seconds of work at ~1.9 GFLOP/s per core of this scalar double-precision port
+    unit_flops = cfg.fwd_bwd_flops() / cfg.units
+    n_units = int(max(1, min(cfg.units, 20.0 * 1.9e9 / unit_flops)))
+    t, flops = cpu_time_units(cfg, seed, n_units)
+    heads = n_units * cfg.group
+    return {"value": flops / t / 1e12, "unit": "TFLOP/s", "cores": min(cores, heads), "kind": "port",
+            "sample": f"{n_units} of {cfg.units} (batch, KV head) units of {cfg.name}, forward+backward once, "
+                      f"{t:.2f} s wall on {min(cores, heads)} threads (OpenMP over batch x query head)"}
+
+
+def run_reference_arm(args, cfg, rank, world):
+    """--impl reference: the reference's host attention algorithm (oracle port: the reference's own
+    host function is forward-only and single-threaded) on this box's cores, bounded sample per step."""
+    if rank != 0:
+        return
+    from oracle import attn_oracle as ao
+
+    cores = ao.num_threads()
+    seed = 20260002
+    # calibrate on a few units, then size the per-step sample so that the run ends within ~2 minutes
+    n_cal = min(cfg.units, max(2, min(cores, 8)))
+    t_cal, _ = cpu_time_units(cfg, seed, n_cal)
+    budget = 100.0 / max(1, args.steps + args.warmup)  # seconds per step
+    waves = lambda n: -(-(n * cfg.group) // cores)     # heads are spread over the threads in waves
+    t_head = t_cal / waves(n_cal)                      # wall time of one wave of heads
+    n_units, one_head = 1, True
+    if t_head * waves(1) <= budget:
+        one_head = False
+        while n_units * 2 <= cfg.units and t_head * waves(n_units * 2) <= budget:
+            n_units *= 2
+    arrs, step_flops = cpu_prepare(cfg, seed, n_units, one_head)
+    for _ in range(args.warmup):
+        ao.attn_fwd_bwd_c(*arrs)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        ao.attn_fwd_bwd_c(*arrs)
+    dt = time.perf_counter() - t0
+    val = step_flops * args.steps / dt / 1e12
+    threads = 1 if one_head else min(cores, n_units * cfg.group)
+    sample = ("one query head of one unit" if one_head else f"{n_units} of {cfg.units} (batch, KV head) units") + \
+             f" of {cfg.name} per step, forward+backward on the CPU oracle"
+    line = {
+        "impl": "reference", "metric": "causal_gqa_attn_fwd_bwd_tflops", "value": val, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": cfg.name, "B": cfg.B, "T": cfg.T, "Hq": cfg.Hq, "Hkv": cfg.Hkv, "D": cfg.D,
+                   "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# GPU side
+# ------------------------------------------------------------------------------------------
+class BufferSet:
+    """Device tensors of one step: inputs, outputs and gradients (BHTD layout)."""
+
+    def __init__(self, cfg, host, device):
+        import torch
+
+        self.q, self.k, self.v, self.do = (t.to(device, non_blocking=True) for t in host)
+        self.o = torch.empty_like(self.q)
+        self.lse = torch.empty(cfg.B, cfg.Hq, cfg.T, dtype=torch.float32, device=device)
+        self.dq = torch.empty_like(self.q)
+        self.dk = torch.empty_like(self.k)
+        self.dv = torch.empty_like(self.v)
+
+    def nbytes(self):
+        return sum(t.numel() * t.element_size() for t in
+                   (self.q, self.k, self.v, self.do, self.o, self.lse, self.dq, self.dk, self.dv))
+
+
+def step(m, cfg, s):
+    m.flash_attn_forward_gqa(s.q, s.k, s.v, s.o, s.lse, cfg.B, cfg.T, cfg.Hq, cfg.Hkv, cfg.D)
+    m.flash_attn_backward_gqa(s.q, s.k, s.v, s.o, s.lse, s.do, s.dq, s.dk, s.dv, cfg.B, cfg.T, cfg.Hq, cfg.Hkv, cfg.D)
+
+
+def kernel_breakdown(m, cfg, sets, steps):
+    """Average device time of each kernel of a step, CUDA events on the launching stream."""
+    import torch
+
+    lib = m._lib.load()
+    n = min(steps, 200)
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(n)]
+    for row in evs:  # events get their CUDA handle on first record
+        for e in row:
+            e.record()
+    torch.cuda.synchronize()
+    for i in range(n):
+        s = sets[i % len(sets)]
+        e = evs[i]
+        m._lib.check(lib.b200attn_set_bwd_profile_events(e[2].cuda_event, e[3].cuda_event, e[4].cuda_event,
+                                                         e[5].cuda_event), "set_bwd_profile_events")
+        e[0].record()
+        m.flash_attn_forward_gqa(s.q, s.k, s.v, s.o, s.lse, cfg.B, cfg.T, cfg.Hq, cfg.Hkv, cfg.D)
+        e[1].record()
+        m.flash_attn_backward_gqa(s.q, s.k, s.v, s.o, s.lse, s.do, s.dq, s.dk, s.dv, cfg.B, cfg.T, cfg.Hq, cfg.Hkv,
+                                  cfg.D)
+    lib.b200attn_set_bwd_profile_events(None, None, None, None)
+    torch.cuda.synchronize()
+    names = ["attn_fwd_kernel", "attn_bwd_preprocess_kernel", "attn_bwd_dkdv_kernel", "attn_bwd_dq_kernel"]
+    pairs = [(0, 1), (2, 3), (3, 4), (4, 5)]
+    out = {}
+    for name, (a, b) in zip(names, pairs):
+        out[name] = sum(e[a].elapsed_time(e[b]) for e in evs) / n  # ms
+    return out
+
+
+def e2e_measure(m, cfg, host_sets, steps, warmup, device):
+    """Steps/s through the operator API with HOST buffers: H2D of q,k,v,dO from pinned memory, forward,
+    backward, D2H of O,dQ,dK,dV into pinned memory; three streams, two device buffer sets in flight."""
+    import torch
+
+    n_buf = 2
+    dev = [BufferSet(cfg, host_sets[0], device) for _ in range(n_buf)]
+    outs = [[torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in (d.o, d.dq, d.dk, d.dv)] for d in dev]
+    s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [torch.cuda.Event() for _ in range(n_buf)]
+    ev_cmp = [torch.cuda.Event() for _ in range(n_buf)]
+    ev_out = [torch.cuda.Event() for _ in range(n_buf)]
+    torch.cuda.synchronize()
+
+    def one(i):
+        b = i % n_buf
+        h = host_sets[i % len(host_sets)]
+        d = dev[b]
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(ev_cmp[b])  # the previous use of these device inputs has been consumed
+            for dst, src in zip((d.q, d.k, d.v, d.do), h):
+                dst.copy_(src, non_blocking=True)
+            ev_in[b].record()
+        with torch.cuda.stream(s_cmp):
+            s_cmp.wait_event(ev_in[b])
+            s_cmp.wait_event(ev_out[b])  # the previous outputs of this set have left the device
+            step(m, cfg, d)
+            ev_cmp[b].record()
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_cmp[b])
+            for dst, src in zip(outs[b], (d.o, d.dq, d.dk, d.dv)):
+                dst.copy_(src, non_blocking=True)
+            ev_out[b].record()
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(steps):
+        one(i)
+    for st in (s_in, s_cmp, s_out):
+        torch.cuda.current_stream().wait_stream(st)
+    t1.record()
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1)
+    h2d = sum(t.numel() * t.element_size() for t in host_sets[0])
+    d2h = sum(t.numel() * t.element_size() for t in outs[0])
+    return ms / steps, h2d, d2h

@@ -90,6 +90,16 @@ size_t b200attn_decode_workspace_bytes(int B, int L, int Hq, int Hkv, int D, int
 int b200attn_decode_default_splits(int B, int L, int Hq, int Hkv, int D);
 
 /*
+ * Diagnostics for benchmarks (no counterpart in the reference): when four CUDA events are
+ * set, every following b200attn_bwd records them on its stream before the preprocess
+ * kernel, after it, after the dK/dV pass and after the dQ pass, so a caller can time each
+ * kernel of the backward.  Pass four NULLs to switch it off (the default).  The events stay
+ * owned by the caller.
+ */
+int b200attn_set_bwd_profile_events(void* ev_start, void* ev_after_preprocess, void* ev_after_dkdv,
+                                    void* ev_after_dq);
+
+/*
  * Synchronises `stream` and returns the device status word of the current device:
  * 0, or the code of the first bounded wait that gave up since the last call (the
  * word is then cleared).  The reference surfaces execution errors at a later

@@ -32,6 +32,7 @@ SYMBOLS = (
     "b200attn_fwd",
     "b200attn_bwd",
     "b200attn_bwd_workspace_bytes",
+    "b200attn_set_bwd_profile_events",
     "b200attn_decode",
     "b200attn_decode_workspace_bytes",
     "b200attn_decode_default_splits",
@@ -60,6 +61,8 @@ def load() -> ctypes.CDLL:
     L.b200attn_bwd.restype = i
     L.b200attn_bwd_workspace_bytes.argtypes = [i, i, i, i, i]
     L.b200attn_bwd_workspace_bytes.restype = sz
+    L.b200attn_set_bwd_profile_events.argtypes = [vp, vp, vp, vp]
+    L.b200attn_set_bwd_profile_events.restype = i
     L.b200attn_decode.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, f, i, vp, sz, vp]
     L.b200attn_decode.restype = i
     L.b200attn_decode_workspace_bytes.argtypes = [i, i, i, i, i, i]

@@ -143,6 +143,12 @@ int set_smem_once(K kernel, int bytes, bool* done) {
     return B200ATTN_OK;
 }
 
+cudaEvent_t g_bwd_events[4] = {nullptr, nullptr, nullptr, nullptr};
+
+inline void record_bwd_event(int i, cudaStream_t st) {
+    if (g_bwd_events[i]) cudaEventRecord(g_bwd_events[i], st);
+}
+
 template <int D>
 int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                const CUtensorMap& tdq, const CUtensorMap& tdk, const CUtensorMap& tdv, const PreParams& pre,
@@ -154,15 +160,28 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
     rc = set_smem_once(attn_bwd_dkdv_kernel<D>, Cfg::kSmemBytes, dkdv_set);
     if (rc) return rc;
     const long long pre_threads = (long long)p.B * p.Hq * p.Tpad * (D / 8);
+    record_bwd_event(0, st);
     attn_bwd_preprocess_kernel<D><<<(unsigned)((pre_threads + 255) / 256), 256, 0, st>>>(pre);
     if (cudaGetLastError() != cudaSuccess) return B200ATTN_ERR_CUDA;
+    record_bwd_event(1, st);
     attn_bwd_dkdv_kernel<D><<<dim3(p.n_tiles, p.Hkv, p.B), 320, Cfg::kSmemBytes, st>>>(tk, tv, tq, tdo, tdk, tdv, p);
     if (cudaGetLastError() != cudaSuccess) return B200ATTN_ERR_CUDA;
+    record_bwd_event(2, st);
     attn_bwd_dq_kernel<D><<<dim3(p.n_tiles, p.Hq, p.B), 320, Cfg::kSmemBytes, st>>>(tq, tk, tv, tdo, tdq, p);
-    return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
+    if (cudaGetLastError() != cudaSuccess) return B200ATTN_ERR_CUDA;
+    record_bwd_event(3, st);
+    return B200ATTN_OK;
 }
 
 }  // namespace
+
+extern "C" int b200attn_set_bwd_profile_events(void* e0, void* e1, void* e2, void* e3) {
+    void* ev[4] = {e0, e1, e2, e3};
+    const int n_set = (e0 != nullptr) + (e1 != nullptr) + (e2 != nullptr) + (e3 != nullptr);
+    if (n_set != 0 && n_set != 4) return B200ATTN_ERR_INVALID_ARG;
+    for (int i = 0; i < 4; ++i) g_bwd_events[i] = static_cast<cudaEvent_t>(ev[i]);
+    return B200ATTN_OK;
+}
 
 extern "C" size_t b200attn_bwd_workspace_bytes(int B, int T, int Hq, int Hkv, int D) {
     (void)Hkv;

@@ -43,15 +43,21 @@ def _workspace(kind: str, nbytes: int, device: torch.device) -> torch.Tensor:
     return buf
 
 
-def _check_tensor(t: torch.Tensor, name: str, fn: str, dtype: torch.dtype) -> None:
-    if not isinstance(t, torch.Tensor):
-        raise ValueError(f"{fn}: {name} must be a tensor")
-    if t.dtype != dtype:
-        raise ValueError(f"{fn}: {name} must be {str(dtype).replace('torch.', '').upper()}")
-    if not t.is_cuda:
-        raise ValueError(f"{fn}: {name} must be CUDA")
-    if not t.is_contiguous():
-        raise ValueError(f"{fn}: {name} must be contiguous")
+def _check_tensors(fn: str, items) -> None:
+    """items: (tensor, name, dtype).  Like the reference (llm/src/model/flash_attn.cu:386-397):
+    every dtype is checked first, then every device."""
+    for t, name, dtype in items:
+        if not isinstance(t, torch.Tensor):
+            raise ValueError(f"{fn}: {name} must be a tensor")
+        if t.dtype != dtype:
+            want = {torch.bfloat16: "BF16", torch.float32: "FP32"}.get(dtype, str(dtype))
+            raise ValueError(f"{fn}: {name} must be {want}")
+    for t, name, _ in items:
+        if not t.is_cuda:
+            raise ValueError(f"{fn}: {name} must be CUDA")
+    for t, name, _ in items:
+        if not t.is_contiguous():
+            raise ValueError(f"{fn}: {name} must be contiguous")
 
 
 def _dims_ok(B: int, T: int, D: int) -> bool:
@@ -65,9 +71,8 @@ def flash_attn_forward_gqa(q, k, v, ctx, L, B, T, Hq, Hkv, D, layout="BHTD", sof
     """ctx = causal softmax(scale q k^T) v, L = logsumexp rows.  q, ctx: B*Hq*T*D BF16
     elements in `layout`; k, v: B*Hkv*T*D; L: [B, Hq, T] FP32."""
     fn = "flash_attn_forward"
-    for t, n in ((q, "q"), (k, "k"), (v, "v"), (ctx, "ctx")):
-        _check_tensor(t, n, fn, torch.bfloat16)
-    _check_tensor(L, "L", fn, torch.float32)
+    bf = torch.bfloat16
+    _check_tensors(fn, [(q, "q", bf), (k, "k", bf), (v, "v", bf), (ctx, "ctx", bf), (L, "L", torch.float32)])
     if layout not in _lib.LAYOUTS:
         raise ValueError(f"{fn}: layout must be BHTD or BTHD")
     nq, nkv = B * Hq * T * D, B * Hkv * T * D
@@ -87,10 +92,9 @@ def flash_attn_backward_gqa(q, k, v, ctx, L, d_ctx, d_q, d_k, d_v, B, T, Hq, Hkv
     """d_q, d_k, d_v (overwritten) for the forward above.  d_k, d_v are Hkv-wide: the
     sum over each group's query heads is done inside the kernel."""
     fn = "flash_attn_backward"
-    for t, n in ((q, "q"), (k, "k"), (v, "v"), (ctx, "ctx"), (d_ctx, "d_ctx"), (d_q, "d_q"), (d_k, "d_k"),
-                 (d_v, "d_v")):
-        _check_tensor(t, n, fn, torch.bfloat16)
-    _check_tensor(L, "L", fn, torch.float32)
+    bf = torch.bfloat16
+    _check_tensors(fn, [(q, "q", bf), (k, "k", bf), (v, "v", bf), (ctx, "ctx", bf), (L, "L", torch.float32),
+                        (d_ctx, "d_ctx", bf), (d_q, "d_q", bf), (d_k, "d_k", bf), (d_v, "d_v", bf)])
     if layout not in _lib.LAYOUTS:
         raise ValueError(f"{fn}: layout must be BHTD or BTHD")
     nq, nkv = B * Hq * T * D, B * Hkv * T * D
@@ -137,10 +141,12 @@ def flash_attn_decode(q, kcache, vcache, o, lse, B, L, Hq, Hkv, D, softmax_scale
     """o[b, h] = softmax(scale q[b, h] . K[b, h/g, :L]) V[b, h/g, :L]; q, o [B, Hq, D] BF16,
     caches [B, Hkv, L, D] BF16, lse [B, Hq] FP32 or None."""
     fn = "flash_attn_decode"
-    for t, n in ((q, "q"), (kcache, "kcache"), (vcache, "vcache"), (o, "o")):
-        _check_tensor(t, n, fn, torch.bfloat16)
+    bf = torch.bfloat16
+    items = [(q, "q", bf), (kcache, "kcache", bf), (vcache, "vcache", bf), (o, "o", bf)]
     if lse is not None:
-        _check_tensor(lse, "lse", fn, torch.float32)
+        items.append((lse, "lse", torch.float32))
+    _check_tensors(fn, items)
+    if lse is not None:
         if lse.numel() != B * Hq:
             raise ValueError(f"{fn}: lse must be [B, Hq]")
     if q.numel() != B * Hq * D or o.numel() != B * Hq * D:

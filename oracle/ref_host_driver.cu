@@ -12,6 +12,14 @@
 #define main modernllm_ref_test_attention_main
 #include "tests/test_attention.cu"
 #undef main
+#include "core/dtype.h"
+// BF16 round-to-nearest-even of the reference, llm/src/core/dtype.h:34-49
+extern "C" void ref_f32_to_bf16(const float* x, unsigned short* y, long long n) {
+    for (long long i = 0; i < n; ++i) y[i] = modernllm::f32_to_bf16(x[i]);
+}
+extern "C" void ref_bf16_to_f32(const unsigned short* x, float* y, long long n) {
+    for (long long i = 0; i < n; ++i) y[i] = modernllm::bf16_to_f32(x[i]);
+}
 extern "C" void ref_attn_host(const float* q, const float* k, const float* v, int B, int T, int D, float* ctx,
                               float* probs) {
     attn_host(q, k, v, B, T, D, ctx, probs);

@@ -1,0 +1,55 @@
+"""The CUDA path against the REFERENCE'S OWN GPU attention (its per-row flash kernels and
+its cuBLAS path, compiled unchanged from the reference tree into oracle/_ref/libref_gpu.so)
+on identical BF16-rounded inputs held as FP32, GQA done the reference's way
+(repeat_kv_heads -> attention -> accumulate_kv_grads).  Skipped where that library was not
+built (it needs the reference tree at build time)."""
+import ctypes
+import os
+
+import pytest
+import torch
+
+from gpu_util import TOL_LSE, assert_close, np32, randn_bf16, run_fwd_bwd
+
+pytestmark = pytest.mark.gpu
+
+LIB = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "libref_gpu.so")
+
+
+@pytest.fixture(scope="module")
+def ref():
+    if not os.path.exists(LIB):
+        pytest.skip("oracle/_ref/libref_gpu.so not built")
+    L = ctypes.CDLL(LIB)
+    L.ref_gpu_attention.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 9 + [ctypes.c_int] * 5
+    L.ref_gpu_attention.restype = ctypes.c_int
+    return L
+
+
+def _reference(ref, which, q, k, v, do):
+    B, Hq, T, D = q.shape
+    Hkv = k.shape[1]
+    qf, kf, vf, dof = (x.float().contiguous() for x in (q, k, v, do))
+    o, dq = torch.empty_like(qf), torch.empty_like(qf)
+    dk, dv = torch.empty_like(kf), torch.empty_like(vf)
+    lse = torch.zeros(B, Hq, T, device="cuda")
+    torch.cuda.synchronize()
+    rc = ref.ref_gpu_attention(which, qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), dof.data_ptr(), o.data_ptr(),
+                               lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, T, Hq, Hkv, D)
+    assert rc == 0
+    return o, lse, dq, dk, dv
+
+
+@pytest.mark.parametrize("which", [0, 1])
+@pytest.mark.parametrize("B,T,Hq,Hkv,D", [(2, 128, 6, 2, 64), (2, 512, 6, 2, 64), (1, 200, 4, 1, 128)])
+def test_matches_reference_gpu_attention(ref, which, B, T, Hq, Hkv, D):
+    q, k, v = randn_bf16((B, Hq, T, D), 1), randn_bf16((B, Hkv, T, D), 2), randn_bf16((B, Hkv, T, D), 3)
+    do = randn_bf16((B, Hq, T, D), 4, 0.1)
+    got = run_fwd_bwd(q, k, v, do)
+    want = _reference(ref, which, q, k, v, do)
+    assert_close("O", got[0], np32(want[0]))
+    if which == 0:  # only the flash path produces the logsumexp
+        assert_close("LSE", got[1], np32(want[1]), max_abs=TOL_LSE, rel_l2=1.0)
+    assert_close("dQ", got[2], np32(want[2]))
+    assert_close("dK", got[3], np32(want[3]))
+    assert_close("dV", got[4], np32(want[4]))

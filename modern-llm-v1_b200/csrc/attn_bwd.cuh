@@ -95,29 +95,36 @@ struct BwdCfg {
     static constexpr int kColAcc1 = 384;
 };
 
-// D[tmem] = A[smem, K-major] * B[smem, K-major]^T over the head dimension.
+// D[tmem] = A[smem, K-major] * B[smem, K-major]^T over the head dimension; a_desc / b_desc
+// describe K step 0 of each operand.
 template <int D>
-__device__ __forceinline__ void issue_ss_over_headdim(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr,
+__device__ __forceinline__ void issue_ss_over_headdim(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                                       uint32_t idesc) {
 #pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks) {
-        const uint32_t off = (ks / 4) * BwdCfg<D>::kBoxBytes + (ks % 4) * 32;
-        umma_ss(d_tmem, make_sdesc_sw128(a_addr + off, 16, 1024), make_sdesc_sw128(b_addr + off, 16, 1024), idesc,
-                ks > 0);
-    }
+    for (int ks = 0; ks < D / 16; ++ks)
+        umma_ss(d_tmem, a_desc + kmajor_step(ks, BwdCfg<D>::kBoxBytes), b_desc + kmajor_step(ks, BwdCfg<D>::kBoxBytes),
+                idesc, ks > 0);
 }
 
-// D[tmem] (+)= A[tmem, BF16 pairs] * B[smem, MN-major] over 128 rows of B.  The A
-// operand lives in two 32-column pieces, `a_col` and `a_col + 64`.
+// D[tmem] (+)= A[tmem, BF16 pairs] * B[smem, MN-major] over 128 rows of B (b_desc describes
+// rows 0..15).  The A operand lives in two 32-column pieces, `a_col` and `a_col + 64`.
 template <int D>
-__device__ __forceinline__ void issue_ts_over_rows(uint32_t d_tmem, uint32_t a_col, uint32_t b_addr, uint32_t idesc,
+__device__ __forceinline__ void issue_ts_over_rows(uint32_t d_tmem, uint32_t a_col, uint64_t b_desc, uint32_t idesc,
                                                    bool accumulate) {
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
         const uint32_t a = a_col + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8);
-        umma_ts(d_tmem, a, make_sdesc_sw128(b_addr + ks * 2048, BwdCfg<D>::kBoxBytes, 1024), idesc,
-                accumulate || ks > 0);
+        umma_ts(d_tmem, a, b_desc + uint64_t(ks * 128), idesc, accumulate || ks > 0);
     }
+}
+
+template <int D>
+__device__ __forceinline__ uint64_t kmajor_desc(const void* tile) {
+    return make_sdesc_sw128(smem_u32(tile), 16, 1024);
+}
+template <int D>
+__device__ __forceinline__ uint64_t mnmajor_desc(const void* tile) {
+    return make_sdesc_sw128(smem_u32(tile), BwdCfg<D>::kBoxBytes, 1024);
 }
 
 // Converts 32 FP32 accumulator columns [col, col+32) of this thread's row to BF16 (times
@@ -203,19 +210,22 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const uint32_t tmem = *tmem_slot;
 
     if (warp == 8) {
-        // ------------------------------------------------------------------ producer
-        if (lane == 0) {
+        // ------------------------------------------------------------------ producer (whole warp, one lane issues)
+        if (elect_one()) {
             mbar_arrive_expect_tx(bar_q, 2 * Cfg::kTileBytes);
 #pragma unroll
             for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
                 tma_load_4d(sQ + bx * Cfg::kBoxBytes, &tmQ, bar_q, bx * 64, q0, h, b);
                 tma_load_4d(sdO + bx * Cfg::kBoxBytes, &tmdO, bar_q, bx * 64, q0, h, b);
             }
-            for (int j = 0; j < n_kv; ++j) {
-                const int s = j & 1;
-                if (j >= 2 &&
-                    !mbar_wait(&bar_kv_free[s], ((j >> 1) - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE))
-                    break;
+        }
+        __syncwarp();
+        for (int j = 0; j < n_kv; ++j) {
+            const int s = j & 1;
+            if (j >= 2 &&
+                !mbar_wait_warp(&bar_kv_free[s], ((j >> 1) - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE))
+                break;
+            if (elect_one()) {
                 mbar_arrive_expect_tx(&bar_kv_full[s], 2 * Cfg::kTileBytes);
 #pragma unroll
                 for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
@@ -225,42 +235,53 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                                 hk, b);
                 }
             }
+            __syncwarp();
         }
     } else if (warp == 9) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
-            constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
-            const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO);
-            bool ok = mbar_wait(bar_q, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-            if (ok) ok = mbar_wait(&bar_kv_full[0], 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-            if (ok) {
-                tc_fence_after_sync();
-                issue_ss_over_headdim<D>(tmem + Cfg::kColS, q_addr, smem_u32(sK), idesc_s);
-                issue_ss_over_headdim<D>(tmem + Cfg::kColDP, do_addr, smem_u32(sV), idesc_s);
+        // ------------------------------------------------------------------ MMA issuer (whole warp, one lane issues)
+        constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+        constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
+        const uint64_t q_desc = kmajor_desc<D>(sQ), do_desc = kmajor_desc<D>(sdO);
+        bool ok = mbar_wait_warp(bar_q, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+        if (ok) ok = mbar_wait_warp(&bar_kv_full[0], 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+        if (ok) {
+            tc_fence_after_sync();
+            if (elect_one()) {
+                issue_ss_over_headdim<D>(tmem + Cfg::kColS, q_desc, kmajor_desc<D>(sK), idesc_s);
+                issue_ss_over_headdim<D>(tmem + Cfg::kColDP, do_desc, kmajor_desc<D>(sV), idesc_s);
                 umma_commit(bar_sdp_full);
             }
-            for (int j = 0; j < n_kv && ok; ++j) {
-                const int s = j & 1;
-                ok = mbar_wait(bar_ds_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
-                if (!ok) break;
-                tc_fence_after_sync();
+            __syncwarp();
+        }
+        for (int j = 0; j < n_kv && ok; ++j) {
+            const int s = j & 1;
+            ok = mbar_wait_warp(bar_ds_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+            if (!ok) break;
+            tc_fence_after_sync();
+            if (elect_one()) {
                 // dQ += dS K_j
-                issue_ts_over_rows<D>(tmem + Cfg::kColAcc0, tmem + Cfg::kColDP, smem_u32(sK + s * Cfg::kTileBytes),
+                issue_ts_over_rows<D>(tmem + Cfg::kColAcc0, tmem + Cfg::kColDP, mnmajor_desc<D>(sK + s * Cfg::kTileBytes),
                                       idesc_acc, j > 0);
                 umma_commit(&bar_kv_free[s]);
-                if (j + 1 < n_kv) {
-                    const int s1 = (j + 1) & 1;
-                    ok = mbar_wait(&bar_kv_full[s1], ((j + 1) >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    issue_ss_over_headdim<D>(tmem + Cfg::kColS, q_addr, smem_u32(sK + s1 * Cfg::kTileBytes), idesc_s);
-                    issue_ss_over_headdim<D>(tmem + Cfg::kColDP, do_addr, smem_u32(sV + s1 * Cfg::kTileBytes), idesc_s);
+            }
+            __syncwarp();
+            if (j + 1 < n_kv) {
+                const int s1 = (j + 1) & 1;
+                ok = mbar_wait_warp(&bar_kv_full[s1], ((j + 1) >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+                if (!ok) break;
+                tc_fence_after_sync();
+                if (elect_one()) {
+                    issue_ss_over_headdim<D>(tmem + Cfg::kColS, q_desc, kmajor_desc<D>(sK + s1 * Cfg::kTileBytes),
+                                             idesc_s);
+                    issue_ss_over_headdim<D>(tmem + Cfg::kColDP, do_desc, kmajor_desc<D>(sV + s1 * Cfg::kTileBytes),
+                                             idesc_s);
                     umma_commit(bar_sdp_full);
                 }
+                __syncwarp();
             }
-            umma_commit(bar_acc);
         }
+        if (elect_one()) umma_commit(bar_acc);
+        __syncwarp();
     } else {
         // ------------------------------------------------------------------ compute
         const int w4 = warp & 3, half = warp >> 2;
@@ -402,21 +423,24 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     const uint32_t tmem = *tmem_slot;
 
     if (warp == 8) {
-        // ------------------------------------------------------------------ producer
-        if (lane == 0) {
+        // ------------------------------------------------------------------ producer (whole warp, one lane issues)
+        if (elect_one()) {
             mbar_arrive_expect_tx(bar_kv, 2 * Cfg::kTileBytes);
 #pragma unroll
             for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
                 tma_load_4d(sK + bx * Cfg::kBoxBytes, &tmK, bar_kv, bx * 64, k0, hk, b);
                 tma_load_4d(sV + bx * Cfg::kBoxBytes, &tmV, bar_kv, bx * 64, k0, hk, b);
             }
-            for (int it = 0; it < n_it; ++it) {
-                const int s = it & 1;
-                const int h = hk * p.group + it / n_i;
-                const int i = kt + it % n_i;
-                if (it >= 2 &&
-                    !mbar_wait(&bar_free[s], ((it >> 1) - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE))
-                    break;
+        }
+        __syncwarp();
+        for (int it = 0; it < n_it; ++it) {
+            const int s = it & 1;
+            const int h = hk * p.group + it / n_i;
+            const int i = kt + it % n_i;
+            if (it >= 2 &&
+                !mbar_wait_warp(&bar_free[s], ((it >> 1) - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE))
+                break;
+            if (elect_one()) {
                 mbar_arrive_expect_tx(&bar_full[s], 2 * Cfg::kTileBytes + 1024);
 #pragma unroll
                 for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
@@ -429,44 +453,54 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                 bulk_load_1d(sLse + s * 128, p.lse2 + voff, 512, &bar_full[s]);
                 bulk_load_1d(sDv + s * 128, p.dvec + voff, 512, &bar_full[s]);
             }
+            __syncwarp();
         }
     } else if (warp == 9) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
-            constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
-            const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-            bool ok = mbar_wait(bar_kv, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-            if (ok) ok = mbar_wait(&bar_full[0], 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-            if (ok) {
-                tc_fence_after_sync();
-                issue_ss_over_headdim<D>(tmem + Cfg::kColS, k_addr, smem_u32(sQ), idesc_s);     // S^T  = K Q^T
-                issue_ss_over_headdim<D>(tmem + Cfg::kColDP, v_addr, smem_u32(sdO), idesc_s);   // dP^T = V dO^T
+        // ------------------------------------------------------------------ MMA issuer (whole warp, one lane issues)
+        constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+        constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
+        const uint64_t k_desc = kmajor_desc<D>(sK), v_desc = kmajor_desc<D>(sV);
+        bool ok = mbar_wait_warp(bar_kv, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+        if (ok) ok = mbar_wait_warp(&bar_full[0], 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+        if (ok) {
+            tc_fence_after_sync();
+            if (elect_one()) {
+                issue_ss_over_headdim<D>(tmem + Cfg::kColS, k_desc, kmajor_desc<D>(sQ), idesc_s);     // S^T  = K Q^T
+                issue_ss_over_headdim<D>(tmem + Cfg::kColDP, v_desc, kmajor_desc<D>(sdO), idesc_s);   // dP^T = V dO^T
                 umma_commit(bar_sdp_full);
             }
-            for (int it = 0; it < n_it && ok; ++it) {
-                const int s = it & 1;
-                ok = mbar_wait(bar_pds_full, it & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
-                if (!ok) break;
-                tc_fence_after_sync();
+            __syncwarp();
+        }
+        for (int it = 0; it < n_it && ok; ++it) {
+            const int s = it & 1;
+            ok = mbar_wait_warp(bar_pds_full, it & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+            if (!ok) break;
+            tc_fence_after_sync();
+            if (elect_one()) {
                 // dV += P^T dO ; dK += dS^T Q
-                issue_ts_over_rows<D>(tmem + Cfg::kColAcc0, tmem + Cfg::kColS, smem_u32(sdO + s * Cfg::kTileBytes),
+                issue_ts_over_rows<D>(tmem + Cfg::kColAcc0, tmem + Cfg::kColS, mnmajor_desc<D>(sdO + s * Cfg::kTileBytes),
                                       idesc_acc, it > 0);
-                issue_ts_over_rows<D>(tmem + Cfg::kColAcc1, tmem + Cfg::kColDP, smem_u32(sQ + s * Cfg::kTileBytes),
+                issue_ts_over_rows<D>(tmem + Cfg::kColAcc1, tmem + Cfg::kColDP, mnmajor_desc<D>(sQ + s * Cfg::kTileBytes),
                                       idesc_acc, it > 0);
                 umma_commit(&bar_free[s]);
-                if (it + 1 < n_it) {
-                    const int s1 = (it + 1) & 1;
-                    ok = mbar_wait(&bar_full[s1], ((it + 1) >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    issue_ss_over_headdim<D>(tmem + Cfg::kColS, k_addr, smem_u32(sQ + s1 * Cfg::kTileBytes), idesc_s);
-                    issue_ss_over_headdim<D>(tmem + Cfg::kColDP, v_addr, smem_u32(sdO + s1 * Cfg::kTileBytes), idesc_s);
+            }
+            __syncwarp();
+            if (it + 1 < n_it) {
+                const int s1 = (it + 1) & 1;
+                ok = mbar_wait_warp(&bar_full[s1], ((it + 1) >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+                if (!ok) break;
+                tc_fence_after_sync();
+                if (elect_one()) {
+                    issue_ss_over_headdim<D>(tmem + Cfg::kColS, k_desc, kmajor_desc<D>(sQ + s1 * Cfg::kTileBytes), idesc_s);
+                    issue_ss_over_headdim<D>(tmem + Cfg::kColDP, v_desc, kmajor_desc<D>(sdO + s1 * Cfg::kTileBytes),
+                                             idesc_s);
                     umma_commit(bar_sdp_full);
                 }
+                __syncwarp();
             }
-            umma_commit(bar_acc);
         }
+        if (elect_one()) umma_commit(bar_acc);
+        __syncwarp();
     } else {
         // ------------------------------------------------------------------ compute
         const int w4 = warp & 3, half = warp >> 2;

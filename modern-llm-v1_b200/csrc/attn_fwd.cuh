@@ -87,6 +87,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int q0 = qt * 128;
     const int n_kv = qt + 1;  // key tiles 0..qt
 
+    B200ATTN_STAMP(tid == 0, 0);
     // An earlier CTA already failed: leave at once.  The decision is taken by one thread
     // and shared, so that the whole CTA agrees on it.
     if (tid == 0) *abort_flag = *reinterpret_cast<volatile int*>(p.status);
@@ -123,81 +124,99 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    B200ATTN_STAMP(tid == 0, 1);
 
     if (warp >= 6) {
-        reg_dealloc<48>();  // idle warps
+        reg_dealloc<56>();  // idle warps
     } else if (warp == 4) {
         // ------------------------------------------------------------------ producer
-        reg_dealloc<48>();
-        if (lane == 0) {
+        // All 32 lanes run the loop; one elected lane issues the copies.
+        reg_dealloc<56>();
+        if (elect_one()) {
             mbar_arrive_expect_tx(bar_q, Cfg::kTileBytes);
 #pragma unroll
             for (int bx = 0; bx < Cfg::kBoxes; ++bx)
                 tma_load_4d(sQ + bx * Cfg::kBoxBytes, &tmQ, bar_q, bx * 64, q0, h, b);
-            bool ok = true;
-            for (int j = 0; j < n_kv && ok; ++j) {
-                const int s = j % NST;
-                const uint32_t use = uint32_t(j / NST);
-                if (j >= NST) ok = mbar_wait(&bar_k_free[s], (use - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
-                if (!ok) break;
+        }
+        __syncwarp();
+        for (int j = 0; j < n_kv; ++j) {
+            const int s = j % NST;
+            const uint32_t use = uint32_t(j / NST);
+            if (j >= NST &&
+                !mbar_wait_warp(&bar_k_free[s], (use - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE))
+                break;
+            if (elect_one()) {
                 mbar_arrive_expect_tx(&bar_k_full[s], Cfg::kTileBytes);
 #pragma unroll
                 for (int bx = 0; bx < Cfg::kBoxes; ++bx)
                     tma_load_4d(sK + s * Cfg::kTileBytes + bx * Cfg::kBoxBytes, &tmK, &bar_k_full[s], bx * 64, j * 128,
                                 hk, b);
-                if (j >= NST) ok = mbar_wait(&bar_v_free[s], (use - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
-                if (!ok) break;
+            }
+            __syncwarp();
+            if (j >= NST &&
+                !mbar_wait_warp(&bar_v_free[s], (use - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE))
+                break;
+            if (elect_one()) {
                 mbar_arrive_expect_tx(&bar_v_full[s], Cfg::kTileBytes);
 #pragma unroll
                 for (int bx = 0; bx < Cfg::kBoxes; ++bx)
                     tma_load_4d(sV + s * Cfg::kTileBytes + bx * Cfg::kBoxBytes, &tmV, &bar_v_full[s], bx * 64, j * 128,
                                 hk, b);
             }
+            __syncwarp();
         }
     } else if (warp == 5) {
         // ------------------------------------------------------------------ MMA issuer
-        reg_dealloc<48>();
-        if (lane == 0) {
-            constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
-            constexpr uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);
-            const uint32_t q_addr = smem_u32(sQ);
-            bool ok = mbar_wait(bar_q, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-            for (int j = 0; j < n_kv && ok; ++j) {
-                const int s = j % NST;
-                const uint32_t ph = uint32_t(j / NST) & 1;
-                ok = mbar_wait(&bar_k_full[s], ph, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-                if (!ok) break;
-                tc_fence_after_sync();
-                const uint32_t k_addr = smem_u32(sK + s * Cfg::kTileBytes);
+        // All 32 lanes run the loop; one elected lane issues.
+        reg_dealloc<56>();
+        constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+        constexpr uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);
+        const uint64_t q_desc = make_sdesc_sw128(smem_u32(sQ), 16, 1024);
+        bool ok = mbar_wait_warp(bar_q, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+        for (int j = 0; j < n_kv && ok; ++j) {
+            const int s = j % NST;
+            const uint32_t ph = uint32_t(j / NST) & 1;
+            ok = mbar_wait_warp(&bar_k_full[s], ph, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+            if (!ok) break;
+            B200ATTN_STAMP(lane == 0, 128 + 8 * j);
+            tc_fence_after_sync();
+            const uint64_t k_desc = make_sdesc_sw128(smem_u32(sK + s * Cfg::kTileBytes), 16, 1024);
+            if (elect_one()) {
 #pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t off = (ks / 4) * Cfg::kBoxBytes + (ks % 4) * 32;
-                    umma_ss(tmem + Cfg::kColS, make_sdesc_sw128(q_addr + off, 16, 1024),
-                            make_sdesc_sw128(k_addr + off, 16, 1024), idesc_s, ks > 0);
-                }
+                for (int ks = 0; ks < D / 16; ++ks)
+                    umma_ss(tmem + Cfg::kColS, q_desc + kmajor_step(ks, Cfg::kBoxBytes),
+                            k_desc + kmajor_step(ks, Cfg::kBoxBytes), idesc_s, ks > 0);
                 umma_commit(bar_s_full);
                 umma_commit(&bar_k_free[s]);
-                ok = mbar_wait(bar_p_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
-                if (!ok) break;
-                ok = mbar_wait(&bar_v_full[s], ph, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-                if (!ok) break;
-                tc_fence_after_sync();
-                const uint32_t v_addr = smem_u32(sV + s * Cfg::kTileBytes);
+            }
+            __syncwarp();
+            B200ATTN_STAMP(lane == 0, 129 + 8 * j);
+            ok = mbar_wait_warp(bar_p_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+            if (!ok) break;
+            B200ATTN_STAMP(lane == 0, 130 + 8 * j);
+            ok = mbar_wait_warp(&bar_v_full[s], ph, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+            if (!ok) break;
+            B200ATTN_STAMP(lane == 0, 131 + 8 * j);
+            tc_fence_after_sync();
+            const uint64_t v_desc = make_sdesc_sw128(smem_u32(sV + s * Cfg::kTileBytes), Cfg::kBoxBytes, 1024);
+            if (elect_one()) {
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    umma_ts(tmem + Cfg::kColO, tmem + Cfg::kColP + ks * 8,
-                            make_sdesc_sw128(v_addr + ks * 2048, Cfg::kBoxBytes, 1024), idesc_o, (j > 0) || (ks > 0));
-                }
+                for (int ks = 0; ks < 8; ++ks)
+                    umma_ts(tmem + Cfg::kColO, tmem + Cfg::kColP + ks * 8, v_desc + uint64_t(ks * 128), idesc_o,
+                            (j > 0) || (ks > 0));
                 umma_commit(bar_o_full);
                 umma_commit(&bar_v_free[s]);
             }
-            // Every MMA issued above has completed once this barrier fires; TMEM may then be freed.
-            umma_commit(bar_drain);
-            mbar_wait(bar_drain, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+            __syncwarp();
+            B200ATTN_STAMP(lane == 0, 132 + 8 * j);
         }
+        // Every MMA issued above has completed once this barrier fires; TMEM may then be freed.
+        if (elect_one()) umma_commit(bar_drain);
+        __syncwarp();
+        mbar_wait_warp(bar_drain, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
     } else {
         // ------------------------------------------------------------------ softmax + epilogue
-        reg_alloc<208>();
+        reg_alloc<200>();
         const int row = tid;                                   // query row inside the tile == TMEM lane
         const uint32_t lane_base = uint32_t(warp * 32) << 16;  // this warp's TMEM lane quadrant
         const uint32_t t_s = tmem + lane_base + Cfg::kColS;
@@ -209,11 +228,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int j = 0; j < n_kv; ++j) {
             ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA));
             if (!ok) break;
+            B200ATTN_STAMP(tid == 0, 8 + 8 * j);
             tc_fence_after_sync();
             uint32_t sr[128];
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_ld_x32(t_s + c * 32, &sr[c * 32]);
             tmem_wait_ld();
+            B200ATTN_STAMP(tid == 0, 9 + 8 * j);
             if (j == qt) {
                 // diagonal tile: key column c is visible to query row r iff c <= r
 #pragma unroll
@@ -255,6 +276,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 tmem_st_x16(t_p + c * 16, pk);
             }
             l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));
+            B200ATTN_STAMP(tid == 0, 10 + 8 * j);
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
                 // O must hold PV(j-1) before it is rescaled
                 ok = mbar_wait(bar_o_full, (j - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
@@ -274,9 +296,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(bar_p_full);
+            B200ATTN_STAMP(tid == 0, 11 + 8 * j);
         }
         if (ok) ok = mbar_wait(bar_o_full, (n_kv - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
         ok = __all_sync(0xffffffffu, ok);
+        B200ATTN_STAMP(tid == 0, 2);
         if (ok) {
             tc_fence_after_sync();
             const float inv_l = 1.f / l;
@@ -306,12 +330,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         tc_fence_before_sync();
         named_bar_sync(1, 128);
+        B200ATTN_STAMP(tid == 0, 3);
         if (ok && tid == 0) {
 #pragma unroll
             for (int bx = 0; bx < Cfg::kBoxes; ++bx) tma_store_4d(&tmO, sQ + bx * Cfg::kBoxBytes, bx * 64, q0, h, b);
             tma_store_commit();
             tma_store_wait_read0();
         }
+        B200ATTN_STAMP(tid == 0, 4);
     }
 
     // teardown: every role falls through to here, also after a wait that gave up

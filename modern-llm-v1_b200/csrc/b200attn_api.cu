@@ -397,3 +397,11 @@ extern "C" const char* b200attn_strerror(int status) {
 }
 
 extern "C" int b200attn_version(void) { return 1; }
+
+#ifdef B200ATTN_PROBE
+// Tuning builds only: copies the phase timestamps of the last launch to the host.
+extern "C" int b200attn_debug_read_probe(long long* host, int n) {
+    if (n > 512) n = 512;
+    return cudaMemcpyFromSymbol(host, b200attn::g_probe, sizeof(long long) * n) == cudaSuccess ? 0 : B200ATTN_ERR_CUDA;
+}
+#endif

@@ -184,6 +184,33 @@ __device__ __forceinline__ uint64_t make_sdesc_sw128(uint32_t smem_addr, uint32_
     return d;
 }
 
+// Elects one lane of a fully converged warp.  The MMA and TMA issuing warps run their loops
+// with all 32 lanes (so that addresses and descriptors stay in the uniform datapath) and
+// guard only the issuing instructions with this.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred = 0;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "elect.sync _|P, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(pred));
+    return pred != 0;
+}
+
+// Bounded wait executed by a whole warp; the result is made warp-uniform.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                               int code) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, code));
+}
+
+// Descriptor offset (in the 16-byte units of the start-address field) of K step `ks` of a
+// K-major operand made of [128 rows][64] boxes of `box_bytes`.
+__host__ __device__ constexpr uint32_t kmajor_step(int ks, int box_bytes) {
+    return uint32_t(((ks / 4) * box_bytes + (ks % 4) * 32) >> 4);
+}
+
 // ---------------------------------------------------------------------------
 // tcgen05.mma (issued by ONE thread), cta_group::1, kind::f16.
 // ---------------------------------------------------------------------------
@@ -294,6 +321,21 @@ template <int N>
 __device__ __forceinline__ void reg_dealloc() {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
+
+// Optional phase timestamps for tuning (compiled in only with -DB200ATTN_PROBE): the first
+// CTA of a launch records clock64() at numbered points into a device array.
+#ifdef B200ATTN_PROBE
+__device__ long long g_probe[512];
+#define B200ATTN_STAMP(cond, idx)                                                      \
+    do {                                                                               \
+        if ((cond) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (idx) < 512) \
+            g_probe[(idx)] = clock64();                                                \
+    } while (0)
+#else
+#define B200ATTN_STAMP(cond, idx) \
+    do {                          \
+    } while (0)
+#endif
 
 // Named barrier among a subset of the CTA's warps.
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {

@@ -1,0 +1,107 @@
+// See modernllm_shim.h.  Compiled inside the reference tree; links libb200attn.so.
+#include "modernllm_shim.h"
+
+#include <stdexcept>
+#include <string>
+
+#include "b200attn.h"
+
+namespace modernllm {
+namespace b200 {
+
+namespace {
+
+void check(const Tensor& t, DType want, const char* fn, const char* name) {
+    if (t.dtype() != want)
+        throw std::invalid_argument(std::string(fn) + ": " + name + (want == DType::BF16 ? " must be BF16" : " must be FP32"));
+}
+void check_cuda(const Tensor& t, const char* fn, const char* name) {
+    if (t.device() != Device::Cuda) throw std::invalid_argument(std::string(fn) + ": " + name + " must be CUDA");
+}
+
+void raise(int status, const char* fn) {
+    if (status == B200ATTN_OK) return;
+    std::string msg = std::string(fn) + ": " + b200attn_strerror(status);
+    if (status == B200ATTN_ERR_INVALID_ARG || status == B200ATTN_ERR_UNSUPPORTED ||
+        status == B200ATTN_ERR_ALIGNMENT || status == B200ATTN_ERR_WORKSPACE)
+        throw std::invalid_argument(msg);
+    throw std::runtime_error(msg);
+}
+
+}  // namespace
+
+void flash_attn_forward_gqa(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& ctx, Tensor& L, int B, int T,
+                            int Hq, int Hkv, int D, Layout layout) {
+    const char* fn = "flash_attn_forward";
+    check(q, DType::BF16, fn, "q"); check(k, DType::BF16, fn, "k"); check(v, DType::BF16, fn, "v");
+    check(ctx, DType::BF16, fn, "ctx"); check(L, DType::FP32, fn, "L");
+    check_cuda(q, fn, "q"); check_cuda(k, fn, "k"); check_cuda(v, fn, "v"); check_cuda(ctx, fn, "ctx");
+    check_cuda(L, fn, "L");
+    const long long nq = 1LL * B * Hq * T * D, nkv = 1LL * B * Hkv * T * D;
+    if (q.numel() != nq || ctx.numel() != nq || k.numel() != nkv || v.numel() != nkv)
+        throw std::invalid_argument("flash_attn_forward: shape mismatch (qkv/ctx)");
+    if (L.numel() != 1LL * B * Hq * T) throw std::invalid_argument("flash_attn_forward: L must be [B, T]");
+    raise(b200attn_fwd(q.data(), k.data(), v.data(), ctx.data(), L.data_as<float>(), B, T, Hq, Hkv, D,
+                       static_cast<int>(layout), 0.f, nullptr),
+          fn);
+}
+
+void flash_attn_backward_gqa(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& ctx, const Tensor& L,
+                             const Tensor& d_ctx, Tensor& d_q, Tensor& d_k, Tensor& d_v, int B, int T, int Hq,
+                             int Hkv, int D, Layout layout) {
+    const char* fn = "flash_attn_backward";
+    const Tensor* bf[] = {&q, &k, &v, &ctx, &d_ctx, &d_q, &d_k, &d_v};
+    const char* names[] = {"q", "k", "v", "ctx", "d_ctx", "d_q", "d_k", "d_v"};
+    for (int i = 0; i < 8; ++i) {
+        check(*bf[i], DType::BF16, fn, names[i]);
+        check_cuda(*bf[i], fn, names[i]);
+    }
+    check(L, DType::FP32, fn, "L");
+    check_cuda(L, fn, "L");
+    const long long nq = 1LL * B * Hq * T * D, nkv = 1LL * B * Hkv * T * D;
+    if (q.numel() != nq || ctx.numel() != nq || d_ctx.numel() != nq || d_q.numel() != nq || k.numel() != nkv ||
+        v.numel() != nkv || d_k.numel() != nkv || d_v.numel() != nkv)
+        throw std::invalid_argument("flash_attn_backward: shape mismatch");
+    if (L.numel() != 1LL * B * Hq * T) throw std::invalid_argument("flash_attn_backward: L must be [B, T]");
+    // private temporary, like the reference's Dh (llm/src/model/flash_attn.cu:463)
+    const long long ws_bytes = static_cast<long long>(b200attn_bwd_workspace_bytes(B, T, Hq, Hkv, D));
+    Tensor ws({ws_bytes / 4}, DType::FP32, Device::Cuda);
+    raise(b200attn_bwd(q.data(), k.data(), v.data(), ctx.data(), L.data_as<float>(), d_ctx.data(), d_q.data(),
+                       d_k.data(), d_v.data(), B, T, Hq, Hkv, D, static_cast<int>(layout), 0.f, ws.data(),
+                       static_cast<size_t>(ws_bytes), nullptr),
+          fn);
+    // the workspace is freed at scope exit: wait for the kernels that read it
+    raise(b200attn_last_device_status(nullptr), fn);
+}
+
+void flash_attn_forward(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& ctx, Tensor& L, int B, int T, int D,
+                        int tile_kv) {
+    if (tile_kv <= 0) throw std::invalid_argument("flash_attn_forward: tile_kv must be > 0");
+    flash_attn_forward_gqa(q, k, v, ctx, L, B, T, 1, 1, D, Layout::BHTD);
+}
+
+void flash_attn_backward(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& ctx, const Tensor& L,
+                         const Tensor& d_ctx, Tensor& d_q, Tensor& d_k, Tensor& d_v, int B, int T, int D, int tile) {
+    if (tile <= 0) throw std::invalid_argument("flash_attn_backward: tile must be > 0");
+    flash_attn_backward_gqa(q, k, v, ctx, L, d_ctx, d_q, d_k, d_v, B, T, 1, 1, D, Layout::BHTD);
+}
+
+void flash_attn_decode(const Tensor& q, const Tensor& kcache, const Tensor& vcache, Tensor& o, int B, int Lcache,
+                       int Hq, int Hkv, int D) {
+    const char* fn = "flash_attn_decode";
+    check(q, DType::BF16, fn, "q"); check(kcache, DType::BF16, fn, "kcache"); check(vcache, DType::BF16, fn, "vcache");
+    check(o, DType::BF16, fn, "o");
+    check_cuda(q, fn, "q"); check_cuda(kcache, fn, "kcache"); check_cuda(vcache, fn, "vcache"); check_cuda(o, fn, "o");
+    if (q.numel() != 1LL * B * Hq * D || o.numel() != q.numel() || kcache.numel() != 1LL * B * Hkv * Lcache * D ||
+        vcache.numel() != kcache.numel())
+        throw std::invalid_argument("flash_attn_decode: shape mismatch");
+    const long long ws_bytes = static_cast<long long>(b200attn_decode_workspace_bytes(B, Lcache, Hq, Hkv, D, 0));
+    Tensor ws({(ws_bytes + 3) / 4}, DType::FP32, Device::Cuda);
+    raise(b200attn_decode(q.data(), kcache.data(), vcache.data(), o.data(), nullptr, B, Lcache, Hq, Hkv, D, 0.f, 0,
+                          ws.data(), static_cast<size_t>(ws_bytes), nullptr),
+          fn);
+    raise(b200attn_last_device_status(nullptr), fn);
+}
+
+}  // namespace b200
+}  // namespace modernllm

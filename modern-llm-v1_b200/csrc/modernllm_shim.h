@@ -1,0 +1,43 @@
+// Source-compatible replacement of the reference's flash-attention entry points
+// (llm/src/model/flash_attn.h:25-28,47-52) on top of the b200attn C ABI.
+//
+// This header is meant to be compiled INSIDE the reference tree (it includes the
+// reference's own core/tensor.h), with libb200attn.so on the link line.  Differences
+// from the reference's declarations, all additive:
+//   * tensors are DType::BF16 (the engine's I/O type), L stays FP32;
+//   * `tile_kv` / `tile` are validated like the reference (<= 0 throws) and then ignored;
+//   * `_gqa` overloads take (B, T, Hq, Hkv, D) plus a layout and index the shared KV head
+//     directly, which replaces repeat_kv_heads / accumulate_kv_grads / split_heads /
+//     merge_heads around the call (llm/src/model/modern_gpt.cu:351-378, 505-552).
+// Error behaviour is the reference's: std::invalid_argument for bad arguments,
+// std::runtime_error for CUDA failures (llm/src/model/flash_attn.cu:386-407,
+// llm/src/core/cuda_check.h:12-27).
+#pragma once
+
+#include "core/tensor.h"
+
+namespace modernllm {
+namespace b200 {
+
+enum class Layout { BHTD = 0, BTHD = 1 };
+
+void flash_attn_forward(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& ctx, Tensor& L, int B, int T, int D,
+                        int tile_kv = 32);
+
+void flash_attn_backward(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& ctx, const Tensor& L,
+                         const Tensor& d_ctx, Tensor& d_q, Tensor& d_k, Tensor& d_v, int B, int T, int D,
+                         int tile = 16);
+
+void flash_attn_forward_gqa(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& ctx, Tensor& L, int B, int T,
+                            int Hq, int Hkv, int D, Layout layout = Layout::BHTD);
+
+void flash_attn_backward_gqa(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& ctx, const Tensor& L,
+                             const Tensor& d_ctx, Tensor& d_q, Tensor& d_k, Tensor& d_v, int B, int T, int Hq,
+                             int Hkv, int D, Layout layout = Layout::BHTD);
+
+// One query token per sequence against a [B, Hkv, Lcache, D] KV cache; q, o: [B, Hq, D].
+void flash_attn_decode(const Tensor& q, const Tensor& kcache, const Tensor& vcache, Tensor& o, int B, int Lcache,
+                       int Hq, int Hkv, int D);
+
+}  // namespace b200
+}  // namespace modernllm

@@ -35,7 +35,7 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 
 # DRAM traffic of the dominant kernel per launch at the default workload, from the committed ncu
 # summary (profiles/); None until a capture exists for the current kernel.
-NCU_TRAFFIC_BYTES = {"c2_50m_train": None}
+NCU_TRAFFIC_BYTES = {"c2_50m_train": 34382080}  # dK/dV pass: dram read + write, profiles/attn_fwd_bwd_c2_50m_train.md
 
 
 def load_peaks():

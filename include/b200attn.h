@@ -42,7 +42,8 @@ enum {
     B200ATTN_ERR_CUDA = 5,         /* a CUDA runtime call or a launch failed */
     B200ATTN_ERR_TENSOR_MAP = 6,   /* the driver refused a TMA tensor map */
     B200ATTN_ERR_DEVICE_WAIT = 7,  /* a kernel gave up on a bounded wait (see b200attn_last_device_status) */
-    B200ATTN_ERR_NO_DEVICE = 8     /* no sm_100 device is current */
+    B200ATTN_ERR_NO_DEVICE = 8,    /* no sm_100 device is current */
+    B200ATTN_ERR_TOO_LARGE = 9     /* problem exceeds the fixed scratch of b200attn_bwd_static */
 };
 
 enum { B200ATTN_LAYOUT_BHTD = 0, B200ATTN_LAYOUT_BTHD = 1 };
@@ -71,6 +72,37 @@ int b200attn_bwd(const void* q, const void* k, const void* v, const void* o, con
                  void* dq, void* dk, void* dv, int B, int T, int Hq, int Hkv, int D, int layout, float softmax_scale,
                  void* workspace, size_t workspace_bytes, void* stream);
 size_t b200attn_bwd_workspace_bytes(int B, int T, int Hq, int Hkv, int D);
+
+/*
+ * Backward without a workspace argument and without any allocation (this entry point has no
+ * counterpart in the reference, whose backward allocates its D vector with cudaMalloc on every
+ * call, llm/src/model/flash_attn.cu:463).
+ *
+ * Same inputs, outputs and results as b200attn_bwd (it runs the same kernels), but the two
+ * per-row FP32 vectors the backward needs live in a fixed array inside the library's device
+ * image instead of a caller-provided workspace.  It is meant for callers that cannot obtain
+ * device memory at the point of the call: code that runs between training steps under a
+ * caching allocator that must not see a raw cudaMalloc (which synchronises the whole device),
+ * latency-critical loops that forbid any allocation after start-up, and hosts that have no
+ * allocator of their own to hand a workspace from.  The library calls no cudaMalloc, cudaFree
+ * or other allocating routine here.
+ *
+ * Limit: B * Hq * ceil(T / 128) * 128 <= B200ATTN_BWD_STATIC_MAX_ROWS (524288, i.e. up to the
+ * long-context shape B=4, Hq=16, T=8192); larger problems return B200ATTN_ERR_TOO_LARGE and
+ * launch nothing.  The array costs 4 MiB of device memory on every GPU that loads the library,
+ * until the process exits.
+ *
+ * The first call on each device resolves the array's device address (with that device
+ * current); make that first call before any stream capture begins.  All calls on a device
+ * share the one array: it still holds the previous call's vectors when the next call starts
+ * (every call rewrites all the rows it uses, so nothing has to be cleared), and two calls
+ * whose kernels can overlap on the GPU - different streams, or graphs replayed concurrently -
+ * race on it.  Serialise them, or use b200attn_bwd with one workspace per stream.
+ */
+#define B200ATTN_BWD_STATIC_MAX_ROWS 524288
+int b200attn_bwd_static(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                        const void* dout, void* dq, void* dk, void* dv, int B, int T, int Hq, int Hkv, int D,
+                        int layout, float softmax_scale, void* stream);
 
 /*
  * Decode: one query token per sequence against a KV cache of L tokens (the cache

@@ -22,6 +22,8 @@ ERR_CUDA = 5
 ERR_TENSOR_MAP = 6
 ERR_DEVICE_WAIT = 7
 ERR_NO_DEVICE = 8
+ERR_TOO_LARGE = 9
+BWD_STATIC_MAX_ROWS = 524288
 
 LAYOUT_BHTD = 0
 LAYOUT_BTHD = 1
@@ -32,6 +34,7 @@ SYMBOLS = (
     "b200attn_fwd",
     "b200attn_bwd",
     "b200attn_bwd_workspace_bytes",
+    "b200attn_bwd_static",
     "b200attn_set_bwd_profile_events",
     "b200attn_decode",
     "b200attn_decode_workspace_bytes",
@@ -59,6 +62,8 @@ def load() -> ctypes.CDLL:
     L.b200attn_fwd.restype = i
     L.b200attn_bwd.argtypes = [vp] * 9 + [i, i, i, i, i, i, f, vp, sz, vp]
     L.b200attn_bwd.restype = i
+    L.b200attn_bwd_static.argtypes = [vp] * 9 + [i, i, i, i, i, i, f, vp]
+    L.b200attn_bwd_static.restype = i
     L.b200attn_bwd_workspace_bytes.argtypes = [i, i, i, i, i]
     L.b200attn_bwd_workspace_bytes.restype = sz
     L.b200attn_set_bwd_profile_events.argtypes = [vp, vp, vp, vp]
@@ -87,6 +92,6 @@ def check(status: int, where: str) -> None:
     if status == OK:
         return
     msg = f"{where}: {strerror(status)} (status {status})"
-    if status in (ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_WORKSPACE):
+    if status in (ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_WORKSPACE, ERR_TOO_LARGE):
         raise ValueError(msg)
     raise RuntimeError(msg)

@@ -247,6 +247,52 @@ extern "C" int b200attn_bwd(const void* q, const void* k, const void* v, const v
                    : launch_bwd<128>(tq, tk, tv, tdo, tdq, tdk, tdv, pre, p, st);
 }
 
+// ---------------------------------------------------------------------------------------
+// Backward with its scratch in the library's own device image: no allocation anywhere.
+// ---------------------------------------------------------------------------------------
+namespace {
+
+// Two FP32 vectors of B200ATTN_BWD_STATIC_MAX_ROWS rows (logsumexp * log2(e) and rowsum(O * dO)).
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) float g_bwd_static_scratch[2 * B200ATTN_BWD_STATIC_MAX_ROWS];
+
+float* g_bwd_static_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the array on the current device, resolved once per device.
+float* bwd_static_scratch(int* err) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        *err = B200ATTN_ERR_NO_DEVICE;
+        return nullptr;
+    }
+    if (!g_bwd_static_ptr[dev]) {
+        float* ptr = nullptr;
+        if (cudaGetSymbolAddress((void**)&ptr, g_bwd_static_scratch) != cudaSuccess || ptr == nullptr) {
+            cudaGetLastError();
+            *err = B200ATTN_ERR_CUDA;
+            return nullptr;
+        }
+        g_bwd_static_ptr[dev] = ptr;
+    }
+    return g_bwd_static_ptr[dev];
+}
+
+}  // namespace
+
+extern "C" int b200attn_bwd_static(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                                   const void* dout, void* dq, void* dk, void* dv, int B, int T, int Hq, int Hkv, int D,
+                                   int layout, float softmax_scale, void* stream) {
+    int rc = check_common(B, T, Hq, Hkv, D, layout);
+    if (rc) return rc;
+    if (bwd_vec_elems(B, T, Hq) > (size_t)B200ATTN_BWD_STATIC_MAX_ROWS) return B200ATTN_ERR_TOO_LARGE;
+    float* scratch = bwd_static_scratch(&rc);
+    if (!scratch) return rc;
+    // Same kernels as b200attn_bwd; the preprocess kernel rewrites every row (padding included) that
+    // the two passes read, so stale contents of an earlier call are never seen.
+    return b200attn_bwd(q, k, v, o, lse, dout, dq, dk, dv, B, T, Hq, Hkv, D, layout, softmax_scale, scratch,
+                        2 * sizeof(float) * (size_t)B200ATTN_BWD_STATIC_MAX_ROWS, stream);
+}
+
 namespace {
 
 // Query heads served per decode CTA: the largest divisor of the group size that is <= 8.
@@ -388,6 +434,8 @@ extern "C" const char* b200attn_strerror(int status) {
         case B200ATTN_ERR_TENSOR_MAP: return "the driver refused a TMA tensor map";
         case B200ATTN_ERR_DEVICE_WAIT: return "a kernel gave up on a bounded wait";
         case B200ATTN_ERR_NO_DEVICE: return "no usable CUDA device is current";
+        case B200ATTN_ERR_TOO_LARGE:
+            return "problem exceeds the fixed scratch of b200attn_bwd_static (B*Hq*ceil(T/128)*128 > 524288)";
         case DEV_WAIT_TIMEOUT_LOAD: return "device: a TMA load barrier never completed";
         case DEV_WAIT_TIMEOUT_MMA: return "device: a tensor-core completion barrier never completed";
         case DEV_WAIT_TIMEOUT_SOFTMAX: return "device: a softmax hand-off barrier never completed";

@@ -32,7 +32,7 @@ def test_library_exports_every_declared_symbol(lib):
 
 def test_version_and_strerror(lib):
     assert lib.b200attn_version() >= 1
-    for code in range(0, 9):
+    for code in range(0, 10):
         assert lib.b200attn_strerror(code).decode() not in ("", "unknown status")
     assert lib.b200attn_strerror(12345).decode() == "unknown status"
 

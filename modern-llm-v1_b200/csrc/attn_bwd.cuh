@@ -13,12 +13,18 @@
 // Roles in both passes (320 threads):
 //   warps 0-7  compute: thread owns TMEM lane (warp % 4) * 32 + lane and the 64 score
 //              columns of its half (warp / 4)
-//   warp  8    TMA producer (one elected lane)
-//   warp  9    TMEM allocation and tcgen05.mma issue (one elected lane)
-// TMEM (512 columns): [0,128) S, [128,256) dP, [256,256+D) accumulator 0,
-//   [384,384+D) accumulator 1.  The BF16 operands of the second-stage MMAs overwrite the
-//   FP32 scores they were computed from: half h of a 128-wide block keeps its 64 BF16
-//   values in the first 32 columns of its own 64-column range.
+//   warp  8    TMA producer (converged warp, one elected lane issues)
+//   warp  9    TMEM allocation and tcgen05.mma issue (converged warp, one elected lane issues)
+// TMEM (512 columns), D = 64:  S buffer 0 [0,128), S buffer 1 [128,256), dP [256,384),
+//   accumulators [384,448) and [448,512).  With two S buffers the next tile's QK^T product
+//   is issued while the compute warps still work on the current tile.
+//   D = 128: one S buffer [0,128), dP [128,256), accumulators [256,384) and [384,512).
+// The compute step has two phases so that it can start on S before dP has arrived:
+//   A: P = exp2(S * scale*log2e - L*log2e)   (kept in registers; the dK/dV pass also stores it)
+//   B: dS = P * (dP - D)                      (stored over dP as BF16)
+// The BF16 operands of the second-stage MMAs overwrite the FP32 values they were computed
+// from: half h of a 128-wide block keeps its 64 BF16 values in the first 32 columns of its
+// own 64-column range.
 #pragma once
 
 #include "ptx.cuh"
@@ -80,19 +86,24 @@ __global__ void __launch_bounds__(256) attn_bwd_preprocess_kernel(const PreParam
     }
 }
 
+
 template <int D>
 struct BwdCfg {
+    static constexpr bool kDoubleS = (D == 64);
+    static constexpr int kStages = kDoubleS ? 3 : 2;  // streamed operand pairs in shared memory
     static constexpr int kTileBytes = 128 * D * 2;
     static constexpr int kBoxBytes = 128 * 64 * 2;
     static constexpr int kBoxes = D / 64;
-    static constexpr int kVecBytes = 2 * 2 * 512;  // two stages of (lse2, dvec) for 128 rows
+    static constexpr int kVecBytes = kStages * 2 * 512;  // per stage (lse2, dvec) of 128 rows
     static constexpr int kBarBytes = 256;
-    static constexpr int kSmemBytes = 6 * kTileBytes + kVecBytes + kBarBytes + 1024;
+    static constexpr int kSmemBytes = (2 + 2 * kStages) * kTileBytes + kVecBytes + kBarBytes + 1024;
     static constexpr int kTmemCols = 512;
-    static constexpr int kColS = 0;
-    static constexpr int kColDP = 128;
-    static constexpr int kColAcc0 = 256;
-    static constexpr int kColAcc1 = 384;
+    static constexpr int kColS0 = 0;
+    static constexpr int kColS1 = kDoubleS ? 128 : 0;
+    static constexpr int kColDP = kDoubleS ? 256 : 128;
+    static constexpr int kColAcc0 = kDoubleS ? 384 : 256;
+    static constexpr int kColAcc1 = kDoubleS ? 448 : 384;
+    __host__ __device__ static constexpr int col_s(int buf) { return buf ? kColS1 : kColS0; }
 };
 
 // D[tmem] = A[smem, K-major] * B[smem, K-major]^T over the head dimension; a_desc / b_desc
@@ -154,19 +165,22 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                    const __grid_constant__ CUtensorMap tmdQ, const BwdParams p) {
     using Cfg = BwdCfg<D>;
+    constexpr int NST = Cfg::kStages;
+    constexpr bool DBL = Cfg::kDoubleS;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;
     uint8_t* sdO = sQ + Cfg::kTileBytes;
-    uint8_t* sK = sdO + Cfg::kTileBytes;      // [2]
-    uint8_t* sV = sK + 2 * Cfg::kTileBytes;   // [2]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * Cfg::kTileBytes + Cfg::kVecBytes);
+    uint8_t* sK = sdO + Cfg::kTileBytes;        // [NST]
+    uint8_t* sV = sK + NST * Cfg::kTileBytes;   // [NST]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + NST * Cfg::kTileBytes + Cfg::kVecBytes);
     uint64_t* bar_q = bars + 0;
-    uint64_t* bar_sdp_full = bars + 1;
-    uint64_t* bar_ds_full = bars + 2;
-    uint64_t* bar_acc = bars + 3;
-    uint64_t* bar_kv_full = bars + 4;  // [2]
-    uint64_t* bar_kv_free = bars + 6;  // [2]
+    uint64_t* bar_s_full = bars + 1;   // [2] one per S buffer
+    uint64_t* bar_dp_full = bars + 3;
+    uint64_t* bar_ds_full = bars + 4;
+    uint64_t* bar_acc = bars + 5;
+    uint64_t* bar_kv_full = bars + 6;          // [NST]
+    uint64_t* bar_kv_free = bars + 6 + NST;    // [NST]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
 
@@ -184,10 +198,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
     if (tid == 0) {
         mbar_init(bar_q, 1);
-        mbar_init(bar_sdp_full, 1);
+        mbar_init(&bar_s_full[0], 1);
+        mbar_init(&bar_s_full[1], 1);
+        mbar_init(bar_dp_full, 1);
         mbar_init(bar_ds_full, 256);
         mbar_init(bar_acc, 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < NST; ++s) {
             mbar_init(&bar_kv_full[s], 1);
             mbar_init(&bar_kv_free[s], 1);
         }
@@ -221,9 +237,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         __syncwarp();
         for (int j = 0; j < n_kv; ++j) {
-            const int s = j & 1;
-            if (j >= 2 &&
-                !mbar_wait_warp(&bar_kv_free[s], ((j >> 1) - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE))
+            const int s = j % NST;
+            if (j >= NST &&
+                !mbar_wait_warp(&bar_kv_free[s], ((j / NST) - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE))
                 break;
             if (elect_one()) {
                 mbar_arrive_expect_tx(&bar_kv_full[s], 2 * Cfg::kTileBytes);
@@ -243,18 +259,33 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
         const uint64_t q_desc = kmajor_desc<D>(sQ), do_desc = kmajor_desc<D>(sdO);
         bool ok = mbar_wait_warp(bar_q, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-        if (ok) ok = mbar_wait_warp(&bar_kv_full[0], 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-        if (ok) {
+        // S(j) = Q K_j^T into S buffer (j & 1 when double-buffered); waits for the tile's loads first
+        auto issue_s = [&](int j) -> bool {
+            const int s = j % NST;
+            if (!mbar_wait_warp(&bar_kv_full[s], (j / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD))
+                return false;
             tc_fence_after_sync();
+            const int buf = DBL ? (j & 1) : 0;
             if (elect_one()) {
-                issue_ss_over_headdim<D>(tmem + Cfg::kColS, q_desc, kmajor_desc<D>(sK), idesc_s);
-                issue_ss_over_headdim<D>(tmem + Cfg::kColDP, do_desc, kmajor_desc<D>(sV), idesc_s);
-                umma_commit(bar_sdp_full);
+                issue_ss_over_headdim<D>(tmem + Cfg::col_s(buf), q_desc, kmajor_desc<D>(sK + s * Cfg::kTileBytes), idesc_s);
+                umma_commit(&bar_s_full[buf]);
             }
             __syncwarp();
-        }
+            return true;
+        };
+        auto issue_dp = [&](int j) {  // dP(j) = dO V_j^T; the loads of tile j are known to be complete
+            const int s = j % NST;
+            if (elect_one()) {
+                issue_ss_over_headdim<D>(tmem + Cfg::kColDP, do_desc, kmajor_desc<D>(sV + s * Cfg::kTileBytes), idesc_s);
+                umma_commit(bar_dp_full);
+            }
+            __syncwarp();
+        };
+        if (ok) ok = issue_s(0);
+        if (ok) issue_dp(0);
+        if (ok && DBL && n_kv > 1) ok = issue_s(1);
         for (int j = 0; j < n_kv && ok; ++j) {
-            const int s = j & 1;
+            const int s = j % NST;
             ok = mbar_wait_warp(bar_ds_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
             if (!ok) break;
             tc_fence_after_sync();
@@ -266,18 +297,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             }
             __syncwarp();
             if (j + 1 < n_kv) {
-                const int s1 = (j + 1) & 1;
-                ok = mbar_wait_warp(&bar_kv_full[s1], ((j + 1) >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-                if (!ok) break;
-                tc_fence_after_sync();
-                if (elect_one()) {
-                    issue_ss_over_headdim<D>(tmem + Cfg::kColS, q_desc, kmajor_desc<D>(sK + s1 * Cfg::kTileBytes),
-                                             idesc_s);
-                    issue_ss_over_headdim<D>(tmem + Cfg::kColDP, do_desc, kmajor_desc<D>(sV + s1 * Cfg::kTileBytes),
-                                             idesc_s);
-                    umma_commit(bar_sdp_full);
+                if (!DBL) {
+                    ok = issue_s(j + 1);
+                    if (!ok) break;
                 }
-                __syncwarp();
+                issue_dp(j + 1);  // S(j+1) was issued earlier, so its loads have landed
+            }
+            if (DBL && j + 2 < n_kv) {
+                ok = issue_s(j + 2);
+                if (!ok) break;
             }
         }
         if (elect_one()) umma_commit(bar_acc);
@@ -293,28 +321,40 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const float dv = p.dvec[vrow];
         bool ok = true;
         for (int j = 0; j < n_kv; ++j) {
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_sdp_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA));
+            const int buf = DBL ? (j & 1) : 0;
+            const uint32_t s_par = DBL ? ((j >> 1) & 1) : (j & 1);
+            ok = mbar_wait_warp(&bar_s_full[buf], s_par, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
             if (!ok) break;
             tc_fence_after_sync();
+            // phase A: P from S
+            float pr[64];
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
-                uint32_t sv[32], dp[32], pk[16];
-                tmem_ld_x32(tmem + lane_base + Cfg::kColS + c0 + c * 32, sv);
+                uint32_t sv[32];
+                tmem_ld_x32(tmem + lane_base + Cfg::col_s(buf) + c0 + c * 32, sv);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    pr[c * 32 + i] = ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse2));
+            }
+            if (j == qt) {
+#pragma unroll
+                for (int i = 0; i < 64; ++i)
+                    if (c0 + i > row) pr[i] = 0.f;  // key above the diagonal
+            }
+            ok = mbar_wait_warp(bar_dp_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+            if (!ok) break;
+            tc_fence_after_sync();
+            // phase B: dS = P (dP - D), written over dP as BF16
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t dp[32], pk[16];
                 tmem_ld_x32(tmem + lane_base + Cfg::kColDP + c0 + c * 32, dp);
                 tmem_wait_ld();
-                float ds[32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float pr = ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse2));
-                    ds[i] = pr * (__uint_as_float(dp[i]) - dv);
-                }
-                if (j == qt) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (c0 + c * 32 + i > row) ds[i] = 0.f;  // key above the diagonal
-                }
-#pragma unroll
-                for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(ds[2 * i], ds[2 * i + 1]);
+                for (int i = 0; i < 16; ++i)
+                    pk[i] = pack_bf16x2(pr[c * 32 + 2 * i] * (__uint_as_float(dp[2 * i]) - dv),
+                                        pr[c * 32 + 2 * i + 1] * (__uint_as_float(dp[2 * i + 1]) - dv));
                 tmem_st_x16(tmem + lane_base + Cfg::kColDP + c0 + c * 16, pk);
             }
             tmem_wait_st();
@@ -364,21 +404,24 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                      const __grid_constant__ CUtensorMap tmdK, const __grid_constant__ CUtensorMap tmdV,
                      const BwdParams p) {
     using Cfg = BwdCfg<D>;
+    constexpr int NST = Cfg::kStages;
+    constexpr bool DBL = Cfg::kDoubleS;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sK = smem;
     uint8_t* sV = sK + Cfg::kTileBytes;
-    uint8_t* sQ = sV + Cfg::kTileBytes;       // [2]
-    uint8_t* sdO = sQ + 2 * Cfg::kTileBytes;  // [2]
-    float* sLse = reinterpret_cast<float*>(sdO + 2 * Cfg::kTileBytes);  // [2][128]
-    float* sDv = sLse + 2 * 128;                                         // [2][128]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sdO + 2 * Cfg::kTileBytes + Cfg::kVecBytes);
+    uint8_t* sQ = sV + Cfg::kTileBytes;         // [NST]
+    uint8_t* sdO = sQ + NST * Cfg::kTileBytes;  // [NST]
+    float* sLse = reinterpret_cast<float*>(sdO + NST * Cfg::kTileBytes);  // [NST][128]
+    float* sDv = sLse + NST * 128;                                         // [NST][128]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sdO + NST * Cfg::kTileBytes + Cfg::kVecBytes);
     uint64_t* bar_kv = bars + 0;
-    uint64_t* bar_sdp_full = bars + 1;
-    uint64_t* bar_pds_full = bars + 2;
-    uint64_t* bar_acc = bars + 3;
-    uint64_t* bar_full = bars + 4;  // [2]
-    uint64_t* bar_free = bars + 6;  // [2]
+    uint64_t* bar_s_full = bars + 1;  // [2]
+    uint64_t* bar_dp_full = bars + 3;
+    uint64_t* bar_pds_full = bars + 4;
+    uint64_t* bar_acc = bars + 5;
+    uint64_t* bar_full = bars + 6;        // [NST]
+    uint64_t* bar_free = bars + 6 + NST;  // [NST]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
 
@@ -386,8 +429,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     const int kt = blockIdx.x;  // tile 0 has the most query tiles below it: heaviest first
     const int hk = blockIdx.y, b = blockIdx.z;
     const int k0 = kt * 128;
-    const int n_i = p.n_tiles - kt;     // query tiles kt .. n_tiles-1
-    const int n_it = p.group * n_i;     // times the query heads of the group
+    const int n_i = p.n_tiles - kt;  // query tiles kt .. n_tiles-1
+    const int n_it = p.group * n_i;  // times the query heads of the group
 
     if (tid == 0) *abort_flag = *reinterpret_cast<volatile int*>(p.status);
     __syncthreads();
@@ -396,10 +439,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
 
     if (tid == 0) {
         mbar_init(bar_kv, 1);
-        mbar_init(bar_sdp_full, 1);
+        mbar_init(&bar_s_full[0], 1);
+        mbar_init(&bar_s_full[1], 1);
+        mbar_init(bar_dp_full, 1);
         mbar_init(bar_pds_full, 256);
         mbar_init(bar_acc, 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < NST; ++s) {
             mbar_init(&bar_full[s], 1);
             mbar_init(&bar_free[s], 1);
         }
@@ -434,11 +479,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         }
         __syncwarp();
         for (int it = 0; it < n_it; ++it) {
-            const int s = it & 1;
+            const int s = it % NST;
             const int h = hk * p.group + it / n_i;
             const int i = kt + it % n_i;
-            if (it >= 2 &&
-                !mbar_wait_warp(&bar_free[s], ((it >> 1) - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE))
+            if (it >= NST &&
+                !mbar_wait_warp(&bar_free[s], ((it / NST) - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE))
                 break;
             if (elect_one()) {
                 mbar_arrive_expect_tx(&bar_full[s], 2 * Cfg::kTileBytes + 1024);
@@ -461,43 +506,58 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
         const uint64_t k_desc = kmajor_desc<D>(sK), v_desc = kmajor_desc<D>(sV);
         bool ok = mbar_wait_warp(bar_kv, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-        if (ok) ok = mbar_wait_warp(&bar_full[0], 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-        if (ok) {
+        auto issue_s = [&](int it) -> bool {  // S^T(it) = K Q^T
+            const int s = it % NST;
+            if (!mbar_wait_warp(&bar_full[s], (it / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD)) return false;
             tc_fence_after_sync();
+            const int buf = DBL ? (it & 1) : 0;
             if (elect_one()) {
-                issue_ss_over_headdim<D>(tmem + Cfg::kColS, k_desc, kmajor_desc<D>(sQ), idesc_s);     // S^T  = K Q^T
-                issue_ss_over_headdim<D>(tmem + Cfg::kColDP, v_desc, kmajor_desc<D>(sdO), idesc_s);   // dP^T = V dO^T
-                umma_commit(bar_sdp_full);
+                issue_ss_over_headdim<D>(tmem + Cfg::col_s(buf), k_desc, kmajor_desc<D>(sQ + s * Cfg::kTileBytes), idesc_s);
+                umma_commit(&bar_s_full[buf]);
             }
             __syncwarp();
-        }
+            return true;
+        };
+        auto issue_dp = [&](int it) {  // dP^T(it) = V dO^T; the loads of `it` are known to be complete
+            const int s = it % NST;
+            if (elect_one()) {
+                issue_ss_over_headdim<D>(tmem + Cfg::kColDP, v_desc, kmajor_desc<D>(sdO + s * Cfg::kTileBytes), idesc_s);
+                umma_commit(bar_dp_full);
+            }
+            __syncwarp();
+        };
+        if (ok) ok = issue_s(0);
+        if (ok) issue_dp(0);
+        if (ok && DBL && n_it > 1) ok = issue_s(1);
         for (int it = 0; it < n_it && ok; ++it) {
-            const int s = it & 1;
+            const int s = it % NST;
+            const int buf = DBL ? (it & 1) : 0;
             ok = mbar_wait_warp(bar_pds_full, it & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
             if (!ok) break;
+            B200ATTN_STAMP(lane == 0, 200 + 4 * it);
             tc_fence_after_sync();
             if (elect_one()) {
                 // dV += P^T dO ; dK += dS^T Q
-                issue_ts_over_rows<D>(tmem + Cfg::kColAcc0, tmem + Cfg::kColS, mnmajor_desc<D>(sdO + s * Cfg::kTileBytes),
-                                      idesc_acc, it > 0);
+                issue_ts_over_rows<D>(tmem + Cfg::kColAcc0, tmem + Cfg::col_s(buf),
+                                      mnmajor_desc<D>(sdO + s * Cfg::kTileBytes), idesc_acc, it > 0);
                 issue_ts_over_rows<D>(tmem + Cfg::kColAcc1, tmem + Cfg::kColDP, mnmajor_desc<D>(sQ + s * Cfg::kTileBytes),
                                       idesc_acc, it > 0);
                 umma_commit(&bar_free[s]);
             }
             __syncwarp();
+            B200ATTN_STAMP(lane == 0, 201 + 4 * it);
             if (it + 1 < n_it) {
-                const int s1 = (it + 1) & 1;
-                ok = mbar_wait_warp(&bar_full[s1], ((it + 1) >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-                if (!ok) break;
-                tc_fence_after_sync();
-                if (elect_one()) {
-                    issue_ss_over_headdim<D>(tmem + Cfg::kColS, k_desc, kmajor_desc<D>(sQ + s1 * Cfg::kTileBytes), idesc_s);
-                    issue_ss_over_headdim<D>(tmem + Cfg::kColDP, v_desc, kmajor_desc<D>(sdO + s1 * Cfg::kTileBytes),
-                                             idesc_s);
-                    umma_commit(bar_sdp_full);
+                if (!DBL) {
+                    ok = issue_s(it + 1);
+                    if (!ok) break;
                 }
-                __syncwarp();
+                issue_dp(it + 1);
             }
+            if (DBL && it + 2 < n_it) {
+                ok = issue_s(it + 2);
+                if (!ok) break;
+            }
+            B200ATTN_STAMP(lane == 0, 202 + 4 * it);
         }
         if (elect_one()) umma_commit(bar_acc);
         __syncwarp();
@@ -509,51 +569,65 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         const int c0 = half * 64;  // first query column of this thread's half
         bool ok = true;
         for (int it = 0; it < n_it; ++it) {
-            const int s = it & 1;
+            const int s = it % NST;
+            const int buf = DBL ? (it & 1) : 0;
+            const uint32_t s_par = DBL ? ((it >> 1) & 1) : (it & 1);
             const bool diag = (it % n_i) == 0;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_sdp_full, it & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA));
+            ok = mbar_wait_warp(&bar_s_full[buf], s_par, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
             if (!ok) break;
+            B200ATTN_STAMP(tid == 0, 8 + 4 * it);
             tc_fence_after_sync();
             const float4* lse4 = reinterpret_cast<const float4*>(sLse + s * 128 + c0);
             const float4* dv4 = reinterpret_cast<const float4*>(sDv + s * 128 + c0);
+            // phase A: P^T from S^T (kept in registers and stored over S^T as BF16)
+            float pr[64];
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
-                uint32_t sv[32], dp[32], pk[16], dk[16];
-                tmem_ld_x32(tmem + lane_base + Cfg::kColS + c0 + c * 32, sv);
-                tmem_ld_x32(tmem + lane_base + Cfg::kColDP + c0 + c * 32, dp);
+                uint32_t sv[32], pk[16];
+                tmem_ld_x32(tmem + lane_base + Cfg::col_s(buf) + c0 + c * 32, sv);
                 tmem_wait_ld();
-                float pr[32], ds[32];
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
                     const float4 l4 = lse4[c * 8 + g];
-                    const float4 d4 = dv4[c * 8 + g];
-                    const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
-                    const float dd[4] = {d4.x, d4.y, d4.z, d4.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int i = g * 4 + e;
-                        pr[i] = ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lv[e]));
-                        ds[i] = __uint_as_float(dp[i]) - dd[e];
-                    }
+                    pr[c * 32 + g * 4 + 0] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 0]), p.scale_log2, -l4.x));
+                    pr[c * 32 + g * 4 + 1] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 1]), p.scale_log2, -l4.y));
+                    pr[c * 32 + g * 4 + 2] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 2]), p.scale_log2, -l4.z));
+                    pr[c * 32 + g * 4 + 3] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 3]), p.scale_log2, -l4.w));
                 }
                 if (diag) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        if (c0 + c * 32 + i < row) pr[i] = 0.f;  // query above the key: masked
+                        if (c0 + c * 32 + i < row) pr[c * 32 + i] = 0.f;  // query above the key: masked
                 }
 #pragma unroll
-                for (int i = 0; i < 32; ++i) ds[i] *= pr[i];
+                for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(pr[c * 32 + 2 * i], pr[c * 32 + 2 * i + 1]);
+                tmem_st_x16(tmem + lane_base + Cfg::col_s(buf) + c0 + c * 16, pk);
+            }
+            ok = mbar_wait_warp(bar_dp_full, it & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+            if (!ok) break;
+            B200ATTN_STAMP(tid == 0, 10 + 4 * it);
+            tc_fence_after_sync();
+            // phase B: dS^T = P^T (dP^T - D), stored over dP^T as BF16
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    pk[i] = pack_bf16x2(pr[2 * i], pr[2 * i + 1]);
-                    dk[i] = pack_bf16x2(ds[2 * i], ds[2 * i + 1]);
+            for (int c = 0; c < 2; ++c) {
+                uint32_t dp[32], pk[16];
+                tmem_ld_x32(tmem + lane_base + Cfg::kColDP + c0 + c * 32, dp);
+                tmem_wait_ld();
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const float4 d4 = dv4[c * 8 + g];
+                    const int i = c * 32 + g * 4;
+                    pk[g * 2 + 0] = pack_bf16x2(pr[i + 0] * (__uint_as_float(dp[g * 4 + 0]) - d4.x),
+                                                pr[i + 1] * (__uint_as_float(dp[g * 4 + 1]) - d4.y));
+                    pk[g * 2 + 1] = pack_bf16x2(pr[i + 2] * (__uint_as_float(dp[g * 4 + 2]) - d4.z),
+                                                pr[i + 3] * (__uint_as_float(dp[g * 4 + 3]) - d4.w));
                 }
-                tmem_st_x16(tmem + lane_base + Cfg::kColS + c0 + c * 16, pk);
-                tmem_st_x16(tmem + lane_base + Cfg::kColDP + c0 + c * 16, dk);
+                tmem_st_x16(tmem + lane_base + Cfg::kColDP + c0 + c * 16, pk);
             }
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(bar_pds_full);
+            B200ATTN_STAMP(tid == 0, 9 + 4 * it);
         }
         if (ok) ok = mbar_wait(bar_acc, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
         ok = __all_sync(0xffffffffu, ok);

@@ -74,8 +74,8 @@ int check_common(int B, int T, int Hq, int Hkv, int D, int layout) {
 }
 
 template <int D>
-int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to,
-               const FwdParams& p, cudaStream_t st) {
+int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
+               cudaStream_t st) {
     using Cfg = FwdCfg<D>;
     static bool attr_set[kMaxDevices] = {false};
     int dev = 0;
@@ -88,8 +88,8 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
         }
         attr_set[dev] = true;
     }
-    dim3 grid(p.n_qtiles, p.Hq, p.B);
-    attn_fwd_kernel<D><<<grid, 256, Cfg::kSmemBytes, st>>>(tq, tk, tv, to, p);
+    const unsigned grid = (unsigned)p.n_qtiles * (unsigned)p.Hq * (unsigned)p.B;
+    attn_fwd_kernel<D><<<grid, 256, Cfg::kSmemBytes, st>>>(tq, tk, tv, p);
     return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
 }
 
@@ -104,11 +104,10 @@ extern "C" int b200attn_fwd(const void* q, const void* k, const void* v, void* o
     int* status = status_ptr(&rc);
     if (!status) return rc;
     const Strides sq = strides_for(layout, Hq, T, D), sk = strides_for(layout, Hkv, T, D);
-    CUtensorMap tq, tk, tv, to;
+    CUtensorMap tq, tk, tv;
     if (!make_tmap_bf16_4d(&tq, q, D, T, Hq, B, sq.t, sq.h, sq.b, 128) ||
-        !make_tmap_bf16_4d(&tk, k, D, T, Hkv, B, sk.t, sk.h, sk.b, 128) ||
-        !make_tmap_bf16_4d(&tv, v, D, T, Hkv, B, sk.t, sk.h, sk.b, 128) ||
-        !make_tmap_bf16_4d(&to, o, D, T, Hq, B, sq.t, sq.h, sq.b, 128))
+        !make_tmap_bf16_4d(&tk, k, D, T, Hkv, B, sk.t, sk.h, sk.b, 64) ||
+        !make_tmap_bf16_4d(&tv, v, D, T, Hkv, B, sk.t, sk.h, sk.b, 64))
         return B200ATTN_ERR_TENSOR_MAP;
     FwdParams p;
     p.B = B;
@@ -120,9 +119,13 @@ extern "C" int b200attn_fwd(const void* q, const void* k, const void* v, void* o
     p.scale = softmax_scale > 0.f ? softmax_scale : 1.f / sqrtf((float)D);
     p.scale_log2 = p.scale * 1.4426950408889634f;
     p.lse = lse;
+    p.o = static_cast<uint16_t*>(o);
+    p.o_st = sq.t;
+    p.o_sh = sq.h;
+    p.o_sb = sq.b;
     p.status = status;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return D == 64 ? launch_fwd<64>(tq, tk, tv, to, p, st) : launch_fwd<128>(tq, tk, tv, to, p, st);
+    return D == 64 ? launch_fwd<64>(tq, tk, tv, p, st) : launch_fwd<128>(tq, tk, tv, p, st);
 }
 
 namespace {
@@ -451,5 +454,10 @@ extern "C" int b200attn_version(void) { return 1; }
 extern "C" int b200attn_debug_read_probe(long long* host, int n) {
     if (n > 512) n = 512;
     return cudaMemcpyFromSymbol(host, b200attn::g_probe, sizeof(long long) * n) == cudaSuccess ? 0 : B200ATTN_ERR_CUDA;
+}
+extern "C" int b200attn_debug_read_trace(unsigned long long* host, int n_ctas) {
+    if (n_ctas > 8192) n_ctas = 8192;
+    return cudaMemcpyFromSymbol(host, b200attn::g_trace, sizeof(unsigned long long) * 3 * n_ctas) == cudaSuccess
+               ? 0 : B200ATTN_ERR_CUDA;
 }
 #endif

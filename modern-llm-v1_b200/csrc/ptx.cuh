@@ -331,7 +331,38 @@ __device__ long long g_probe[512];
         if ((cond) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (idx) < 512) \
             g_probe[(idx)] = clock64();                                                \
     } while (0)
+// Per-CTA trace: SM id and begin/end times (ns) of every CTA of a launch (first 8192 CTAs).
+__device__ unsigned long long g_trace[8192 * 3];
+__device__ __forceinline__ unsigned long long b200attn_globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ unsigned b200attn_smid() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(r));
+    return r;
+}
+#define B200ATTN_TRACE_BEGIN()                                                                      \
+    do {                                                                                            \
+        const unsigned lin_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);       \
+        if (threadIdx.x == 0 && lin_ < 8192) {                                                      \
+            g_trace[lin_ * 3 + 0] = b200attn_smid();                                                \
+            g_trace[lin_ * 3 + 1] = b200attn_globaltimer();                                         \
+        }                                                                                           \
+    } while (0)
+#define B200ATTN_TRACE_END()                                                                        \
+    do {                                                                                            \
+        const unsigned lin_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);       \
+        if (threadIdx.x == 0 && lin_ < 8192) g_trace[lin_ * 3 + 2] = b200attn_globaltimer();        \
+    } while (0)
 #else
+#define B200ATTN_TRACE_BEGIN() \
+    do {                       \
+    } while (0)
+#define B200ATTN_TRACE_END() \
+    do {                     \
+    } while (0)
 #define B200ATTN_STAMP(cond, idx) \
     do {                          \
     } while (0)

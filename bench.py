@@ -235,7 +235,7 @@ def kernel_breakdown(m, cfg, sets, steps):
 
     lib = m._lib.load()
     n = min(steps, 200)
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(n)]
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(n)]
     for row in evs:  # events get their CUDA handle on first record
         for e in row:
             e.record()
@@ -243,17 +243,17 @@ def kernel_breakdown(m, cfg, sets, steps):
     for i in range(n):
         s = sets[i % len(sets)]
         e = evs[i]
-        m._lib.check(lib.b200attn_set_bwd_profile_events(e[2].cuda_event, e[3].cuda_event, e[4].cuda_event,
-                                                         e[5].cuda_event), "set_bwd_profile_events")
+        m._lib.check(lib.b200attn_set_bwd_profile_events(e[2].cuda_event, e[3].cuda_event, e[4].cuda_event),
+                     "set_bwd_profile_events")
         e[0].record()
         m.flash_attn_forward_gqa(s.q, s.k, s.v, s.o, s.lse, cfg.B, cfg.T, cfg.Hq, cfg.Hkv, cfg.D)
         e[1].record()
         m.flash_attn_backward_gqa(s.q, s.k, s.v, s.o, s.lse, s.do, s.dq, s.dk, s.dv, cfg.B, cfg.T, cfg.Hq, cfg.Hkv,
                                   cfg.D)
-    lib.b200attn_set_bwd_profile_events(None, None, None, None)
+    lib.b200attn_set_bwd_profile_events(None, None, None)
     torch.cuda.synchronize()
-    names = ["attn_fwd_kernel", "attn_bwd_preprocess_kernel", "attn_bwd_dkdv_kernel", "attn_bwd_dq_kernel"]
-    pairs = [(0, 1), (2, 3), (3, 4), (4, 5)]
+    names = ["attn_fwd_kernel", "attn_bwd_dq_kernel", "attn_bwd_dkdv_kernel"]
+    pairs = [(0, 1), (2, 3), (3, 4)]
     out = {}
     for name, (a, b) in zip(names, pairs):
         out[name] = sum(e[a].elapsed_time(e[b]) for e in evs) / n  # ms
@@ -440,7 +440,7 @@ def main():
             "per_gpu_tflops": value / world,
             "pct_of_bf16_peak": {"burst": 100 * value / world / float(peaks["bf16_tflops"]),
                                  "sustained": 100 * value / world / peak, "source": peaks["_source"]},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": 4 * steps, "roofline": roofline,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": 3 * steps, "roofline": roofline,
             "checksum_dq_abs_sum": checksum,
         }
         if cpu is not None:

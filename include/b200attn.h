@@ -61,8 +61,8 @@ int b200attn_fwd(const void* q, const void* k, const void* v, void* o, float* ls
 /*
  * Backward: dq, dk, dv (overwritten, not accumulated) from q, k, v, o, lse, dout.
  * Replaces flash_attn_backward (llm/src/model/flash_attn.h:47-52,
- * llm/src/model/flash_attn.cu:428-504): D = rowsum(o * dout), a dQ pass and a dK/dV
- * pass.  dk/dv are already summed over the query heads of each KV group (what
+ * llm/src/model/flash_attn.cu:428-504): a dQ pass (which also computes D = rowsum(o * dout)) and
+ * a dK/dV pass.  dk/dv are already summed over the query heads of each KV group (what
  * accumulate_kv_grads does in the reference, llm/src/model/attention.cu:510-543),
  * in a fixed order, so results are bit-reproducible.  The reference allocates its
  * D vector per call (llm/src/model/flash_attn.cu:463); here the caller passes a
@@ -122,14 +122,13 @@ size_t b200attn_decode_workspace_bytes(int B, int L, int Hq, int Hkv, int D, int
 int b200attn_decode_default_splits(int B, int L, int Hq, int Hkv, int D);
 
 /*
- * Diagnostics for benchmarks (no counterpart in the reference): when four CUDA events are
- * set, every following b200attn_bwd records them on its stream before the preprocess
- * kernel, after it, after the dK/dV pass and after the dQ pass, so a caller can time each
- * kernel of the backward.  Pass four NULLs to switch it off (the default).  The events stay
+ * Diagnostics for benchmarks (no counterpart in the reference): when three CUDA events are
+ * set, every following b200attn_bwd records them on its stream before the dQ pass (which also
+ * computes D = rowsum(o * dout)), after it, and after the dK/dV pass, so a caller can time each
+ * kernel of the backward.  Pass three NULLs to switch it off (the default).  The events stay
  * owned by the caller.
  */
-int b200attn_set_bwd_profile_events(void* ev_start, void* ev_after_preprocess, void* ev_after_dkdv,
-                                    void* ev_after_dq);
+int b200attn_set_bwd_profile_events(void* ev_start, void* ev_after_dq, void* ev_after_dkdv);
 
 /*
  * Synchronises `stream` and returns the device status word of the current device:

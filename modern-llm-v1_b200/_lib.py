@@ -66,7 +66,7 @@ def load() -> ctypes.CDLL:
     L.b200attn_bwd_static.restype = i
     L.b200attn_bwd_workspace_bytes.argtypes = [i, i, i, i, i]
     L.b200attn_bwd_workspace_bytes.restype = sz
-    L.b200attn_set_bwd_profile_events.argtypes = [vp, vp, vp, vp]
+    L.b200attn_set_bwd_profile_events.argtypes = [vp, vp, vp]
     L.b200attn_set_bwd_profile_events.restype = i
     L.b200attn_decode.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, f, i, vp, sz, vp]
     L.b200attn_decode.restype = i

@@ -1,6 +1,7 @@
 // Causal grouped-query attention backward for sm_100a, the three steps of the
 // reference's flash_attn_backward (llm/src/model/flash_attn.cu:428-504, math :137-146):
 //   1. preprocess  D[i] = sum_d O[i,d] dO[i,d]            (flash_attn_compute_D_kernel, :150-172)
+//                  - done by the dQ pass for its own rows, no separate kernel
 //   2. dQ pass     query tile stationary, walks key tiles  (flash_attn_dq_kernel, :175-274)
 //   3. dK/dV pass  key tile stationary, walks query tiles  (flash_attn_dkdv_kernel, :277-379)
 // with  P = exp(s - L),  dP = dO V^T,  dS = P (dP - D),  dQ = scale dS K,
@@ -10,7 +11,7 @@
 // the query heads of its group and keeps one accumulator, which replaces
 // accumulate_kv_grads (llm/src/model/attention.cu:412-429,510-543).
 //
-// Roles in both passes (320 threads):
+// Roles in the dK/dV pass (320 threads; the dQ pass is described at its kernel):
 //   warps 0-7  compute: thread owns TMEM lane (warp % 4) * 32 + lane and the 64 score
 //              columns of its half (warp / 4)
 //   warp  8    TMA producer (converged warp, one elected lane issues)
@@ -34,58 +35,17 @@ namespace b200attn {
 struct BwdParams {
     int B, T, Tpad, Hq, Hkv, group, n_tiles;
     float scale, scale_log2;
-    const float* lse2;  // [B, Hq, Tpad]  logsumexp * log2(e); +inf in the padding rows
-    const float* dvec;  // [B, Hq, Tpad]  rowsum(O * dO);       0 in the padding rows
+    const float* lse2;  // [B, Hq, Tpad]  logsumexp * log2(e); +inf in the padding rows   (read by the dK/dV pass)
+    const float* dvec;  // [B, Hq, Tpad]  rowsum(O * dO);       0 in the padding rows     (read by the dK/dV pass)
+    float* lse2_w;      // the same two vectors, written by the dQ pass
+    float* dvec_w;
+    const float* lse;       // [B, Hq, T]
+    const uint16_t* o;      // forward output, q layout
+    const uint16_t* dout;   // upstream gradient, q layout
+    uint16_t* dq;           // q layout
+    long long q_st, q_sh, q_sb;  // element strides of the q layout: token, head, batch
     int* status;
 };
-
-struct PreParams {
-    const uint16_t* o;
-    const uint16_t* dout;
-    const float* lse;  // [B, Hq, T]
-    float* lse2;       // [B, Hq, Tpad]
-    float* dvec;       // [B, Hq, Tpad]
-    int B, T, Tpad, Hq;
-    long long st, sh, sb;  // element strides of o / dout
-};
-
-// One thread per 8 head-dim elements; D/8 neighbouring lanes reduce one row.
-template <int D>
-__global__ void __launch_bounds__(256) attn_bwd_preprocess_kernel(const PreParams p) {
-    constexpr int LPR = D / 8;  // lanes per row
-    const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long row = gid / LPR;
-    const int part = int(gid % LPR);
-    const long long rows = (long long)p.B * p.Hq * p.Tpad;
-    const bool in_range = row < rows;
-    const int t = in_range ? int(row % p.Tpad) : 0;
-    const long long bh = in_range ? row / p.Tpad : 0;
-    float acc = 0.f;
-    if (in_range && t < p.T) {
-        const long long off = (bh / p.Hq) * p.sb + (bh % p.Hq) * p.sh + (long long)t * p.st + part * 8;
-        const uint4 a = *reinterpret_cast<const uint4*>(p.o + off);
-        const uint4 g = *reinterpret_cast<const uint4*>(p.dout + off);
-        const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
-        const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            acc = fmaf(__uint_as_float(aw[i] << 16), __uint_as_float(gw[i] << 16), acc);
-            acc = fmaf(__uint_as_float(aw[i] & 0xffff0000u), __uint_as_float(gw[i] & 0xffff0000u), acc);
-        }
-    }
-#pragma unroll
-    for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (in_range && part == 0) {
-        if (t < p.T) {
-            p.dvec[row] = acc;
-            p.lse2[row] = p.lse[bh * p.T + t] * 1.4426950408889634f;
-        } else {
-            p.dvec[row] = 0.f;
-            p.lse2[row] = INFINITY;  // exp2(x - inf) = 0: padding query rows contribute nothing
-        }
-    }
-}
-
 
 template <int D>
 struct BwdCfg {
@@ -157,205 +117,253 @@ __device__ __forceinline__ void stage_row_chunk(uint8_t* tile, int row, int col,
 }
 
 // ---------------------------------------------------------------------------------------
-// dQ pass: one CTA per (query tile, query head, batch).
+// dQ pass: one CTA per (128-row query tile, query head, batch), walking 64-key tiles.
+// It also does the preprocess step for its rows, D = rowsum(O * dO) and L * log2(e)
+// (flash_attn_compute_D_kernel, llm/src/model/flash_attn.cu:150-172), and leaves both in the
+// workspace for the dK/dV pass, which therefore has to run after this kernel.
+//
+// Roles (192 threads): warps 0-3 compute (thread r owns query row r == TMEM lane r),
+// warp 4 TMA producer, warp 5 TMEM allocation + MMA issue (converged warps, elected lane).
+// TMEM: S buffer 0 [0,64), S buffer 1 [64,128), dP [128,192) (dS as BF16 over its first 32
+// columns), dQ accumulator [192,192+D).  D = 64 needs 256 columns, so two CTAs share an SM.
 // ---------------------------------------------------------------------------------------
 template <int D>
-__global__ void __launch_bounds__(320, 1)
+struct DqCfg {
+    static constexpr int kKeys = 64;
+    static constexpr int kStages = (D == 64) ? 4 : 2;
+    static constexpr int kQTileBytes = 128 * D * 2;
+    static constexpr int kQBoxBytes = 128 * 64 * 2;
+    static constexpr int kKVTileBytes = kKeys * D * 2;
+    static constexpr int kKVBoxBytes = kKeys * 64 * 2;
+    static constexpr int kBoxes = D / 64;
+    static constexpr int kSmemBytes = 2 * kQTileBytes + 2 * kStages * kKVTileBytes + 256 + 1024;
+    static constexpr int kTmemCols = (D == 64) ? 256 : 512;
+    static constexpr int kCtasPerSm = (D == 64) ? 2 : 1;
+    static constexpr int kColS0 = 0, kColS1 = 64, kColDP = 128, kColAcc = 192;
+};
+
+template <int D>
+__global__ void __launch_bounds__(192, DqCfg<D>::kCtasPerSm)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                   const __grid_constant__ CUtensorMap tmdQ, const BwdParams p) {
-    using Cfg = BwdCfg<D>;
+                   const BwdParams p) {
+    using Cfg = DqCfg<D>;
     constexpr int NST = Cfg::kStages;
-    constexpr bool DBL = Cfg::kDoubleS;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;
-    uint8_t* sdO = sQ + Cfg::kTileBytes;
-    uint8_t* sK = sdO + Cfg::kTileBytes;        // [NST]
-    uint8_t* sV = sK + NST * Cfg::kTileBytes;   // [NST]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + NST * Cfg::kTileBytes + Cfg::kVecBytes);
+    uint8_t* sdO = sQ + Cfg::kQTileBytes;
+    uint8_t* sK = sdO + Cfg::kQTileBytes;        // [NST]
+    uint8_t* sV = sK + NST * Cfg::kKVTileBytes;  // [NST]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + NST * Cfg::kKVTileBytes);
     uint64_t* bar_q = bars + 0;
-    uint64_t* bar_s_full = bars + 1;   // [2] one per S buffer
+    uint64_t* bar_s_full = bars + 1;  // [2]
     uint64_t* bar_dp_full = bars + 3;
     uint64_t* bar_ds_full = bars + 4;
     uint64_t* bar_acc = bars + 5;
-    uint64_t* bar_kv_full = bars + 6;          // [NST]
-    uint64_t* bar_kv_free = bars + 6 + NST;    // [NST]
+    uint64_t* bar_kv_full = bars + 6;        // [NST]
+    uint64_t* bar_kv_free = bars + 6 + NST;  // [NST]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int qt = p.n_tiles - 1 - int(blockIdx.x);
-    const int h = blockIdx.y, b = blockIdx.z;
+    // 1-D grid ordered by work: all CTAs of the heaviest query tile come first
+    const int n_bh = p.B * p.Hq;
+    const int qt = p.n_tiles - 1 - int(blockIdx.x) / n_bh;
+    const int h = (int(blockIdx.x) % n_bh) % p.Hq, b = (int(blockIdx.x) % n_bh) / p.Hq;
     const int hk = h / p.group;
     const int q0 = qt * 128;
-    const int n_kv = qt + 1;
+    const int k_end = min(p.T, q0 + 128);
+    const int n_kv = (k_end + Cfg::kKeys - 1) / Cfg::kKeys;
 
-    if (tid == 0) *abort_flag = *reinterpret_cast<volatile int*>(p.status);
-    __syncthreads();
-    if (*abort_flag != 0) return;
-    __syncthreads();
-
-    if (tid == 0) {
+    // Set-up with one CTA-wide barrier (see the forward kernel).
+    if (warp == 4 && lane == 0) {
+        const int failed = *reinterpret_cast<volatile int*>(p.status);
+        *abort_flag = failed;
         mbar_init(bar_q, 1);
         mbar_init(&bar_s_full[0], 1);
         mbar_init(&bar_s_full[1], 1);
         mbar_init(bar_dp_full, 1);
-        mbar_init(bar_ds_full, 256);
+        mbar_init(bar_ds_full, 128);
         mbar_init(bar_acc, 1);
         for (int s = 0; s < NST; ++s) {
             mbar_init(&bar_kv_full[s], 1);
             mbar_init(&bar_kv_free[s], 1);
         }
         fence_mbar_init();
+        if (!failed) {
+            mbar_arrive_expect_tx(bar_q, 2 * Cfg::kQTileBytes);
+#pragma unroll
+            for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
+                tma_load_4d(sQ + bx * Cfg::kQBoxBytes, &tmQ, bar_q, bx * 64, q0, h, b);
+                tma_load_4d(sdO + bx * Cfg::kQBoxBytes, &tmdO, bar_q, bx * 64, q0, h, b);
+            }
+            const int n_pre = n_kv < NST ? n_kv : NST;
+            for (int j = 0; j < n_pre; ++j) {
+                mbar_arrive_expect_tx(&bar_kv_full[j], 2 * Cfg::kKVTileBytes);
+#pragma unroll
+                for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
+                    tma_load_4d(sK + j * Cfg::kKVTileBytes + bx * Cfg::kKVBoxBytes, &tmK, &bar_kv_full[j], bx * 64,
+                                j * Cfg::kKeys, hk, b);
+                    tma_load_4d(sV + j * Cfg::kKVTileBytes + bx * Cfg::kKVBoxBytes, &tmV, &bar_kv_full[j], bx * 64,
+                                j * Cfg::kKeys, hk, b);
+                }
+            }
+        }
     }
-    if (warp == 9) {
+    if (warp == 5) {
         tmem_alloc(tmem_slot, Cfg::kTmemCols);
         tmem_relinquish();
-    }
-    if (warp == 8 && lane == 0) {
-        tma_prefetch_desc(&tmQ);
-        tma_prefetch_desc(&tmK);
-        tma_prefetch_desc(&tmV);
-        tma_prefetch_desc(&tmdO);
-        tma_prefetch_desc(&tmdQ);
     }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    const bool failed_early = (*abort_flag != 0);
 
-    if (warp == 8) {
-        // ------------------------------------------------------------------ producer (whole warp, one lane issues)
-        if (elect_one()) {
-            mbar_arrive_expect_tx(bar_q, 2 * Cfg::kTileBytes);
-#pragma unroll
-            for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
-                tma_load_4d(sQ + bx * Cfg::kBoxBytes, &tmQ, bar_q, bx * 64, q0, h, b);
-                tma_load_4d(sdO + bx * Cfg::kBoxBytes, &tmdO, bar_q, bx * 64, q0, h, b);
-            }
-        }
-        __syncwarp();
-        for (int j = 0; j < n_kv; ++j) {
+    if (failed_early) {
+        // nothing was started; fall through to the teardown
+    } else if (warp == 4) {
+        // ------------------------------------------------------------------ producer (tiles >= NST)
+        for (int j = NST; j < n_kv; ++j) {
             const int s = j % NST;
-            if (j >= NST &&
-                !mbar_wait_warp(&bar_kv_free[s], ((j / NST) - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE))
+            if (!mbar_wait_warp(&bar_kv_free[s], ((j / NST) - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE))
                 break;
             if (elect_one()) {
-                mbar_arrive_expect_tx(&bar_kv_full[s], 2 * Cfg::kTileBytes);
+                mbar_arrive_expect_tx(&bar_kv_full[s], 2 * Cfg::kKVTileBytes);
 #pragma unroll
                 for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
-                    tma_load_4d(sK + s * Cfg::kTileBytes + bx * Cfg::kBoxBytes, &tmK, &bar_kv_full[s], bx * 64, j * 128,
-                                hk, b);
-                    tma_load_4d(sV + s * Cfg::kTileBytes + bx * Cfg::kBoxBytes, &tmV, &bar_kv_full[s], bx * 64, j * 128,
-                                hk, b);
+                    tma_load_4d(sK + s * Cfg::kKVTileBytes + bx * Cfg::kKVBoxBytes, &tmK, &bar_kv_full[s], bx * 64,
+                                j * Cfg::kKeys, hk, b);
+                    tma_load_4d(sV + s * Cfg::kKVTileBytes + bx * Cfg::kKVBoxBytes, &tmV, &bar_kv_full[s], bx * 64,
+                                j * Cfg::kKeys, hk, b);
                 }
             }
             __syncwarp();
         }
-    } else if (warp == 9) {
-        // ------------------------------------------------------------------ MMA issuer (whole warp, one lane issues)
-        constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+    } else if (warp == 5) {
+        // ------------------------------------------------------------------ MMA issuer
+        constexpr uint32_t idesc_s = make_idesc_bf16(128, Cfg::kKeys, 0, 0);
         constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
-        const uint64_t q_desc = kmajor_desc<D>(sQ), do_desc = kmajor_desc<D>(sdO);
+        const uint64_t q_desc = make_sdesc_sw128(smem_u32(sQ), 16, 1024);
+        const uint64_t do_desc = make_sdesc_sw128(smem_u32(sdO), 16, 1024);
         bool ok = mbar_wait_warp(bar_q, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-        // S(j) = Q K_j^T into S buffer (j & 1 when double-buffered); waits for the tile's loads first
-        auto issue_s = [&](int j) -> bool {
+        auto issue_s = [&](int j) -> bool {  // S(j) = Q K_j^T into S buffer j & 1
             const int s = j % NST;
             if (!mbar_wait_warp(&bar_kv_full[s], (j / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD))
                 return false;
             tc_fence_after_sync();
-            const int buf = DBL ? (j & 1) : 0;
+            const uint64_t k_desc = make_sdesc_sw128(smem_u32(sK + s * Cfg::kKVTileBytes), 16, 1024);
             if (elect_one()) {
-                issue_ss_over_headdim<D>(tmem + Cfg::col_s(buf), q_desc, kmajor_desc<D>(sK + s * Cfg::kTileBytes), idesc_s);
-                umma_commit(&bar_s_full[buf]);
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks)
+                    umma_ss(tmem + ((j & 1) ? Cfg::kColS1 : Cfg::kColS0), q_desc + kmajor_step(ks, Cfg::kQBoxBytes),
+                            k_desc + kmajor_step(ks, Cfg::kKVBoxBytes), idesc_s, ks > 0);
+                umma_commit(&bar_s_full[j & 1]);
             }
             __syncwarp();
             return true;
         };
-        auto issue_dp = [&](int j) {  // dP(j) = dO V_j^T; the loads of tile j are known to be complete
+        auto issue_dp = [&](int j) {  // dP(j) = dO V_j^T; tile j's loads have landed (S(j) was issued)
             const int s = j % NST;
+            const uint64_t v_desc = make_sdesc_sw128(smem_u32(sV + s * Cfg::kKVTileBytes), 16, 1024);
             if (elect_one()) {
-                issue_ss_over_headdim<D>(tmem + Cfg::kColDP, do_desc, kmajor_desc<D>(sV + s * Cfg::kTileBytes), idesc_s);
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks)
+                    umma_ss(tmem + Cfg::kColDP, do_desc + kmajor_step(ks, Cfg::kQBoxBytes),
+                            v_desc + kmajor_step(ks, Cfg::kKVBoxBytes), idesc_s, ks > 0);
                 umma_commit(bar_dp_full);
             }
             __syncwarp();
         };
         if (ok) ok = issue_s(0);
         if (ok) issue_dp(0);
-        if (ok && DBL && n_kv > 1) ok = issue_s(1);
+        if (ok && n_kv > 1) ok = issue_s(1);
         for (int j = 0; j < n_kv && ok; ++j) {
             const int s = j % NST;
             ok = mbar_wait_warp(bar_ds_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
             if (!ok) break;
             tc_fence_after_sync();
+            const uint64_t kmn_desc = make_sdesc_sw128(smem_u32(sK + s * Cfg::kKVTileBytes), Cfg::kKVBoxBytes, 1024);
             if (elect_one()) {
-                // dQ += dS K_j
-                issue_ts_over_rows<D>(tmem + Cfg::kColAcc0, tmem + Cfg::kColDP, mnmajor_desc<D>(sK + s * Cfg::kTileBytes),
-                                      idesc_acc, j > 0);
+                // dQ += dS_j K_j : 64 keys = 4 K steps, dS in the first 32 columns of the dP block
+#pragma unroll
+                for (int ks = 0; ks < Cfg::kKeys / 16; ++ks)
+                    umma_ts(tmem + Cfg::kColAcc, tmem + Cfg::kColDP + ks * 8, kmn_desc + uint64_t(ks * 128), idesc_acc,
+                            (j > 0) || (ks > 0));
                 umma_commit(&bar_kv_free[s]);
             }
             __syncwarp();
-            if (j + 1 < n_kv) {
-                if (!DBL) {
-                    ok = issue_s(j + 1);
-                    if (!ok) break;
-                }
-                issue_dp(j + 1);  // S(j+1) was issued earlier, so its loads have landed
-            }
-            if (DBL && j + 2 < n_kv) {
-                ok = issue_s(j + 2);
-                if (!ok) break;
-            }
+            if (j + 1 < n_kv) issue_dp(j + 1);
+            if (j + 2 < n_kv) ok = issue_s(j + 2);
         }
         if (elect_one()) umma_commit(bar_acc);
         __syncwarp();
     } else {
         // ------------------------------------------------------------------ compute
-        const int w4 = warp & 3, half = warp >> 2;
-        const int row = w4 * 32 + lane;  // query row in the tile == TMEM lane
-        const uint32_t lane_base = uint32_t(w4 * 32) << 16;
-        const int c0 = half * 64;  // first key column of this thread's half
+        const int row = tid;  // query row in the tile == TMEM lane
+        const uint32_t lane_base = uint32_t(warp * 32) << 16;
+        const bool in_range = q0 + row < p.T;
         const size_t vrow = (size_t(b) * p.Hq + h) * p.Tpad + q0 + row;
-        const float lse2 = p.lse2[vrow];
-        const float dv = p.dvec[vrow];
+        const size_t qoff = size_t(b) * p.q_sb + size_t(h) * p.q_sh + size_t(q0 + row) * p.q_st;
+        // preprocess for this row, under the latency of the first loads
+        float lse2 = INFINITY;  // exp2(x - inf) = 0: padding query rows contribute nothing
+        float dv = 0.f;
+        if (in_range) {
+            const uint4* orow = reinterpret_cast<const uint4*>(p.o + qoff);
+            const uint4* grow = reinterpret_cast<const uint4*>(p.dout + qoff);
+#pragma unroll
+            for (int c = 0; c < D / 8; ++c) {
+                const uint4 a = orow[c], g = grow[c];
+                const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+                const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    dv = fmaf(__uint_as_float(aw[i] << 16), __uint_as_float(gw[i] << 16), dv);
+                    dv = fmaf(__uint_as_float(aw[i] & 0xffff0000u), __uint_as_float(gw[i] & 0xffff0000u), dv);
+                }
+            }
+            lse2 = p.lse[(size_t(b) * p.Hq + h) * p.T + q0 + row] * 1.4426950408889634f;
+        }
+        p.lse2_w[vrow] = lse2;
+        p.dvec_w[vrow] = dv;
         bool ok = true;
         for (int j = 0; j < n_kv; ++j) {
-            const int buf = DBL ? (j & 1) : 0;
-            const uint32_t s_par = DBL ? ((j >> 1) & 1) : (j & 1);
-            ok = mbar_wait_warp(&bar_s_full[buf], s_par, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+            const uint32_t t_s = tmem + lane_base + ((j & 1) ? Cfg::kColS1 : Cfg::kColS0);
+            ok = mbar_wait_warp(&bar_s_full[j & 1], uint32_t(j >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
             if (!ok) break;
             tc_fence_after_sync();
             // phase A: P from S
             float pr[64];
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t sv[32];
-                tmem_ld_x32(tmem + lane_base + Cfg::col_s(buf) + c0 + c * 32, sv);
+            {
+                uint32_t sv[64];
+                tmem_ld_x32(t_s, &sv[0]);
+                tmem_ld_x32(t_s + 32, &sv[32]);
                 tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    pr[c * 32 + i] = ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse2));
+                for (int i = 0; i < 64; ++i) pr[i] = ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse2));
             }
-            if (j == qt) {
+            const int kbase = j * Cfg::kKeys;
+            if (kbase + Cfg::kKeys - 1 > q0) {
+                const int lim = q0 + row - kbase;  // columns c <= lim are visible
 #pragma unroll
                 for (int i = 0; i < 64; ++i)
-                    if (c0 + i > row) pr[i] = 0.f;  // key above the diagonal
+                    if (i > lim) pr[i] = 0.f;
             }
             ok = mbar_wait_warp(bar_dp_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
             if (!ok) break;
             tc_fence_after_sync();
             // phase B: dS = P (dP - D), written over dP as BF16
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t dp[32], pk[16];
-                tmem_ld_x32(tmem + lane_base + Cfg::kColDP + c0 + c * 32, dp);
+            {
+                uint32_t dp[64], pk[32];
+                tmem_ld_x32(tmem + lane_base + Cfg::kColDP, &dp[0]);
+                tmem_ld_x32(tmem + lane_base + Cfg::kColDP + 32, &dp[32]);
                 tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    pk[i] = pack_bf16x2(pr[c * 32 + 2 * i] * (__uint_as_float(dp[2 * i]) - dv),
-                                        pr[c * 32 + 2 * i + 1] * (__uint_as_float(dp[2 * i + 1]) - dv));
-                tmem_st_x16(tmem + lane_base + Cfg::kColDP + c0 + c * 16, pk);
+                for (int i = 0; i < 32; ++i)
+                    pk[i] = pack_bf16x2(pr[2 * i] * (__uint_as_float(dp[2 * i]) - dv),
+                                        pr[2 * i + 1] * (__uint_as_float(dp[2 * i + 1]) - dv));
+                tmem_st_x32(tmem + lane_base + Cfg::kColDP, pk);
             }
             tmem_wait_st();
             tc_fence_before_sync();
@@ -365,29 +373,28 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             tc_fence_after_sync();
+            uint16_t* dqrow = p.dq + qoff;
 #pragma unroll
-            for (int c = 0; c < D / 64; ++c) {
+            for (int c = 0; c < D / 32; ++c) {
                 uint32_t v[32];
-                const int col = half * (D / 2) + c * 32;
-                tmem_ld_x32(tmem + lane_base + Cfg::kColAcc0 + col, v);
+                tmem_ld_x32(tmem + lane_base + Cfg::kColAcc + c * 32, v);
                 tmem_wait_ld();
-                stage_row_chunk<D>(sQ, row, col, v, p.scale);
-            }
-            fence_proxy_async_smem();
-        }
-        tc_fence_before_sync();
-        named_bar_sync(1, 256);
-        if (ok && tid == 0) {
 #pragma unroll
-            for (int bx = 0; bx < Cfg::kBoxes; ++bx) tma_store_4d(&tmdQ, sQ + bx * Cfg::kBoxBytes, bx * 64, q0, h, b);
-            tma_store_commit();
-            tma_store_wait_read0();
+                for (int g = 0; g < 4; ++g) {
+                    uint4 w;
+                    w.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]) * p.scale, __uint_as_float(v[g * 8 + 1]) * p.scale);
+                    w.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * p.scale, __uint_as_float(v[g * 8 + 3]) * p.scale);
+                    w.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * p.scale, __uint_as_float(v[g * 8 + 5]) * p.scale);
+                    w.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * p.scale, __uint_as_float(v[g * 8 + 7]) * p.scale);
+                    if (in_range) *reinterpret_cast<uint4*>(dqrow + c * 32 + g * 8) = w;
+                }
+            }
         }
     }
 
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == 5) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, Cfg::kTmemCols);
     }
@@ -426,8 +433,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kt = blockIdx.x;  // tile 0 has the most query tiles below it: heaviest first
-    const int hk = blockIdx.y, b = blockIdx.z;
+    // 1-D grid ordered by work: key tile 0 has the most query tiles below it, so all its CTAs come first
+    const int n_bh = p.B * p.Hkv;
+    const int kt = int(blockIdx.x) / n_bh;
+    const int hk = (int(blockIdx.x) % n_bh) % p.Hkv, b = (int(blockIdx.x) % n_bh) / p.Hkv;
     const int k0 = kt * 128;
     const int n_i = p.n_tiles - kt;  // query tiles kt .. n_tiles-1
     const int n_it = p.group * n_i;  // times the query heads of the group

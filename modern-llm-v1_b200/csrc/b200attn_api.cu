@@ -146,43 +146,40 @@ int set_smem_once(K kernel, int bytes, bool* done) {
     return B200ATTN_OK;
 }
 
-cudaEvent_t g_bwd_events[4] = {nullptr, nullptr, nullptr, nullptr};
+cudaEvent_t g_bwd_events[3] = {nullptr, nullptr, nullptr};
 
 inline void record_bwd_event(int i, cudaStream_t st) {
     if (g_bwd_events[i]) cudaEventRecord(g_bwd_events[i], st);
 }
 
 template <int D>
-int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
-               const CUtensorMap& tdq, const CUtensorMap& tdk, const CUtensorMap& tdv, const PreParams& pre,
+int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk64, const CUtensorMap& tv64, const CUtensorMap& tk,
+               const CUtensorMap& tv, const CUtensorMap& tdo, const CUtensorMap& tdk, const CUtensorMap& tdv,
                const BwdParams& p, cudaStream_t st) {
-    using Cfg = BwdCfg<D>;
     static bool dq_set[kMaxDevices] = {false}, dkdv_set[kMaxDevices] = {false};
-    int rc = set_smem_once(attn_bwd_dq_kernel<D>, Cfg::kSmemBytes, dq_set);
+    int rc = set_smem_once(attn_bwd_dq_kernel<D>, DqCfg<D>::kSmemBytes, dq_set);
     if (rc) return rc;
-    rc = set_smem_once(attn_bwd_dkdv_kernel<D>, Cfg::kSmemBytes, dkdv_set);
+    rc = set_smem_once(attn_bwd_dkdv_kernel<D>, BwdCfg<D>::kSmemBytes, dkdv_set);
     if (rc) return rc;
-    const long long pre_threads = (long long)p.B * p.Hq * p.Tpad * (D / 8);
     record_bwd_event(0, st);
-    attn_bwd_preprocess_kernel<D><<<(unsigned)((pre_threads + 255) / 256), 256, 0, st>>>(pre);
+    // the dQ pass also writes the two per-row vectors the dK/dV pass reads
+    attn_bwd_dq_kernel<D><<<(unsigned)(p.n_tiles * p.Hq * p.B), 192, DqCfg<D>::kSmemBytes, st>>>(tq, tk64, tv64, tdo, p);
     if (cudaGetLastError() != cudaSuccess) return B200ATTN_ERR_CUDA;
     record_bwd_event(1, st);
-    attn_bwd_dkdv_kernel<D><<<dim3(p.n_tiles, p.Hkv, p.B), 320, Cfg::kSmemBytes, st>>>(tk, tv, tq, tdo, tdk, tdv, p);
+    attn_bwd_dkdv_kernel<D><<<(unsigned)(p.n_tiles * p.Hkv * p.B), 320, BwdCfg<D>::kSmemBytes, st>>>(tk, tv, tq, tdo, tdk,
+                                                                                                  tdv, p);
     if (cudaGetLastError() != cudaSuccess) return B200ATTN_ERR_CUDA;
     record_bwd_event(2, st);
-    attn_bwd_dq_kernel<D><<<dim3(p.n_tiles, p.Hq, p.B), 320, Cfg::kSmemBytes, st>>>(tq, tk, tv, tdo, tdq, p);
-    if (cudaGetLastError() != cudaSuccess) return B200ATTN_ERR_CUDA;
-    record_bwd_event(3, st);
     return B200ATTN_OK;
 }
 
 }  // namespace
 
-extern "C" int b200attn_set_bwd_profile_events(void* e0, void* e1, void* e2, void* e3) {
-    void* ev[4] = {e0, e1, e2, e3};
-    const int n_set = (e0 != nullptr) + (e1 != nullptr) + (e2 != nullptr) + (e3 != nullptr);
-    if (n_set != 0 && n_set != 4) return B200ATTN_ERR_INVALID_ARG;
-    for (int i = 0; i < 4; ++i) g_bwd_events[i] = static_cast<cudaEvent_t>(ev[i]);
+extern "C" int b200attn_set_bwd_profile_events(void* e0, void* e1, void* e2) {
+    void* ev[3] = {e0, e1, e2};
+    const int n_set = (e0 != nullptr) + (e1 != nullptr) + (e2 != nullptr);
+    if (n_set != 0 && n_set != 3) return B200ATTN_ERR_INVALID_ARG;
+    for (int i = 0; i < 3; ++i) g_bwd_events[i] = static_cast<cudaEvent_t>(ev[i]);
     return B200ATTN_OK;
 }
 
@@ -208,46 +205,43 @@ extern "C" int b200attn_bwd(const void* q, const void* k, const void* v, const v
     int* status = status_ptr(&rc);
     if (!status) return rc;
     const Strides sq = strides_for(layout, Hq, T, D), sk = strides_for(layout, Hkv, T, D);
-    CUtensorMap tq, tk, tv, tdo, tdq, tdk, tdv;
+    CUtensorMap tq, tk, tv, tk64, tv64, tdo, tdk, tdv;
     if (!make_tmap_bf16_4d(&tq, q, D, T, Hq, B, sq.t, sq.h, sq.b, 128) ||
         !make_tmap_bf16_4d(&tk, k, D, T, Hkv, B, sk.t, sk.h, sk.b, 128) ||
         !make_tmap_bf16_4d(&tv, v, D, T, Hkv, B, sk.t, sk.h, sk.b, 128) ||
+        !make_tmap_bf16_4d(&tk64, k, D, T, Hkv, B, sk.t, sk.h, sk.b, 64) ||
+        !make_tmap_bf16_4d(&tv64, v, D, T, Hkv, B, sk.t, sk.h, sk.b, 64) ||
         !make_tmap_bf16_4d(&tdo, dout, D, T, Hq, B, sq.t, sq.h, sq.b, 128) ||
-        !make_tmap_bf16_4d(&tdq, dq, D, T, Hq, B, sq.t, sq.h, sq.b, 128) ||
         !make_tmap_bf16_4d(&tdk, dk, D, T, Hkv, B, sk.t, sk.h, sk.b, 128) ||
         !make_tmap_bf16_4d(&tdv, dv, D, T, Hkv, B, sk.t, sk.h, sk.b, 128))
         return B200ATTN_ERR_TENSOR_MAP;
     float* ws = static_cast<float*>(workspace);
     const size_t nvec = bwd_vec_elems(B, T, Hq);
-    PreParams pre;
-    pre.o = static_cast<const uint16_t*>(o);
-    pre.dout = static_cast<const uint16_t*>(dout);
-    pre.lse = lse;
-    pre.lse2 = ws;
-    pre.dvec = ws + nvec;
-    pre.B = B;
-    pre.T = T;
-    pre.Tpad = (T + 127) / 128 * 128;
-    pre.Hq = Hq;
-    pre.st = sq.t;
-    pre.sh = sq.h;
-    pre.sb = sq.b;
     BwdParams p;
     p.B = B;
     p.T = T;
-    p.Tpad = pre.Tpad;
+    p.Tpad = (T + 127) / 128 * 128;
     p.Hq = Hq;
     p.Hkv = Hkv;
     p.group = Hq / Hkv;
     p.n_tiles = (T + 127) / 128;
     p.scale = softmax_scale > 0.f ? softmax_scale : 1.f / sqrtf((float)D);
     p.scale_log2 = p.scale * 1.4426950408889634f;
-    p.lse2 = pre.lse2;
-    p.dvec = pre.dvec;
+    p.lse2 = ws;
+    p.dvec = ws + nvec;
+    p.lse2_w = ws;
+    p.dvec_w = ws + nvec;
+    p.lse = lse;
+    p.o = static_cast<const uint16_t*>(o);
+    p.dout = static_cast<const uint16_t*>(dout);
+    p.dq = static_cast<uint16_t*>(dq);
+    p.q_st = sq.t;
+    p.q_sh = sq.h;
+    p.q_sb = sq.b;
     p.status = status;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return D == 64 ? launch_bwd<64>(tq, tk, tv, tdo, tdq, tdk, tdv, pre, p, st)
-                   : launch_bwd<128>(tq, tk, tv, tdo, tdq, tdk, tdv, pre, p, st);
+    return D == 64 ? launch_bwd<64>(tq, tk64, tv64, tk, tv, tdo, tdk, tdv, p, st)
+                   : launch_bwd<128>(tq, tk64, tv64, tk, tv, tdo, tdk, tdv, p, st);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -11,11 +11,12 @@
 // the query heads of its group and keeps one accumulator, which replaces
 // accumulate_kv_grads (llm/src/model/attention.cu:412-429,510-543).
 //
-// Roles in the dK/dV pass (320 threads; the dQ pass is described at its kernel):
-//   warps 0-7  compute: thread owns TMEM lane (warp % 4) * 32 + lane and the 64 score
-//              columns of its half (warp / 4)
-//   warp  8    TMA producer (converged warp, one elected lane issues)
-//   warp  9    TMEM allocation and tcgen05.mma issue (converged warp, one elected lane issues)
+// Roles in the dK/dV pass (576 threads; the dQ pass is described at its kernel):
+//   warps 0-15  compute: thread owns TMEM lane (warp % 4) * 32 + lane and the 32 score
+//               columns of its part (warp / 4); four warps per scheduler hide the TMEM and
+//               MUFU latencies of one another
+//   warp  16    TMA producer (converged warp, one elected lane issues)
+//   warp  17    TMEM allocation and tcgen05.mma issue (converged warp, one elected lane issues)
 // TMEM (512 columns), D = 64:  S buffer 0 [0,128), S buffer 1 [128,256), dP [256,384),
 //   accumulators [384,448) and [448,512).  With two S buffers the next tile's QK^T product
 //   is issued while the compute warps still work on the current tile.
@@ -24,8 +25,8 @@
 //   A: P = exp2(S * scale*log2e - L*log2e)   (kept in registers; the dK/dV pass also stores it)
 //   B: dS = P * (dP - D)                      (stored over dP as BF16)
 // The BF16 operands of the second-stage MMAs overwrite the FP32 values they were computed
-// from: half h of a 128-wide block keeps its 64 BF16 values in the first 32 columns of its
-// own 64-column range.
+// from: part q of a 128-wide block keeps its 32 BF16 values in the first 16 columns of its
+// own 32-column range.
 #pragma once
 
 #include "ptx.cuh"
@@ -56,6 +57,10 @@ struct BwdCfg {
     static constexpr int kBoxes = D / 64;
     static constexpr int kVecBytes = kStages * 2 * 512;  // per stage (lse2, dvec) of 128 rows
     static constexpr int kBarBytes = 256;
+    static constexpr int kParts = 4;                       // compute warpgroups: each owns 128 / kParts score columns
+    static constexpr int kPartCols = 128 / kParts;         // 32
+    static constexpr int kComputeThreads = 128 * kParts;   // 512
+    static constexpr int kThreads = kComputeThreads + 64;  // + producer warp + MMA warp
     static constexpr int kSmemBytes = (2 + 2 * kStages) * kTileBytes + kVecBytes + kBarBytes + 1024;
     static constexpr int kTmemCols = 512;
     static constexpr int kColS0 = 0;
@@ -78,13 +83,15 @@ __device__ __forceinline__ void issue_ss_over_headdim(uint32_t d_tmem, uint64_t 
 }
 
 // D[tmem] (+)= A[tmem, BF16 pairs] * B[smem, MN-major] over 128 rows of B (b_desc describes
-// rows 0..15).  The A operand lives in two 32-column pieces, `a_col` and `a_col + 64`.
+// rows 0..15).  The A operand lives in kParts pieces: part q keeps its kPartCols BF16 values in
+// the first kPartCols / 2 columns of its own FP32 column range, which starts at a_col + q * kPartCols.
 template <int D>
 __device__ __forceinline__ void issue_ts_over_rows(uint32_t d_tmem, uint32_t a_col, uint64_t b_desc, uint32_t idesc,
                                                    bool accumulate) {
+    constexpr int kStepsPerPart = BwdCfg<D>::kPartCols / 16;  // K steps (16 rows of B) per part
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
-        const uint32_t a = a_col + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8);
+        const uint32_t a = a_col + (ks / kStepsPerPart) * BwdCfg<D>::kPartCols + (ks % kStepsPerPart) * 8;
         umma_ts(d_tmem, a, b_desc + uint64_t(ks * 128), idesc, accumulate || ks > 0);
     }
 }
@@ -124,8 +131,8 @@ __device__ __forceinline__ void stage_row_chunk(uint8_t* tile, int row, int col,
 //
 // Roles (192 threads): warps 0-3 compute (thread r owns query row r == TMEM lane r),
 // warp 4 TMA producer, warp 5 TMEM allocation + MMA issue (converged warps, elected lane).
-// TMEM: S buffer 0 [0,64), S buffer 1 [64,128), dP [128,192) (dS as BF16 over its first 32
-// columns), dQ accumulator [192,192+D).  D = 64 needs 256 columns, so two CTAs share an SM.
+// TMEM: S buffer 0 [0,64), S buffer 1 [64,128) (dS as BF16 over the first 32 columns of the
+// tile's S buffer), dP [128,192), dQ accumulator [192,192+D).  D = 64 needs 256 columns, so two CTAs share an SM.
 // ---------------------------------------------------------------------------------------
 template <int D>
 struct DqCfg {
@@ -176,10 +183,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int k_end = min(p.T, q0 + 128);
     const int n_kv = (k_end + Cfg::kKeys - 1) / Cfg::kKeys;
 
+    B200ATTN_TRACE_BEGIN();
+    B200ATTN_STAMP(tid == 0, 300);
     // Set-up with one CTA-wide barrier (see the forward kernel).
+    grid_dep_launch();
     if (warp == 4 && lane == 0) {
-        const int failed = *reinterpret_cast<volatile int*>(p.status);
-        *abort_flag = failed;
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        tma_prefetch_desc(&tmdO);
         mbar_init(bar_q, 1);
         mbar_init(&bar_s_full[0], 1);
         mbar_init(&bar_s_full[1], 1);
@@ -191,6 +203,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             mbar_init(&bar_kv_free[s], 1);
         }
         fence_mbar_init();
+        grid_dep_wait();  // first global access of this CTA comes next
+        const int failed = *reinterpret_cast<volatile int*>(p.status);
+        *abort_flag = failed;
         if (!failed) {
             mbar_arrive_expect_tx(bar_q, 2 * Cfg::kQTileBytes);
 #pragma unroll
@@ -215,11 +230,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tmem_alloc(tmem_slot, Cfg::kTmemCols);
         tmem_relinquish();
     }
+    grid_dep_wait();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
     const bool failed_early = (*abort_flag != 0);
+    B200ATTN_STAMP(tid == 0, 301);
 
     if (failed_early) {
         // nothing was started; fall through to the teardown
@@ -284,17 +301,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             ok = mbar_wait_warp(bar_ds_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
             if (!ok) break;
             tc_fence_after_sync();
+            // dP of the next tile first: dS_j lives in S buffer j & 1, the dP block is free again
+            if (j + 1 < n_kv) issue_dp(j + 1);
             const uint64_t kmn_desc = make_sdesc_sw128(smem_u32(sK + s * Cfg::kKVTileBytes), Cfg::kKVBoxBytes, 1024);
             if (elect_one()) {
-                // dQ += dS_j K_j : 64 keys = 4 K steps, dS in the first 32 columns of the dP block
+                // dQ += dS_j K_j : 64 keys = 4 K steps, dS in the first 32 columns of S buffer j & 1
 #pragma unroll
                 for (int ks = 0; ks < Cfg::kKeys / 16; ++ks)
-                    umma_ts(tmem + Cfg::kColAcc, tmem + Cfg::kColDP + ks * 8, kmn_desc + uint64_t(ks * 128), idesc_acc,
-                            (j > 0) || (ks > 0));
+                    umma_ts(tmem + Cfg::kColAcc, tmem + ((j & 1) ? Cfg::kColS1 : Cfg::kColS0) + ks * 8,
+                            kmn_desc + uint64_t(ks * 128), idesc_acc, (j > 0) || (ks > 0));
                 umma_commit(&bar_kv_free[s]);
             }
             __syncwarp();
-            if (j + 1 < n_kv) issue_dp(j + 1);
             if (j + 2 < n_kv) ok = issue_s(j + 2);
         }
         if (elect_one()) umma_commit(bar_acc);
@@ -306,32 +324,47 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const bool in_range = q0 + row < p.T;
         const size_t vrow = (size_t(b) * p.Hq + h) * p.Tpad + q0 + row;
         const size_t qoff = size_t(b) * p.q_sb + size_t(h) * p.q_sh + size_t(q0 + row) * p.q_st;
-        // preprocess for this row, under the latency of the first loads
+        // Preprocess for the warp's 32 rows, under the latency of the first loads: D = rowsum(O * dO).
+        // The warp reads whole rows with coalesced 16-byte loads (D/8 lanes per row), reduces with
+        // shuffles and hands every row's sum to the lane that owns the row.
         float lse2 = INFINITY;  // exp2(x - inf) = 0: padding query rows contribute nothing
         float dv = 0.f;
-        if (in_range) {
-            const uint4* orow = reinterpret_cast<const uint4*>(p.o + qoff);
-            const uint4* grow = reinterpret_cast<const uint4*>(p.dout + qoff);
+        {
+            constexpr int LPR = D / 8;     // lanes per row
+            constexpr int RPP = 32 / LPR;  // rows per pass
+            const size_t tile_off = size_t(b) * p.q_sb + size_t(h) * p.q_sh;
 #pragma unroll
-            for (int c = 0; c < D / 8; ++c) {
-                const uint4 a = orow[c], g = grow[c];
-                const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
-                const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+            for (int i = 0; i < LPR; ++i) {
+                const int r = q0 + warp * 32 + i * RPP + lane / LPR;  // global query row read by this lane
+                float acc = 0.f;
+                if (r < p.T) {
+                    const size_t off = tile_off + size_t(r) * p.q_st + (lane % LPR) * 8;
+                    const uint4 a = *reinterpret_cast<const uint4*>(p.o + off);
+                    const uint4 g = *reinterpret_cast<const uint4*>(p.dout + off);
+                    const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+                    const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    dv = fmaf(__uint_as_float(aw[i] << 16), __uint_as_float(gw[i] << 16), dv);
-                    dv = fmaf(__uint_as_float(aw[i] & 0xffff0000u), __uint_as_float(gw[i] & 0xffff0000u), dv);
+                    for (int e = 0; e < 4; ++e) {
+                        acc = fmaf(__uint_as_float(aw[e] << 16), __uint_as_float(gw[e] << 16), acc);
+                        acc = fmaf(__uint_as_float(aw[e] & 0xffff0000u), __uint_as_float(gw[e] & 0xffff0000u), acc);
+                    }
                 }
+#pragma unroll
+                for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                const float v = __shfl_sync(0xffffffffu, acc, (lane % RPP) * LPR);
+                if (lane / RPP == i) dv = v;
             }
-            lse2 = p.lse[(size_t(b) * p.Hq + h) * p.T + q0 + row] * 1.4426950408889634f;
+            if (in_range) lse2 = p.lse[(size_t(b) * p.Hq + h) * p.T + q0 + row] * 1.4426950408889634f;
         }
         p.lse2_w[vrow] = lse2;
         p.dvec_w[vrow] = dv;
+        B200ATTN_STAMP(tid == 0, 302);
         bool ok = true;
         for (int j = 0; j < n_kv; ++j) {
             const uint32_t t_s = tmem + lane_base + ((j & 1) ? Cfg::kColS1 : Cfg::kColS0);
             ok = mbar_wait_warp(&bar_s_full[j & 1], uint32_t(j >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
             if (!ok) break;
+            B200ATTN_STAMP(tid == 0, 308 + 4 * j);
             tc_fence_after_sync();
             // phase A: P from S
             float pr[64];
@@ -352,8 +385,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             }
             ok = mbar_wait_warp(bar_dp_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
             if (!ok) break;
+            B200ATTN_STAMP(tid == 0, 309 + 4 * j);
             tc_fence_after_sync();
-            // phase B: dS = P (dP - D), written over dP as BF16
+            // phase B: dS = P (dP - D), written as BF16 over the S buffer of this tile
             {
                 uint32_t dp[64], pk[32];
                 tmem_ld_x32(tmem + lane_base + Cfg::kColDP, &dp[0]);
@@ -363,14 +397,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 for (int i = 0; i < 32; ++i)
                     pk[i] = pack_bf16x2(pr[2 * i] * (__uint_as_float(dp[2 * i]) - dv),
                                         pr[2 * i + 1] * (__uint_as_float(dp[2 * i + 1]) - dv));
-                tmem_st_x32(tmem + lane_base + Cfg::kColDP, pk);
+                tmem_st_x32(t_s, pk);
             }
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(bar_ds_full);
+            B200ATTN_STAMP(tid == 0, 310 + 4 * j);
         }
         if (ok) ok = mbar_wait(bar_acc, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
         ok = __all_sync(0xffffffffu, ok);
+        B200ATTN_STAMP(tid == 0, 303);
         if (ok) {
             tc_fence_after_sync();
             uint16_t* dqrow = p.dq + qoff;
@@ -398,6 +434,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tc_fence_after_sync();
         tmem_dealloc(tmem, Cfg::kTmemCols);
     }
+    B200ATTN_STAMP(tid == 0, 304);
+    B200ATTN_TRACE_END();
 }
 
 // ---------------------------------------------------------------------------------------
@@ -405,7 +443,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 // group and, for each, over the query tiles at or below the diagonal.
 // ---------------------------------------------------------------------------------------
 template <int D>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(BwdCfg<D>::kThreads, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                      const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                      const __grid_constant__ CUtensorMap tmdK, const __grid_constant__ CUtensorMap tmdV,
@@ -433,6 +471,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    constexpr int kProducerWarp = Cfg::kParts * 4, kMmaWarp = Cfg::kParts * 4 + 1;
     // 1-D grid ordered by work: key tile 0 has the most query tiles below it, so all its CTAs come first
     const int n_bh = p.B * p.Hkv;
     const int kt = int(blockIdx.x) / n_bh;
@@ -441,17 +480,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     const int n_i = p.n_tiles - kt;  // query tiles kt .. n_tiles-1
     const int n_it = p.group * n_i;  // times the query heads of the group
 
-    if (tid == 0) *abort_flag = *reinterpret_cast<volatile int*>(p.status);
-    __syncthreads();
-    if (*abort_flag != 0) return;
-    __syncthreads();
-
+    grid_dep_launch();
     if (tid == 0) {
         mbar_init(bar_kv, 1);
         mbar_init(&bar_s_full[0], 1);
         mbar_init(&bar_s_full[1], 1);
         mbar_init(bar_dp_full, 1);
-        mbar_init(bar_pds_full, 256);
+        mbar_init(bar_pds_full, Cfg::kComputeThreads);
         mbar_init(bar_acc, 1);
         for (int s = 0; s < NST; ++s) {
             mbar_init(&bar_full[s], 1);
@@ -459,11 +494,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         }
         fence_mbar_init();
     }
-    if (warp == 9) {
+    if (warp == kMmaWarp) {
         tmem_alloc(tmem_slot, Cfg::kTmemCols);
         tmem_relinquish();
     }
-    if (warp == 8 && lane == 0) {
+    if (warp == kProducerWarp && lane == 0) {
         tma_prefetch_desc(&tmK);
         tma_prefetch_desc(&tmV);
         tma_prefetch_desc(&tmQ);
@@ -475,8 +510,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    // Everything above touched no global memory.  From here on the previous kernel of the stream
+    // (the dQ pass, which writes the two per-row vectors) must have completed.
+    grid_dep_wait();
+    if (tid == 0) *abort_flag = *reinterpret_cast<volatile int*>(p.status);
+    __syncthreads();
 
-    if (warp == 8) {
+    if (*abort_flag != 0) {
+        // an earlier CTA already failed: fall through to the teardown
+    } else if (warp == kProducerWarp) {
         // ------------------------------------------------------------------ producer (whole warp, one lane issues)
         if (elect_one()) {
             mbar_arrive_expect_tx(bar_kv, 2 * Cfg::kTileBytes);
@@ -509,7 +551,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             }
             __syncwarp();
         }
-    } else if (warp == 9) {
+    } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------------ MMA issuer (whole warp, one lane issues)
         constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
         constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
@@ -545,22 +587,30 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             if (!ok) break;
             B200ATTN_STAMP(lane == 0, 200 + 4 * it);
             tc_fence_after_sync();
+            // dP^T of the next iteration first: nothing of this iteration lives in the dP block any more
+            // (dS^T was written next to P^T inside the S buffer), so the compute warps get it early.
+            if (it + 1 < n_it) {
+                if (!DBL && !mbar_wait_warp(&bar_full[(it + 1) % NST], ((it + 1) / NST) & 1, abort_flag, p.status,
+                                            DEV_WAIT_TIMEOUT_LOAD)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                issue_dp(it + 1);
+            }
             if (elect_one()) {
-                // dV += P^T dO ; dK += dS^T Q
+                // dV += P^T dO ; dK += dS^T Q   (P^T and dS^T sit side by side in S buffer `buf`)
                 issue_ts_over_rows<D>(tmem + Cfg::kColAcc0, tmem + Cfg::col_s(buf),
                                       mnmajor_desc<D>(sdO + s * Cfg::kTileBytes), idesc_acc, it > 0);
-                issue_ts_over_rows<D>(tmem + Cfg::kColAcc1, tmem + Cfg::kColDP, mnmajor_desc<D>(sQ + s * Cfg::kTileBytes),
-                                      idesc_acc, it > 0);
+                issue_ts_over_rows<D>(tmem + Cfg::kColAcc1, tmem + Cfg::col_s(buf) + Cfg::kPartCols / 2,
+                                      mnmajor_desc<D>(sQ + s * Cfg::kTileBytes), idesc_acc, it > 0);
                 umma_commit(&bar_free[s]);
             }
             __syncwarp();
             B200ATTN_STAMP(lane == 0, 201 + 4 * it);
-            if (it + 1 < n_it) {
-                if (!DBL) {
-                    ok = issue_s(it + 1);
-                    if (!ok) break;
-                }
-                issue_dp(it + 1);
+            if (!DBL && it + 1 < n_it) {
+                ok = issue_s(it + 1);
+                if (!ok) break;
             }
             if (DBL && it + 2 < n_it) {
                 ok = issue_s(it + 2);
@@ -572,10 +622,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         __syncwarp();
     } else {
         // ------------------------------------------------------------------ compute
-        const int w4 = warp & 3, half = warp >> 2;
+        const int w4 = warp & 3, part = warp >> 2;
         const int row = w4 * 32 + lane;  // key row in the tile == TMEM lane
         const uint32_t lane_base = uint32_t(w4 * 32) << 16;
-        const int c0 = half * 64;  // first query column of this thread's half
+        const int c0 = part * Cfg::kPartCols;  // first query column of this thread's part
         bool ok = true;
         for (int it = 0; it < n_it; ++it) {
             const int s = it % NST;
@@ -589,49 +639,46 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             const float4* lse4 = reinterpret_cast<const float4*>(sLse + s * 128 + c0);
             const float4* dv4 = reinterpret_cast<const float4*>(sDv + s * 128 + c0);
             // phase A: P^T from S^T (kept in registers and stored over S^T as BF16)
-            float pr[64];
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            float pr[32];
+            {
                 uint32_t sv[32], pk[16];
-                tmem_ld_x32(tmem + lane_base + Cfg::col_s(buf) + c0 + c * 32, sv);
+                tmem_ld_x32(tmem + lane_base + Cfg::col_s(buf) + c0, sv);
                 tmem_wait_ld();
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
-                    const float4 l4 = lse4[c * 8 + g];
-                    pr[c * 32 + g * 4 + 0] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 0]), p.scale_log2, -l4.x));
-                    pr[c * 32 + g * 4 + 1] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 1]), p.scale_log2, -l4.y));
-                    pr[c * 32 + g * 4 + 2] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 2]), p.scale_log2, -l4.z));
-                    pr[c * 32 + g * 4 + 3] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 3]), p.scale_log2, -l4.w));
+                    const float4 l4 = lse4[g];
+                    pr[g * 4 + 0] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 0]), p.scale_log2, -l4.x));
+                    pr[g * 4 + 1] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 1]), p.scale_log2, -l4.y));
+                    pr[g * 4 + 2] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 2]), p.scale_log2, -l4.z));
+                    pr[g * 4 + 3] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 3]), p.scale_log2, -l4.w));
                 }
                 if (diag) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        if (c0 + c * 32 + i < row) pr[c * 32 + i] = 0.f;  // query above the key: masked
+                        if (c0 + i < row) pr[i] = 0.f;  // query above the key: masked
                 }
 #pragma unroll
-                for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(pr[c * 32 + 2 * i], pr[c * 32 + 2 * i + 1]);
-                tmem_st_x16(tmem + lane_base + Cfg::col_s(buf) + c0 + c * 16, pk);
+                for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(pr[2 * i], pr[2 * i + 1]);
+                tmem_st_x16(tmem + lane_base + Cfg::col_s(buf) + c0, pk);
             }
             ok = mbar_wait_warp(bar_dp_full, it & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
             if (!ok) break;
             B200ATTN_STAMP(tid == 0, 10 + 4 * it);
             tc_fence_after_sync();
-            // phase B: dS^T = P^T (dP^T - D), stored over dP^T as BF16
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            // phase B: dS^T = P^T (dP^T - D), stored as BF16 next to P^T in the S buffer
+            {
                 uint32_t dp[32], pk[16];
-                tmem_ld_x32(tmem + lane_base + Cfg::kColDP + c0 + c * 32, dp);
+                tmem_ld_x32(tmem + lane_base + Cfg::kColDP + c0, dp);
                 tmem_wait_ld();
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
-                    const float4 d4 = dv4[c * 8 + g];
-                    const int i = c * 32 + g * 4;
-                    pk[g * 2 + 0] = pack_bf16x2(pr[i + 0] * (__uint_as_float(dp[g * 4 + 0]) - d4.x),
-                                                pr[i + 1] * (__uint_as_float(dp[g * 4 + 1]) - d4.y));
-                    pk[g * 2 + 1] = pack_bf16x2(pr[i + 2] * (__uint_as_float(dp[g * 4 + 2]) - d4.z),
-                                                pr[i + 3] * (__uint_as_float(dp[g * 4 + 3]) - d4.w));
+                    const float4 d4 = dv4[g];
+                    pk[g * 2 + 0] = pack_bf16x2(pr[g * 4 + 0] * (__uint_as_float(dp[g * 4 + 0]) - d4.x),
+                                                pr[g * 4 + 1] * (__uint_as_float(dp[g * 4 + 1]) - d4.y));
+                    pk[g * 2 + 1] = pack_bf16x2(pr[g * 4 + 2] * (__uint_as_float(dp[g * 4 + 2]) - d4.z),
+                                                pr[g * 4 + 3] * (__uint_as_float(dp[g * 4 + 3]) - d4.w));
                 }
-                tmem_st_x16(tmem + lane_base + Cfg::kColDP + c0 + c * 16, pk);
+                tmem_st_x16(tmem + lane_base + Cfg::col_s(buf) + c0 + Cfg::kPartCols / 2, pk);
             }
             tmem_wait_st();
             tc_fence_before_sync();
@@ -642,21 +689,26 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             tc_fence_after_sync();
-            // half 0 drains dV into the first Q stage, half 1 drains dK (times scale) into the first dO stage
-            uint8_t* tile = half == 0 ? sQ : sdO;
-            const uint32_t acc = half == 0 ? Cfg::kColAcc0 : Cfg::kColAcc1;
-            const float mul = half == 0 ? 1.f : p.scale;
+            // parts 0,1 drain dV into the first Q stage, parts 2,3 drain dK (times scale) into the first dO
+            // stage; each part takes D / 2 of the accumulator's columns
+            constexpr int kHalfParts = Cfg::kParts / 2;
+            constexpr int kColsPerPart = D / kHalfParts;
+            const bool is_dk = part >= kHalfParts;
+            uint8_t* tile = is_dk ? sdO : sQ;
+            const uint32_t acc = is_dk ? Cfg::kColAcc1 : Cfg::kColAcc0;
+            const float mul = is_dk ? p.scale : 1.f;
+            const int col0 = (part % kHalfParts) * kColsPerPart;
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
+            for (int c = 0; c < kColsPerPart / 32; ++c) {
                 uint32_t v[32];
-                tmem_ld_x32(tmem + lane_base + acc + c * 32, v);
+                tmem_ld_x32(tmem + lane_base + acc + col0 + c * 32, v);
                 tmem_wait_ld();
-                stage_row_chunk<D>(tile, row, c * 32, v, mul);
+                stage_row_chunk<D>(tile, row, col0 + c * 32, v, mul);
             }
             fence_proxy_async_smem();
         }
         tc_fence_before_sync();
-        named_bar_sync(1, 256);
+        named_bar_sync(1, Cfg::kComputeThreads);
         if (ok && tid == 0) {
 #pragma unroll
             for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
@@ -670,7 +722,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
 
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == kMmaWarp) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, Cfg::kTmemCols);
     }

@@ -101,9 +101,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // Set-up with one CTA-wide barrier: one lane of the producer warp reads the device status word
     // (an earlier CTA may already have failed), initialises every mbarrier and immediately starts
     // the first loads, while the MMA warp allocates TMEM.
+    grid_dep_launch();
     if (warp == 4 && lane == 0) {
-        const int failed = *reinterpret_cast<volatile int*>(p.status);
-        *abort_flag = failed;
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
         mbar_init(bar_q, 1);
         mbar_init(&bar_s_full[0], 1);
         mbar_init(&bar_s_full[1], 1);
@@ -118,6 +120,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             mbar_init(&bar_v_free[s], 1);
         }
         fence_mbar_init();
+        grid_dep_wait();  // first global access of this CTA comes next
+        const int failed = *reinterpret_cast<volatile int*>(p.status);
+        *abort_flag = failed;
         if (!failed) {
             mbar_arrive_expect_tx(bar_q, Cfg::kQTileBytes);
 #pragma unroll
@@ -142,6 +147,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_alloc(tmem_slot, Cfg::kTmemCols);
         tmem_relinquish();
     }
+    grid_dep_wait();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();

@@ -73,6 +73,24 @@ int check_common(int B, int T, int Hq, int Hkv, int D, int layout) {
     return B200ATTN_OK;
 }
 
+// Launch with programmatic stream serialization: the kernel may become resident while the
+// previous kernel of the stream drains; it calls griddepcontrol.wait before touching global memory.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t st,
+                       Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(block, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <int D>
 int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FwdParams& p,
                cudaStream_t st) {
@@ -89,8 +107,11 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
         attr_set[dev] = true;
     }
     const unsigned grid = (unsigned)p.n_qtiles * (unsigned)p.Hq * (unsigned)p.B;
-    attn_fwd_kernel<D><<<grid, 256, Cfg::kSmemBytes, st>>>(tq, tk, tv, p);
-    return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
+    if (launch_pdl(attn_fwd_kernel<D>, grid, 256, Cfg::kSmemBytes, st, tq, tk, tv, p) != cudaSuccess) {
+        cudaGetLastError();
+        return B200ATTN_ERR_CUDA;
+    }
+    return B200ATTN_OK;
 }
 
 }  // namespace
@@ -163,12 +184,17 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk64, const CUtensorMap
     if (rc) return rc;
     record_bwd_event(0, st);
     // the dQ pass also writes the two per-row vectors the dK/dV pass reads
-    attn_bwd_dq_kernel<D><<<(unsigned)(p.n_tiles * p.Hq * p.B), 192, DqCfg<D>::kSmemBytes, st>>>(tq, tk64, tv64, tdo, p);
-    if (cudaGetLastError() != cudaSuccess) return B200ATTN_ERR_CUDA;
+    if (launch_pdl(attn_bwd_dq_kernel<D>, (unsigned)(p.n_tiles * p.Hq * p.B), 192, DqCfg<D>::kSmemBytes, st, tq, tk64, tv64,
+                   tdo, p) != cudaSuccess) {
+        cudaGetLastError();
+        return B200ATTN_ERR_CUDA;
+    }
     record_bwd_event(1, st);
-    attn_bwd_dkdv_kernel<D><<<(unsigned)(p.n_tiles * p.Hkv * p.B), 320, BwdCfg<D>::kSmemBytes, st>>>(tk, tv, tq, tdo, tdk,
-                                                                                                  tdv, p);
-    if (cudaGetLastError() != cudaSuccess) return B200ATTN_ERR_CUDA;
+    if (launch_pdl(attn_bwd_dkdv_kernel<D>, (unsigned)(p.n_tiles * p.Hkv * p.B), BwdCfg<D>::kThreads,
+                   BwdCfg<D>::kSmemBytes, st, tk, tv, tq, tdo, tdk, tdv, p) != cudaSuccess) {
+        cudaGetLastError();
+        return B200ATTN_ERR_CUDA;
+    }
     record_bwd_event(2, st);
     return B200ATTN_OK;
 }

@@ -184,6 +184,15 @@ __device__ __forceinline__ uint64_t make_sdesc_sw128(uint32_t smem_addr, uint32_
     return d;
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization
+// attribute may become resident while the previous kernel of the stream is still draining.
+// grid_dep_launch() lets the NEXT kernel start its own set-up early; grid_dep_wait() blocks
+// until the PREVIOUS kernel has completed and its writes are visible.  Every kernel here does
+// its set-up (barriers, TMEM, tensor-map prefetch) first and calls grid_dep_wait() before its
+// first access to global memory, so only set-up and launch latency overlap.
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Elects one lane of a fully converged warp.  The MMA and TMA issuing warps run their loops
 // with all 32 lanes (so that addresses and descriptors stay in the uniform datapath) and
 // guard only the issuing instructions with this.

@@ -439,6 +439,312 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 }
 
 // ---------------------------------------------------------------------------------------
+// dQ pass, wide variant used for D = 128: 128-key tiles, eight compute warps (thread owns a row
+// and 64 of the 128 score columns), one CTA per SM.  With D = 128 the pass is bound by the
+// tensor pipe, and 128-wide S = Q K^T products keep the shared-memory operand traffic of the
+// SS MMAs at the 128 B/clk the SM can deliver (a 64-wide product needs 192 B/clk).
+// ---------------------------------------------------------------------------------------
+template <int D>
+struct DqWideCfg {
+    static constexpr bool kDoubleS = (D == 64);
+    static constexpr int kStages = kDoubleS ? 3 : 2;
+    static constexpr int kTileBytes = 128 * D * 2;
+    static constexpr int kBoxBytes = 128 * 64 * 2;
+    static constexpr int kBoxes = D / 64;
+    static constexpr int kVecBytes = 0;
+    static constexpr int kSmemBytes = (2 + 2 * kStages) * kTileBytes + 256 + 1024;
+    static constexpr int kTmemCols = 512;
+    static constexpr int kColS0 = 0;
+    static constexpr int kColS1 = kDoubleS ? 128 : 0;
+    static constexpr int kColDP = kDoubleS ? 256 : 128;
+    static constexpr int kColAcc0 = kDoubleS ? 384 : 256;
+    __host__ __device__ static constexpr int col_s(int buf) { return buf ? kColS1 : kColS0; }
+};
+
+template <int D>
+__device__ __forceinline__ void wide_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks)
+        umma_ss(d_tmem, a_desc + kmajor_step(ks, 16384), b_desc + kmajor_step(ks, 16384), idesc, ks > 0);
+}
+// A in two 32-column pieces at a_col and a_col + 64 (one per column half)
+template <int D>
+__device__ __forceinline__ void wide_ts(uint32_t d_tmem, uint32_t a_col, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks)
+        umma_ts(d_tmem, a_col + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8), b_desc + uint64_t(ks * 128), idesc,
+                accumulate || ks > 0);
+}
+template <int D>
+__global__ void __launch_bounds__(320, 1)
+attn_bwd_dq_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                   const __grid_constant__ CUtensorMap tmdQ, const BwdParams p) {
+    using Cfg = DqWideCfg<D>;
+    constexpr int NST = Cfg::kStages;
+    constexpr bool DBL = Cfg::kDoubleS;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sQ = smem;
+    uint8_t* sdO = sQ + Cfg::kTileBytes;
+    uint8_t* sK = sdO + Cfg::kTileBytes;        // [NST]
+    uint8_t* sV = sK + NST * Cfg::kTileBytes;   // [NST]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + NST * Cfg::kTileBytes + Cfg::kVecBytes);
+    uint64_t* bar_q = bars + 0;
+    uint64_t* bar_s_full = bars + 1;   // [2] one per S buffer
+    uint64_t* bar_dp_full = bars + 3;
+    uint64_t* bar_ds_full = bars + 4;
+    uint64_t* bar_acc = bars + 5;
+    uint64_t* bar_kv_full = bars + 6;          // [NST]
+    uint64_t* bar_kv_free = bars + 6 + NST;    // [NST]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_bh = p.B * p.Hq;
+    const int qt = p.n_tiles - 1 - int(blockIdx.x) / n_bh;
+    const int h = (int(blockIdx.x) % n_bh) % p.Hq, b = (int(blockIdx.x) % n_bh) / p.Hq;
+    const int hk = h / p.group;
+    const int q0 = qt * 128;
+    const int n_kv = qt + 1;
+
+    // launched with programmatic stream serialization: wait for the previous kernel before any global access
+    grid_dep_launch();
+    grid_dep_wait();
+    if (tid == 0) *abort_flag = *reinterpret_cast<volatile int*>(p.status);
+    __syncthreads();
+    if (*abort_flag != 0) return;
+    __syncthreads();
+
+    if (tid == 0) {
+        mbar_init(bar_q, 1);
+        mbar_init(&bar_s_full[0], 1);
+        mbar_init(&bar_s_full[1], 1);
+        mbar_init(bar_dp_full, 1);
+        mbar_init(bar_ds_full, 256);
+        mbar_init(bar_acc, 1);
+        for (int s = 0; s < NST; ++s) {
+            mbar_init(&bar_kv_full[s], 1);
+            mbar_init(&bar_kv_free[s], 1);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 9) {
+        tmem_alloc(tmem_slot, Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    if (warp == 8 && lane == 0) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        tma_prefetch_desc(&tmdO);
+        tma_prefetch_desc(&tmdQ);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 8) {
+        // ------------------------------------------------------------------ producer (whole warp, one lane issues)
+        if (elect_one()) {
+            mbar_arrive_expect_tx(bar_q, 2 * Cfg::kTileBytes);
+#pragma unroll
+            for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
+                tma_load_4d(sQ + bx * Cfg::kBoxBytes, &tmQ, bar_q, bx * 64, q0, h, b);
+                tma_load_4d(sdO + bx * Cfg::kBoxBytes, &tmdO, bar_q, bx * 64, q0, h, b);
+            }
+        }
+        __syncwarp();
+        for (int j = 0; j < n_kv; ++j) {
+            const int s = j % NST;
+            if (j >= NST &&
+                !mbar_wait_warp(&bar_kv_free[s], ((j / NST) - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE))
+                break;
+            if (elect_one()) {
+                mbar_arrive_expect_tx(&bar_kv_full[s], 2 * Cfg::kTileBytes);
+#pragma unroll
+                for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
+                    tma_load_4d(sK + s * Cfg::kTileBytes + bx * Cfg::kBoxBytes, &tmK, &bar_kv_full[s], bx * 64, j * 128,
+                                hk, b);
+                    tma_load_4d(sV + s * Cfg::kTileBytes + bx * Cfg::kBoxBytes, &tmV, &bar_kv_full[s], bx * 64, j * 128,
+                                hk, b);
+                }
+            }
+            __syncwarp();
+        }
+    } else if (warp == 9) {
+        // ------------------------------------------------------------------ MMA issuer (whole warp, one lane issues)
+        constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+        constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
+        const uint64_t q_desc = kmajor_desc<D>(sQ), do_desc = kmajor_desc<D>(sdO);
+        bool ok = mbar_wait_warp(bar_q, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+        // S(j) = Q K_j^T into S buffer (j & 1 when double-buffered); waits for the tile's loads first
+        auto issue_s = [&](int j) -> bool {
+            const int s = j % NST;
+            if (!mbar_wait_warp(&bar_kv_full[s], (j / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD))
+                return false;
+            tc_fence_after_sync();
+            const int buf = DBL ? (j & 1) : 0;
+            if (elect_one()) {
+                wide_ss<D>(tmem + Cfg::col_s(buf), q_desc, kmajor_desc<D>(sK + s * Cfg::kTileBytes), idesc_s);
+                umma_commit(&bar_s_full[buf]);
+            }
+            __syncwarp();
+            return true;
+        };
+        auto issue_dp = [&](int j) {  // dP(j) = dO V_j^T; the loads of tile j are known to be complete
+            const int s = j % NST;
+            if (elect_one()) {
+                wide_ss<D>(tmem + Cfg::kColDP, do_desc, kmajor_desc<D>(sV + s * Cfg::kTileBytes), idesc_s);
+                umma_commit(bar_dp_full);
+            }
+            __syncwarp();
+        };
+        if (ok) ok = issue_s(0);
+        if (ok) issue_dp(0);
+        if (ok && DBL && n_kv > 1) ok = issue_s(1);
+        for (int j = 0; j < n_kv && ok; ++j) {
+            const int s = j % NST;
+            ok = mbar_wait_warp(bar_ds_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+            if (!ok) break;
+            tc_fence_after_sync();
+            if (elect_one()) {
+                // dQ += dS K_j
+                wide_ts<D>(tmem + Cfg::kColAcc0, tmem + Cfg::kColDP, mnmajor_desc<D>(sK + s * Cfg::kTileBytes),
+                                      idesc_acc, j > 0);
+                umma_commit(&bar_kv_free[s]);
+            }
+            __syncwarp();
+            if (j + 1 < n_kv) {
+                if (!DBL) {
+                    ok = issue_s(j + 1);
+                    if (!ok) break;
+                }
+                issue_dp(j + 1);  // S(j+1) was issued earlier, so its loads have landed
+            }
+            if (DBL && j + 2 < n_kv) {
+                ok = issue_s(j + 2);
+                if (!ok) break;
+            }
+        }
+        if (elect_one()) umma_commit(bar_acc);
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ compute
+        const int w4 = warp & 3, half = warp >> 2;
+        const int row = w4 * 32 + lane;  // query row in the tile == TMEM lane
+        const uint32_t lane_base = uint32_t(w4 * 32) << 16;
+        const int c0 = half * 64;  // first key column of this thread's half
+        const size_t vrow = (size_t(b) * p.Hq + h) * p.Tpad + q0 + row;
+        // preprocess for the warp's 32 rows (both halves compute it, half 0 stores it for the dK/dV pass)
+        float lse2 = INFINITY, dv = 0.f;
+        {
+            constexpr int LPR = D / 8, RPP = 32 / LPR;
+            const size_t tile_off = size_t(b) * p.q_sb + size_t(h) * p.q_sh;
+#pragma unroll
+            for (int i = 0; i < LPR; ++i) {
+                const int r = q0 + w4 * 32 + i * RPP + lane / LPR;
+                float acc = 0.f;
+                if (r < p.T) {
+                    const size_t off = tile_off + size_t(r) * p.q_st + (lane % LPR) * 8;
+                    const uint4 a = *reinterpret_cast<const uint4*>(p.o + off);
+                    const uint4 g = *reinterpret_cast<const uint4*>(p.dout + off);
+                    const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+                    const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        acc = fmaf(__uint_as_float(aw[e] << 16), __uint_as_float(gw[e] << 16), acc);
+                        acc = fmaf(__uint_as_float(aw[e] & 0xffff0000u), __uint_as_float(gw[e] & 0xffff0000u), acc);
+                    }
+                }
+#pragma unroll
+                for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                const float v = __shfl_sync(0xffffffffu, acc, (lane % RPP) * LPR);
+                if (lane / RPP == i) dv = v;
+            }
+            if (q0 + row < p.T) lse2 = p.lse[(size_t(b) * p.Hq + h) * p.T + q0 + row] * 1.4426950408889634f;
+            if (half == 0) {
+                p.lse2_w[vrow] = lse2;
+                p.dvec_w[vrow] = dv;
+            }
+        }
+        bool ok = true;
+        for (int j = 0; j < n_kv; ++j) {
+            const int buf = DBL ? (j & 1) : 0;
+            const uint32_t s_par = DBL ? ((j >> 1) & 1) : (j & 1);
+            ok = mbar_wait_warp(&bar_s_full[buf], s_par, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+            if (!ok) break;
+            tc_fence_after_sync();
+            // phase A: P from S
+            float pr[64];
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t sv[32];
+                tmem_ld_x32(tmem + lane_base + Cfg::col_s(buf) + c0 + c * 32, sv);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    pr[c * 32 + i] = ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse2));
+            }
+            if (j == qt) {
+#pragma unroll
+                for (int i = 0; i < 64; ++i)
+                    if (c0 + i > row) pr[i] = 0.f;  // key above the diagonal
+            }
+            ok = mbar_wait_warp(bar_dp_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+            if (!ok) break;
+            tc_fence_after_sync();
+            // phase B: dS = P (dP - D), written over dP as BF16
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t dp[32], pk[16];
+                tmem_ld_x32(tmem + lane_base + Cfg::kColDP + c0 + c * 32, dp);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    pk[i] = pack_bf16x2(pr[c * 32 + 2 * i] * (__uint_as_float(dp[2 * i]) - dv),
+                                        pr[c * 32 + 2 * i + 1] * (__uint_as_float(dp[2 * i + 1]) - dv));
+                tmem_st_x16(tmem + lane_base + Cfg::kColDP + c0 + c * 16, pk);
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(bar_ds_full);
+        }
+        if (ok) ok = mbar_wait(bar_acc, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            tc_fence_after_sync();
+#pragma unroll
+            for (int c = 0; c < D / 64; ++c) {
+                uint32_t v[32];
+                const int col = half * (D / 2) + c * 32;
+                tmem_ld_x32(tmem + lane_base + Cfg::kColAcc0 + col, v);
+                tmem_wait_ld();
+                stage_row_chunk<D>(sQ, row, col, v, p.scale);
+            }
+            fence_proxy_async_smem();
+        }
+        tc_fence_before_sync();
+        named_bar_sync(1, 256);
+        if (ok && tid == 0) {
+#pragma unroll
+            for (int bx = 0; bx < Cfg::kBoxes; ++bx) tma_store_4d(&tmdQ, sQ + bx * Cfg::kBoxBytes, bx * 64, q0, h, b);
+            tma_store_commit();
+            tma_store_wait_read0();
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, Cfg::kTmemCols);
+    }
+}
+
+
+// ---------------------------------------------------------------------------------------
 // dK/dV pass: one CTA per (key tile, KV head, batch); loops over the query heads of the
 // group and, for each, over the query tiles at or below the diagonal.
 // ---------------------------------------------------------------------------------------
@@ -589,15 +895,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             tc_fence_after_sync();
             // dP^T of the next iteration first: nothing of this iteration lives in the dP block any more
             // (dS^T was written next to P^T inside the S buffer), so the compute warps get it early.
-            if (it + 1 < n_it) {
-                if (!DBL && !mbar_wait_warp(&bar_full[(it + 1) % NST], ((it + 1) / NST) & 1, abort_flag, p.status,
-                                            DEV_WAIT_TIMEOUT_LOAD)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after_sync();
-                issue_dp(it + 1);
-            }
+            // (with a single S buffer, D = 128, the loads of the next iteration may still be in flight:
+            // there dP^T follows S^T below instead)
+            if (DBL && it + 1 < n_it) issue_dp(it + 1);
             if (elect_one()) {
                 // dV += P^T dO ; dK += dS^T Q   (P^T and dS^T sit side by side in S buffer `buf`)
                 issue_ts_over_rows<D>(tmem + Cfg::kColAcc0, tmem + Cfg::col_s(buf),
@@ -611,6 +911,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             if (!DBL && it + 1 < n_it) {
                 ok = issue_s(it + 1);
                 if (!ok) break;
+                issue_dp(it + 1);
             }
             if (DBL && it + 2 < n_it) {
                 ok = issue_s(it + 2);

@@ -175,17 +175,24 @@ inline void record_bwd_event(int i, cudaStream_t st) {
 
 template <int D>
 int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk64, const CUtensorMap& tv64, const CUtensorMap& tk,
-               const CUtensorMap& tv, const CUtensorMap& tdo, const CUtensorMap& tdk, const CUtensorMap& tdv,
-               const BwdParams& p, cudaStream_t st) {
+               const CUtensorMap& tv, const CUtensorMap& tdo, const CUtensorMap& tdq, const CUtensorMap& tdk,
+               const CUtensorMap& tdv, const BwdParams& p, cudaStream_t st) {
     static bool dq_set[kMaxDevices] = {false}, dkdv_set[kMaxDevices] = {false};
-    int rc = set_smem_once(attn_bwd_dq_kernel<D>, DqCfg<D>::kSmemBytes, dq_set);
+    // D = 64: 64-key tiles, two CTAs per SM.  D = 128: 128-key tiles, one CTA per SM (tensor-pipe bound).
+    constexpr bool kWide = (D == 128);
+    int rc = kWide ? set_smem_once(attn_bwd_dq_wide_kernel<D>, DqWideCfg<D>::kSmemBytes, dq_set)
+                   : set_smem_once(attn_bwd_dq_kernel<D>, DqCfg<D>::kSmemBytes, dq_set);
     if (rc) return rc;
     rc = set_smem_once(attn_bwd_dkdv_kernel<D>, BwdCfg<D>::kSmemBytes, dkdv_set);
     if (rc) return rc;
     record_bwd_event(0, st);
     // the dQ pass also writes the two per-row vectors the dK/dV pass reads
-    if (launch_pdl(attn_bwd_dq_kernel<D>, (unsigned)(p.n_tiles * p.Hq * p.B), 192, DqCfg<D>::kSmemBytes, st, tq, tk64, tv64,
-                   tdo, p) != cudaSuccess) {
+    const unsigned dq_grid = (unsigned)(p.n_tiles * p.Hq * p.B);
+    const cudaError_t e = kWide ? launch_pdl(attn_bwd_dq_wide_kernel<D>, dq_grid, 320, DqWideCfg<D>::kSmemBytes, st, tq, tk,
+                                             tv, tdo, tdq, p)
+                                : launch_pdl(attn_bwd_dq_kernel<D>, dq_grid, 192, DqCfg<D>::kSmemBytes, st, tq, tk64, tv64,
+                                             tdo, p);
+    if (e != cudaSuccess) {
         cudaGetLastError();
         return B200ATTN_ERR_CUDA;
     }
@@ -231,13 +238,14 @@ extern "C" int b200attn_bwd(const void* q, const void* k, const void* v, const v
     int* status = status_ptr(&rc);
     if (!status) return rc;
     const Strides sq = strides_for(layout, Hq, T, D), sk = strides_for(layout, Hkv, T, D);
-    CUtensorMap tq, tk, tv, tk64, tv64, tdo, tdk, tdv;
+    CUtensorMap tq, tk, tv, tk64, tv64, tdo, tdq, tdk, tdv;
     if (!make_tmap_bf16_4d(&tq, q, D, T, Hq, B, sq.t, sq.h, sq.b, 128) ||
         !make_tmap_bf16_4d(&tk, k, D, T, Hkv, B, sk.t, sk.h, sk.b, 128) ||
         !make_tmap_bf16_4d(&tv, v, D, T, Hkv, B, sk.t, sk.h, sk.b, 128) ||
         !make_tmap_bf16_4d(&tk64, k, D, T, Hkv, B, sk.t, sk.h, sk.b, 64) ||
         !make_tmap_bf16_4d(&tv64, v, D, T, Hkv, B, sk.t, sk.h, sk.b, 64) ||
         !make_tmap_bf16_4d(&tdo, dout, D, T, Hq, B, sq.t, sq.h, sq.b, 128) ||
+        !make_tmap_bf16_4d(&tdq, dq, D, T, Hq, B, sq.t, sq.h, sq.b, 128) ||
         !make_tmap_bf16_4d(&tdk, dk, D, T, Hkv, B, sk.t, sk.h, sk.b, 128) ||
         !make_tmap_bf16_4d(&tdv, dv, D, T, Hkv, B, sk.t, sk.h, sk.b, 128))
         return B200ATTN_ERR_TENSOR_MAP;
@@ -266,8 +274,8 @@ extern "C" int b200attn_bwd(const void* q, const void* k, const void* v, const v
     p.q_sb = sq.b;
     p.status = status;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return D == 64 ? launch_bwd<64>(tq, tk64, tv64, tk, tv, tdo, tdk, tdv, p, st)
-                   : launch_bwd<128>(tq, tk64, tv64, tk, tv, tdo, tdk, tdv, p, st);
+    return D == 64 ? launch_bwd<64>(tq, tk64, tv64, tk, tv, tdo, tdq, tdk, tdv, p, st)
+                   : launch_bwd<128>(tq, tk64, tv64, tk, tv, tdo, tdq, tdk, tdv, p, st);
 }
 
 // ---------------------------------------------------------------------------------------

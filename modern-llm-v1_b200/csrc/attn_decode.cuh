@@ -9,8 +9,8 @@
 // (128 keys) stream through a 3-stage shared-memory ring filled by TMA (128-byte swizzle,
 // which also makes the row-per-thread reads bank-conflict free).
 //
-// Roles (160 threads): warps 0-3 compute (thread t <-> key t of the tile for q.k; warp w,
-// lane <-> head-dim pair for p.V over the warp's own 32 keys), warp 4 = TMA producer.
+// Roles (160 threads): warps 0-3 compute with warp-level BF16 MMAs (m16n8k16: the 16 rows are
+// the query heads of the group), each warp on its own 32 keys of a tile; warp 4 = TMA producer.
 // Each split writes an un-normalised partial (m, l, O); a small combine kernel merges them.
 #pragma once
 
@@ -20,7 +20,7 @@ namespace b200attn {
 
 struct DecodeParams {
     int B, L, Hq, Hkv, group;
-    int G;         // query heads served per CTA (a divisor of group, <= 8)
+    int G;         // query heads served per CTA (a divisor of group, <= 16)
     int n_chunks;  // group / G
     int n_splits;
     int tiles_per_split;
@@ -39,31 +39,62 @@ struct DecodeCfg {
     static constexpr int kTileBytes = kTileKeys * D * 2;
     static constexpr int kBoxBytes = 128 * 64 * 2;
     static constexpr int kBoxes = D / 64;
-    static constexpr int kMaxG = 8;
-    // K and V rings, q (G x D floats), p (128 x G floats), cross-warp scratch
-    static constexpr int kSmemBytes =
-        2 * kStages * kTileBytes + kMaxG * D * 4 + 128 * kMaxG * 4 + 4 * kMaxG * D * 4 + 256 + 1024;
+    static constexpr int kMaxG = 16;                    // query heads per CTA = rows of the m16n8k16 MMA
+    static constexpr int kQBytes = 16 * D * 2;          // q rows as BF16, zero padded to 16 rows, swizzled
+    // the end-of-kernel merge scratch (per warp 16 rows x (O row, m, l) as FP32) re-uses the K ring
+    static constexpr int kSmemBytes = 2 * kStages * kTileBytes + kQBytes + 256 + 1024;
 };
 
-template <int D, int G>
+// ---- warp-level tensor-core pieces (mma.sync is enough here: the kernel is bound by HBM, and the
+// ---- 16-row MMA shape matches "all query heads of a KV group against one key tile")
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// Byte offset of the 16-byte chunk `chunk` (8 BF16 of the head dimension) of row `r` inside a tile of
+// [rows][64]-boxes written by TMA with the 128-byte swizzle.
+__device__ __forceinline__ uint32_t swz_off(int r, int chunk, int box_bytes) {
+    return uint32_t((chunk >> 3) * box_bytes + r * 128 + (((chunk & 7) ^ (r & 7)) << 4));
+}
+
+// One CTA = (split of the cache, KV head x head chunk, batch).  Warps 0-3 compute, each on its own
+// 32 keys of every 128-key tile and with its own running (m, l, O), so there is no CTA-wide
+// synchronisation inside the loop; the four states are merged once at the end.  Warp 4 is the TMA
+// producer.  S = Q K^T and O += P V run as m16n8k16 BF16 MMAs whose 16 rows are the G <= 16 query
+// heads that share this KV head (rows >= G are zero padding).
+template <int D>
 __global__ void __launch_bounds__(160)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                    const DecodeParams p) {
     using Cfg = DecodeCfg<D>;
     constexpr int NST = Cfg::kStages;
+    constexpr int KS = D / 16;  // k-steps of Q K^T
+    constexpr int DT = D / 8;   // 8-column output tiles of P V
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sK = smem;
     uint8_t* sV = sK + NST * Cfg::kTileBytes;
-    float* sQ = reinterpret_cast<float*>(sV + NST * Cfg::kTileBytes);  // [G][D]
-    float* sP = sQ + Cfg::kMaxG * D;                                    // [128][G]
-    float* sRed = sP + 128 * Cfg::kMaxG;                                // [4][G][D] / [4][G]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sRed + 4 * Cfg::kMaxG * D);
-    uint64_t* bar_full = bars;         // [NST]
-    uint64_t* bar_free = bars + NST;   // [NST]
+    uint8_t* sQ = sV + NST * Cfg::kTileBytes;                        // [16 rows][D] BF16, swizzled like a tile
+    float* sRed = reinterpret_cast<float*>(sK);  // [4 warps][16 rows][D + 2], used after the last tile only
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sQ + Cfg::kQBytes);
+    uint64_t* bar_full = bars;        // [NST]
+    uint64_t* bar_free = bars + NST;  // [NST]
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * NST);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = p.G;
     const int split = blockIdx.x;
     const int hk = int(blockIdx.y) / p.n_chunks;
     const int chunk = int(blockIdx.y) % p.n_chunks;
@@ -85,10 +116,12 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         }
         fence_mbar_init();
     }
-    // q rows of the G heads -> FP32 in shared memory
-    for (int i = tid; i < G * D; i += blockDim.x) {
-        const uint32_t raw = p.q[(size_t(b) * p.Hq + h0) * D + i];
-        sQ[i] = __uint_as_float(raw << 16);
+    // q rows of the G heads -> shared memory (BF16, 16-byte chunks, swizzled); rows >= G are zero
+    for (int i = tid; i < 16 * (D / 8); i += blockDim.x) {
+        const int r = i / (D / 8), c = i % (D / 8);
+        uint4 val = make_uint4(0u, 0u, 0u, 0u);
+        if (r < G) val = *reinterpret_cast<const uint4*>(p.q + (size_t(b) * p.Hq + h0 + r) * D + c * 8);
+        *reinterpret_cast<uint4*>(sQ + swz_off(r, c, 16 * 128)) = val;
     }
     __syncthreads();
 
@@ -115,144 +148,148 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     }
 
     // ---------------------------------------------------------------------- compute warps
-    constexpr int DPT = D / 32;  // head-dim elements per lane in the p.V phase (2 or 4)
-    float m_run[G], l_part[G], acc[G][DPT];
+    // A fragments of Q (rows = heads): one ldmatrix.x4 per k-step
+    uint32_t aq[KS][4];
+    {
+        const uint32_t q_base = smem_u32(sQ);
+        const int r = (lane & 7) + ((lane >> 3) & 1) * 8;  // matrices 0,2: rows 0-7; 1,3: rows 8-15
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-        m_run[g] = -INFINITY;
-        l_part[g] = 0.f;
-#pragma unroll
-        for (int e = 0; e < DPT; ++e) acc[g][e] = 0.f;
+        for (int ks = 0; ks < KS; ++ks) {
+            const int c = ks * 2 + (lane >> 4);  // matrices 0,1: k 0-7; 2,3: k 8-15
+            ldsm_x4(q_base + swz_off(r, c, 16 * 128), aq[ks][0], aq[ks][1], aq[ks][2], aq[ks][3]);
+        }
     }
+    // this thread holds rows r0 = lane / 4 and r1 = r0 + 8 (query heads), key / head-dim columns (lane % 4) * 2 + {0, 1}
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float o[DT][4];
+#pragma unroll
+    for (int dt = 0; dt < DT; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
+    const int kw = warp * 32;  // this warp's keys inside a tile
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
         const int s = j % NST;
-        // A wait that gives up sets the CTA's abort word; the barrier makes every compute thread
-        // see the same word, so the whole group leaves the loop together (no thread is left
-        // behind at a later named barrier).
-        mbar_wait(&bar_full[s], (j / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-        named_bar_sync(1, 128);
-        if (*abort_flag != 0) {
-            ok = false;
-            break;
-        }
-        const uint8_t* kt = sK + s * Cfg::kTileBytes;
-        const uint8_t* vt = sV + s * Cfg::kTileBytes;
-        // ---- scores of key `tid` against the G heads
-        float sc[G];
+        ok = mbar_wait_warp(&bar_full[s], (j / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+        if (!ok) break;
+        const uint32_t k_base = smem_u32(sK + s * Cfg::kTileBytes);
+        const uint32_t v_base = smem_u32(sV + s * Cfg::kTileBytes);
+        // ---- S[16 heads x 32 keys] = Q K^T
+        float sc[4][4];
 #pragma unroll
-        for (int g = 0; g < G; ++g) sc[g] = 0.f;
+        for (int nt = 0; nt < 4; ++nt) {
+            sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+            const int key = kw + nt * 8 + (lane & 7);
 #pragma unroll
-        for (int c = 0; c < D / 8; ++c) {
-            const int bx = c >> 3, cc = c & 7;
-            const uint4 kw = *reinterpret_cast<const uint4*>(kt + bx * Cfg::kBoxBytes + tid * 128 + ((cc ^ (tid & 7)) << 4));
-            const uint32_t w[4] = {kw.x, kw.y, kw.z, kw.w};
-            float kf[8];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                kf[2 * i] = __uint_as_float(w[i] << 16);
-                kf[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-            }
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float4 qa = *reinterpret_cast<const float4*>(sQ + g * D + c * 8);
-                const float4 qb = *reinterpret_cast<const float4*>(sQ + g * D + c * 8 + 4);
-                sc[g] = fmaf(kf[0], qa.x, sc[g]);
-                sc[g] = fmaf(kf[1], qa.y, sc[g]);
-                sc[g] = fmaf(kf[2], qa.z, sc[g]);
-                sc[g] = fmaf(kf[3], qa.w, sc[g]);
-                sc[g] = fmaf(kf[4], qb.x, sc[g]);
-                sc[g] = fmaf(kf[5], qb.y, sc[g]);
-                sc[g] = fmaf(kf[6], qb.z, sc[g]);
-                sc[g] = fmaf(kf[7], qb.w, sc[g]);
+            for (int kk = 0; kk < KS / 2; ++kk) {
+                uint32_t b0, b1, b2, b3;  // chunks 4kk .. 4kk+3 of the key rows: two k-steps
+                ldsm_x4(k_base + swz_off(key, kk * 4 + (lane >> 3), Cfg::kBoxBytes), b0, b1, b2, b3);
+                mma_bf16_16816(sc[nt], aq[2 * kk], b0, b1);
+                mma_bf16_16816(sc[nt], aq[2 * kk + 1], b2, b3);
             }
         }
-        const bool valid = (tile0 + j) * 128 + tid < p.L;
-        // ---- tile maximum per head: warp shuffle, then across the 4 warps
-        float mx[G];
+        // ---- mask keys beyond the cache length (last tile only)
+        const int key0 = (tile0 + j) * 128 + kw + (lane & 3) * 2;
+        if ((tile0 + j) * 128 + 128 > p.L) {
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-            if (!valid) sc[g] = -INFINITY;
-            mx[g] = sc[g];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) mx[g] = fmaxf(mx[g], __shfl_xor_sync(0xffffffffu, mx[g], o));
-        }
-        float* sMax = sRed;  // [4][G]
-        if (lane == 0) {
-#pragma unroll
-            for (int g = 0; g < G; ++g) sMax[warp * G + g] = mx[g];
-        }
-        named_bar_sync(1, 128);
-        float pv[G];
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            const float m_new = fmaxf(fmaxf(fmaxf(sMax[g], sMax[G + g]), fmaxf(sMax[2 * G + g], sMax[3 * G + g])), m_run[g]);
-            const float alpha = ex2_approx((m_run[g] - m_new) * p.scale_log2);  // 0 on the first tile
-            m_run[g] = m_new;
-            pv[g] = ex2_approx((sc[g] - m_new) * p.scale_log2);
-            l_part[g] = l_part[g] * alpha + pv[g];
-#pragma unroll
-            for (int e = 0; e < DPT; ++e) acc[g][e] *= alpha;
-            sP[tid * G + g] = pv[g];
-        }
-        named_bar_sync(1, 128);  // also orders the sMax reads before the next tile's writes
-        // ---- O += p V over this warp's own 32 keys; lane owns DPT consecutive head-dim elements
-#pragma unroll 4
-        for (int kk = 0; kk < 32; ++kk) {
-            const int key = warp * 32 + kk;
-            const int col = lane * DPT;  // first head-dim element of this lane
-            const int bx = col >> 6, cc = (col & 63) >> 3;
-            const uint8_t* src = vt + bx * Cfg::kBoxBytes + key * 128 + ((cc ^ (key & 7)) << 4) + (col & 7) * 2;
-            float vf[DPT];
-            if (DPT == 2) {
-                const uint32_t w = *reinterpret_cast<const uint32_t*>(src);
-                vf[0] = __uint_as_float(w << 16);
-                vf[1] = __uint_as_float(w & 0xffff0000u);
-            } else {
-                const uint2 w = *reinterpret_cast<const uint2*>(src);
-                vf[0] = __uint_as_float(w.x << 16);
-                vf[1] = __uint_as_float(w.x & 0xffff0000u);
-                vf[2] = __uint_as_float(w.y << 16);
-                vf[3] = __uint_as_float(w.y & 0xffff0000u);
+            for (int nt = 0; nt < 4; ++nt) {
+                if (key0 + nt * 8 >= p.L) sc[nt][0] = sc[nt][2] = -INFINITY;
+                if (key0 + nt * 8 + 1 >= p.L) sc[nt][1] = sc[nt][3] = -INFINITY;
             }
+        }
+        // ---- online softmax per head row (rows r0 and r1), over this warp's 32 keys
+        float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
+        float mx1 = fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3]));
+        mx0 = fmaxf(mx0, fmaxf(fmaxf(sc[2][0], sc[2][1]), fmaxf(sc[3][0], sc[3][1])));
+        mx1 = fmaxf(mx1, fmaxf(fmaxf(sc[2][2], sc[2][3]), fmaxf(sc[3][2], sc[3][3])));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        // a warp whose 32 keys are all beyond the cache has mn = -inf: keep its state neutral
+        const float a0 = (mn0 == -INFINITY) ? 1.f : ex2_approx((m0 - mn0) * p.scale_log2);
+        const float a1 = (mn1 == -INFINITY) ? 1.f : ex2_approx((m1 - mn1) * p.scale_log2);
+        const float nb0 = (mn0 == -INFINITY) ? 0.f : -mn0 * p.scale_log2;
+        const float nb1 = (mn1 == -INFINITY) ? 0.f : -mn1 * p.scale_log2;
+        m0 = mn0;
+        m1 = mn1;
+        float rs0 = 0.f, rs1 = 0.f;
+        uint32_t ap[2][4];  // P as A fragments: k-step kk covers keys 16 kk .. 16 kk + 15
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float pg = sP[key * G + g];
+        for (int nt = 0; nt < 4; ++nt) {
+            const float p0 = ex2_approx(fmaf(sc[nt][0], p.scale_log2, nb0));
+            const float p1 = ex2_approx(fmaf(sc[nt][1], p.scale_log2, nb0));
+            const float p2 = ex2_approx(fmaf(sc[nt][2], p.scale_log2, nb1));
+            const float p3 = ex2_approx(fmaf(sc[nt][3], p.scale_log2, nb1));
+            rs0 += p0 + p1;
+            rs1 += p2 + p3;
+            ap[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16x2(p0, p1);
+            ap[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16x2(p2, p3);
+        }
+        l0 = l0 * a0 + rs0;
+        l1 = l1 * a1 + rs1;
+        // ---- O[16 x D] = alpha O + P V
 #pragma unroll
-                for (int e = 0; e < DPT; ++e) acc[g][e] = fmaf(pg, vf[e], acc[g][e]);
+        for (int dt = 0; dt < DT; ++dt) {
+            o[dt][0] *= a0;
+            o[dt][1] *= a0;
+            o[dt][2] *= a1;
+            o[dt][3] *= a1;
+        }
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+            const int key = kw + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;  // matrices 0,2: keys 0-7; 1,3: 8-15
+#pragma unroll
+            for (int dp = 0; dp < DT / 2; ++dp) {
+                uint32_t b0, b1, b2, b3;  // head-dim chunks 2dp (matrices 0,1) and 2dp+1 (matrices 2,3)
+                ldsm_x4_trans(v_base + swz_off(key, dp * 2 + (lane >> 4), Cfg::kBoxBytes), b0, b1, b2, b3);
+                mma_bf16_16816(o[2 * dp], ap[kk], b0, b1);
+                mma_bf16_16816(o[2 * dp + 1], ap[kk], b2, b3);
             }
         }
         mbar_arrive(&bar_free[s]);
     }
-    if (!ok) return;
-    // ---- reduce l over all threads and O over the 4 warps, write the partial
-    float* sAcc = sRed;  // [4][G][D]
-    named_bar_sync(1, 128);
+    // ---- merge the four warps' states and write the split's partial (un-normalised O, m, l)
+    named_bar_sync(1, 128);  // every compute thread, also after a wait that gave up
+    if (*abort_flag != 0) return;
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    constexpr int RS = D + 2;  // row stride of the scratch: O row, then m, then l
+    float* mine = sRed + warp * 16 * RS;
+    const int r0 = lane >> 2, r1 = r0 + 8, cq = (lane & 3) * 2;
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) l_part[g] += __shfl_xor_sync(0xffffffffu, l_part[g], o);
-#pragma unroll
-        for (int e = 0; e < DPT; ++e) sAcc[(warp * G + g) * D + lane * DPT + e] = acc[g][e];
+    for (int dt = 0; dt < DT; ++dt) {
+        mine[r0 * RS + dt * 8 + cq] = o[dt][0];
+        mine[r0 * RS + dt * 8 + cq + 1] = o[dt][1];
+        mine[r1 * RS + dt * 8 + cq] = o[dt][2];
+        mine[r1 * RS + dt * 8 + cq + 1] = o[dt][3];
     }
-    float* sL = sP;  // [4][G]
-    if (lane == 0) {
-#pragma unroll
-        for (int g = 0; g < G; ++g) sL[warp * G + g] = l_part[g];
+    if ((lane & 3) == 0) {
+        mine[r0 * RS + D] = m0;
+        mine[r0 * RS + D + 1] = l0;
+        mine[r1 * RS + D] = m1;
+        mine[r1 * RS + D + 1] = l1;
     }
     named_bar_sync(1, 128);
     for (int i = tid; i < G * D; i += 128) {
         const int g = i / D, d = i % D;
-        const float o = sAcc[(0 * G + g) * D + d] + sAcc[(1 * G + g) * D + d] + sAcc[(2 * G + g) * D + d] +
-                        sAcc[(3 * G + g) * D + d];
-        p.part_o[((size_t(b) * p.Hq + h0 + g) * p.n_splits + split) * D + d] = o;
-    }
+        float m = -INFINITY;
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-        if (tid == g) {
-            const size_t idx = (size_t(b) * p.Hq + h0 + g) * p.n_splits + split;
-            p.part_m[idx] = m_run[g];
-            p.part_l[idx] = sL[g] + sL[G + g] + sL[2 * G + g] + sL[3 * G + g];
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, sRed[(w * 16 + g) * RS + D]);
+        float acc = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = sRed[(w * 16 + g) * RS + D];
+            const float f = (mw == -INFINITY) ? 0.f : ex2_approx((mw - m) * p.scale_log2);
+            acc += f * sRed[(w * 16 + g) * RS + d];
+            l += f * sRed[(w * 16 + g) * RS + D + 1];
+        }
+        const size_t idx = (size_t(b) * p.Hq + h0 + g) * p.n_splits + split;
+        p.part_o[idx * D + d] = acc;
+        if (d == 0) {
+            p.part_m[idx] = m;
+            p.part_l[idx] = l;
         }
     }
 }

@@ -326,9 +326,10 @@ extern "C" int b200attn_bwd_static(const void* q, const void* k, const void* v, 
 
 namespace {
 
-// Query heads served per decode CTA: the largest divisor of the group size that is <= 8.
+// Query heads served per decode CTA: the largest divisor of the group size that is <= 16
+// (the row count of the kernel's MMA shape).
 inline int decode_heads_per_cta(int group) {
-    for (int g = 8; g >= 1; --g)
+    for (int g = 16; g >= 1; --g)
         if (group % g == 0) return g;
     return 1;
 }
@@ -338,8 +339,9 @@ inline int decode_pick_splits(int B, int L, int Hq, int Hkv, int n_splits) {
     if (n_splits <= 0) {
         const int group = Hq / Hkv;
         const long long units = (long long)B * Hkv * (group / decode_heads_per_cta(group));
-        // aim at four CTAs per SM of a 148-SM part so that the tail is short
-        long long want = (4 * 148 + units - 1) / units;
+        // two CTAs fit on an SM: fill the 2 x 148 slots of the part once, and do not split further
+        // (every extra split costs a partial write, a combine read and a shorter stream per CTA)
+        long long want = (2 * 148) / units;
         n_splits = (int)(want < 1 ? 1 : want);
     }
     if (n_splits > n_all) n_splits = n_all;
@@ -348,28 +350,14 @@ inline int decode_pick_splits(int B, int L, int Hq, int Hkv, int n_splits) {
     return (n_all + tps - 1) / tps;  // drop splits that would be empty
 }
 
-template <int D, int G>
-int launch_decode_g(const CUtensorMap& tk, const CUtensorMap& tv, const DecodeParams& p, cudaStream_t st) {
-    using Cfg = DecodeCfg<D>;
-    static bool set[kMaxDevices] = {false};
-    int rc = set_smem_once(attn_decode_kernel<D, G>, Cfg::kSmemBytes, set);
-    if (rc) return rc;
-    attn_decode_kernel<D, G><<<dim3(p.n_splits, p.Hkv * p.n_chunks, p.B), 160, Cfg::kSmemBytes, st>>>(tk, tv, p);
-    return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
-}
-
 template <int D>
 int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, const DecodeParams& p, cudaStream_t st) {
-    switch (p.G) {
-        case 1: return launch_decode_g<D, 1>(tk, tv, p, st);
-        case 2: return launch_decode_g<D, 2>(tk, tv, p, st);
-        case 3: return launch_decode_g<D, 3>(tk, tv, p, st);
-        case 4: return launch_decode_g<D, 4>(tk, tv, p, st);
-        case 5: return launch_decode_g<D, 5>(tk, tv, p, st);
-        case 6: return launch_decode_g<D, 6>(tk, tv, p, st);
-        case 7: return launch_decode_g<D, 7>(tk, tv, p, st);
-        default: return launch_decode_g<D, 8>(tk, tv, p, st);
-    }
+    using Cfg = DecodeCfg<D>;
+    static bool set[kMaxDevices] = {false};
+    int rc = set_smem_once(attn_decode_kernel<D>, Cfg::kSmemBytes, set);
+    if (rc) return rc;
+    attn_decode_kernel<D><<<dim3(p.n_splits, p.Hkv * p.n_chunks, p.B), 160, Cfg::kSmemBytes, st>>>(tk, tv, p);
+    return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
 }
 
 }  // namespace

@@ -35,7 +35,7 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 
 # DRAM traffic of the dominant kernel per launch at the default workload, from the committed ncu
 # summary (profiles/); None until a capture exists for the current kernel.
-NCU_TRAFFIC_BYTES = {"c2_50m_train": 34382080}  # dK/dV pass: dram read + write, profiles/attn_fwd_bwd_c2_50m_train.md
+NCU_TRAFFIC_BYTES = {"c2_50m_train": 46674176}  # dQ pass: dram read + write, profiles/attn_fwd_bwd_c2_50m_train.md
 
 
 def load_peaks():
@@ -312,14 +312,65 @@ def e2e_measure(m, cfg, host_sets, steps, warmup, device):
     return ms / steps, h2d, d2h
 
 
+def run_decode(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier):
+    """Split-KV decode (one query token per sequence against the KV cache): HBM GB/s.  Algorithmic bytes
+    per step = K cache + V cache + q + o.  The cache (268 MB at the default shape) is larger than L2."""
+    import torch
+    import torch.distributed as dist
+    from modern_llm_v1_b200 import inputs
+
+    q, kc, vc, _, _ = inputs.make_decode_inputs(cfg, 20260005 + 1000 * rank)
+    q, kc, vc = q.to(device), kc.to(device), vc.to(device)
+    o = torch.empty_like(q)
+    lse = torch.empty(cfg.B, cfg.Hq, dtype=torch.float32, device=device)
+
+    def step():
+        m.flash_attn_decode(q, kc, vc, o, lse, cfg.B, cfg.T, cfg.Hq, cfg.Hkv, cfg.D)
+
+    for _ in range(warmup):
+        step()
+    m.device_status()
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    m.device_status()
+    nbytes = cfg.decode_bytes()
+    gbs = world * nbytes / (ms * 1e-3) / 1e9
+    peak = float(peaks["hbm_gbs"])
+    if rank == 0:
+        print(json.dumps({
+            "metric": "decode_attn_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": cfg.name, "B_per_gpu": cfg.B, "cache_len": cfg.T, "Hq": cfg.Hq, "Hkv": cfg.Hkv,
+                       "D": cfg.D, "l2": f"cache of {nbytes / 1e6:.0f} MB > 126 MB L2"},
+            "clocks": clocks, "gpu_launches": 2 * steps,
+            "roofline": {"bound": "hbm", "kernel": "attn_decode_kernel", "achieved": gbs / world, "peak": peak,
+                         "unit": "GB/s", "frac": gbs / world / peak,
+                         "traffic": 273453056 if cfg.name == "c5_decode" else None,  # profiles/attn_decode_c5_decode.md
+                         "peak_source": f"hbm_gbs of {peaks['_source']}", "bytes_per_launch": nbytes,
+                         "note": "time includes the combine kernel (2 launches per step)"},
+        }), flush=True)
+
+
 def main():
     args = parse_args()
     import modern_llm_v1_b200 as m
     from modern_llm_v1_b200 import inputs
 
     cfg = inputs.CONFIGS[args.config]
-    if cfg.kind != "train":
-        raise SystemExit("bench.py times the forward+backward path; pick a training configuration")
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -347,6 +398,12 @@ def main():
     peaks = load_peaks()
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
+    if cfg.kind == "decode":
+        run_decode(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
 
     # Distinct buffer sets so that the working set of consecutive steps exceeds the 126 MB L2.
     seed0 = 20260002 + 1000 * rank

@@ -145,10 +145,22 @@ def cpu_time_units(cfg, seed, n_units, repeats=1):
     return best, flops
 
 
+def use_all_host_cores():
+    """torchrun exports OMP_NUM_THREADS=1; the CPU legs want every core this process may run on."""
+    from oracle import attn_oracle as ao
+
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    ao.set_num_threads(n)
+    return ao.num_threads()
+
+
 def cpu_baseline(cfg, seed):
     from oracle import attn_oracle as ao
 
-    cores = ao.num_threads()
+    cores = use_all_host_cores()
     # about 20 core-seconds of work at ~1.9 GFLOP/s per core of this scalar double-precision port
     unit_flops = cfg.fwd_bwd_flops() / cfg.units
     n_units = int(max(1, min(cfg.units, 20.0 * 1.9e9 / unit_flops)))
@@ -166,7 +178,7 @@ def run_reference_arm(args, cfg, rank, world):
         return
     from oracle import attn_oracle as ao
 
-    cores = ao.num_threads()
+    cores = use_all_host_cores()
     seed = 20260002
     # calibrate on a few units, then size the per-step sample so that the run ends within ~2 minutes
     n_cal = min(cfg.units, max(2, min(cores, 8)))

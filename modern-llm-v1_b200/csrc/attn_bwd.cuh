@@ -129,8 +129,9 @@ __device__ __forceinline__ void stage_row_chunk(uint8_t* tile, int row, int col,
 // (flash_attn_compute_D_kernel, llm/src/model/flash_attn.cu:150-172), and leaves both in the
 // workspace for the dK/dV pass, which therefore has to run after this kernel.
 //
-// Roles (192 threads): warps 0-3 compute (thread r owns query row r == TMEM lane r),
-// warp 4 TMA producer, warp 5 TMEM allocation + MMA issue (converged warps, elected lane).
+// Roles (320 threads): warps 0-7 compute (thread owns query row (warp % 4) * 32 + lane == TMEM lane
+// and the 32 key columns of its part warp / 4), warp 8 TMA producer, warp 9 TMEM allocation + MMA
+// issue (converged warps, elected lane).
 // TMEM: S buffer 0 [0,64), S buffer 1 [64,128) (dS as BF16 over the first 32 columns of the
 // tile's S buffer), dP [128,192), dQ accumulator [192,192+D).  D = 64 needs 256 columns, so two CTAs share an SM.
 // ---------------------------------------------------------------------------------------
@@ -147,10 +148,15 @@ struct DqCfg {
     static constexpr int kTmemCols = (D == 64) ? 256 : 512;
     static constexpr int kCtasPerSm = (D == 64) ? 2 : 1;
     static constexpr int kColS0 = 0, kColS1 = 64, kColDP = 128, kColAcc = 192;
+    static constexpr int kParts = 2;                 // compute warpgroups, each owns 64 / kParts key columns
+    static constexpr int kPartCols = kKeys / kParts;  // 32
+    static constexpr int kComputeThreads = 128 * kParts;
+    static constexpr int kThreads = kComputeThreads + 64;
+    static constexpr int kProducerWarp = 4 * kParts, kMmaWarp = 4 * kParts + 1;
 };
 
 template <int D>
-__global__ void __launch_bounds__(192, DqCfg<D>::kCtasPerSm)
+__global__ void __launch_bounds__(DqCfg<D>::kThreads, DqCfg<D>::kCtasPerSm)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                    const BwdParams p) {
@@ -168,6 +174,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     uint64_t* bar_dp_full = bars + 3;
     uint64_t* bar_ds_full = bars + 4;
     uint64_t* bar_acc = bars + 5;
+    uint64_t* bar_dp_free = bars + 15;       // dP has been read into registers by every compute thread
     uint64_t* bar_kv_full = bars + 6;        // [NST]
     uint64_t* bar_kv_free = bars + 6 + NST;  // [NST]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
@@ -187,7 +194,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     B200ATTN_STAMP(tid == 0, 300);
     // Set-up with one CTA-wide barrier (see the forward kernel).
     grid_dep_launch();
-    if (warp == 4 && lane == 0) {
+    if (warp == Cfg::kProducerWarp && lane == 0) {
         tma_prefetch_desc(&tmQ);
         tma_prefetch_desc(&tmK);
         tma_prefetch_desc(&tmV);
@@ -196,7 +203,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mbar_init(&bar_s_full[0], 1);
         mbar_init(&bar_s_full[1], 1);
         mbar_init(bar_dp_full, 1);
-        mbar_init(bar_ds_full, 128);
+        mbar_init(bar_ds_full, Cfg::kComputeThreads);
+        mbar_init(bar_dp_free, Cfg::kComputeThreads);
         mbar_init(bar_acc, 1);
         for (int s = 0; s < NST; ++s) {
             mbar_init(&bar_kv_full[s], 1);
@@ -226,7 +234,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             }
         }
     }
-    if (warp == 5) {
+    if (warp == Cfg::kMmaWarp) {
         tmem_alloc(tmem_slot, Cfg::kTmemCols);
         tmem_relinquish();
     }
@@ -240,7 +248,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
     if (failed_early) {
         // nothing was started; fall through to the teardown
-    } else if (warp == 4) {
+    } else if (warp == Cfg::kProducerWarp) {
         // ------------------------------------------------------------------ producer (tiles >= NST)
         for (int j = NST; j < n_kv; ++j) {
             const int s = j % NST;
@@ -258,7 +266,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             }
             __syncwarp();
         }
-    } else if (warp == 5) {
+    } else if (warp == Cfg::kMmaWarp) {
         // ------------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc_s = make_idesc_bf16(128, Cfg::kKeys, 0, 0);
         constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
@@ -298,18 +306,30 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (ok && n_kv > 1) ok = issue_s(1);
         for (int j = 0; j < n_kv && ok; ++j) {
             const int s = j % NST;
+            // dP of the next tile as soon as the compute warps have read dP_j into registers (dS_j goes
+            // into S buffer j & 1, so the dP block is free): the MMA round trip then runs under their
+            // arithmetic instead of after it
+            if (j + 1 < n_kv) {
+                ok = mbar_wait_warp(bar_dp_free, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+                if (!ok) break;
+                tc_fence_after_sync();
+                issue_dp(j + 1);
+            }
             ok = mbar_wait_warp(bar_ds_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
             if (!ok) break;
             tc_fence_after_sync();
-            // dP of the next tile first: dS_j lives in S buffer j & 1, the dP block is free again
-            if (j + 1 < n_kv) issue_dp(j + 1);
             const uint64_t kmn_desc = make_sdesc_sw128(smem_u32(sK + s * Cfg::kKVTileBytes), Cfg::kKVBoxBytes, 1024);
             if (elect_one()) {
                 // dQ += dS_j K_j : 64 keys = 4 K steps, dS in the first 32 columns of S buffer j & 1
 #pragma unroll
-                for (int ks = 0; ks < Cfg::kKeys / 16; ++ks)
-                    umma_ts(tmem + Cfg::kColAcc, tmem + ((j & 1) ? Cfg::kColS1 : Cfg::kColS0) + ks * 8,
-                            kmn_desc + uint64_t(ks * 128), idesc_acc, (j > 0) || (ks > 0));
+                for (int ks = 0; ks < Cfg::kKeys / 16; ++ks) {
+                    // part q keeps its BF16 dS values in the first kPartCols / 2 columns of its own range
+                    constexpr int kStepsPerPart = Cfg::kPartCols / 16;
+                    const uint32_t a_col = ((j & 1) ? Cfg::kColS1 : Cfg::kColS0) + (ks / kStepsPerPart) * Cfg::kPartCols +
+                                           (ks % kStepsPerPart) * 8;
+                    umma_ts(tmem + Cfg::kColAcc, tmem + a_col, kmn_desc + uint64_t(ks * 128), idesc_acc,
+                            (j > 0) || (ks > 0));
+                }
                 umma_commit(&bar_kv_free[s]);
             }
             __syncwarp();
@@ -319,8 +339,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         __syncwarp();
     } else {
         // ------------------------------------------------------------------ compute
-        const int row = tid;  // query row in the tile == TMEM lane
-        const uint32_t lane_base = uint32_t(warp * 32) << 16;
+        const int w4 = warp & 3, part = warp >> 2;
+        const int row = w4 * 32 + lane;  // query row in the tile == TMEM lane
+        const uint32_t lane_base = uint32_t(w4 * 32) << 16;
+        const int c0 = part * Cfg::kPartCols;  // first key column of this thread's part
         const bool in_range = q0 + row < p.T;
         const size_t vrow = (size_t(b) * p.Hq + h) * p.Tpad + q0 + row;
         const size_t qoff = size_t(b) * p.q_sb + size_t(h) * p.q_sh + size_t(q0 + row) * p.q_st;
@@ -335,7 +357,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             const size_t tile_off = size_t(b) * p.q_sb + size_t(h) * p.q_sh;
 #pragma unroll
             for (int i = 0; i < LPR; ++i) {
-                const int r = q0 + warp * 32 + i * RPP + lane / LPR;  // global query row read by this lane
+                const int r = q0 + w4 * 32 + i * RPP + lane / LPR;  // global query row read by this lane
                 float acc = 0.f;
                 if (r < p.T) {
                     const size_t off = tile_off + size_t(r) * p.q_st + (lane % LPR) * 8;
@@ -356,48 +378,50 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             }
             if (in_range) lse2 = p.lse[(size_t(b) * p.Hq + h) * p.T + q0 + row] * 1.4426950408889634f;
         }
-        p.lse2_w[vrow] = lse2;
-        p.dvec_w[vrow] = dv;
+        if (part == 0) {
+            p.lse2_w[vrow] = lse2;
+            p.dvec_w[vrow] = dv;
+        }
         B200ATTN_STAMP(tid == 0, 302);
         bool ok = true;
         for (int j = 0; j < n_kv; ++j) {
-            const uint32_t t_s = tmem + lane_base + ((j & 1) ? Cfg::kColS1 : Cfg::kColS0);
+            const uint32_t t_s = tmem + lane_base + ((j & 1) ? Cfg::kColS1 : Cfg::kColS0) + c0;
             ok = mbar_wait_warp(&bar_s_full[j & 1], uint32_t(j >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
             if (!ok) break;
             B200ATTN_STAMP(tid == 0, 308 + 4 * j);
             tc_fence_after_sync();
             // phase A: P from S
-            float pr[64];
+            float pr[32];
             {
-                uint32_t sv[64];
-                tmem_ld_x32(t_s, &sv[0]);
-                tmem_ld_x32(t_s + 32, &sv[32]);
+                uint32_t sv[32];
+                tmem_ld_x32(t_s, sv);
                 tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 64; ++i) pr[i] = ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse2));
+                for (int i = 0; i < 32; ++i) pr[i] = ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse2));
             }
             const int kbase = j * Cfg::kKeys;
             if (kbase + Cfg::kKeys - 1 > q0) {
-                const int lim = q0 + row - kbase;  // columns c <= lim are visible
+                const int lim = q0 + row - kbase - c0;  // columns i <= lim of this part are visible
 #pragma unroll
-                for (int i = 0; i < 64; ++i)
+                for (int i = 0; i < 32; ++i)
                     if (i > lim) pr[i] = 0.f;
             }
             ok = mbar_wait_warp(bar_dp_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
             if (!ok) break;
             B200ATTN_STAMP(tid == 0, 309 + 4 * j);
             tc_fence_after_sync();
-            // phase B: dS = P (dP - D), written as BF16 over the S buffer of this tile
+            // phase B: dS = P (dP - D), written as BF16 over the part's first 16 columns of the S buffer
             {
-                uint32_t dp[64], pk[32];
-                tmem_ld_x32(tmem + lane_base + Cfg::kColDP, &dp[0]);
-                tmem_ld_x32(tmem + lane_base + Cfg::kColDP + 32, &dp[32]);
+                uint32_t dp[32], pk[16];
+                tmem_ld_x32(tmem + lane_base + Cfg::kColDP + c0, dp);
                 tmem_wait_ld();
+                tc_fence_before_sync();
+                mbar_arrive(bar_dp_free);  // dP_j is in registers: the next dP may overwrite the block
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
+                for (int i = 0; i < 16; ++i)
                     pk[i] = pack_bf16x2(pr[2 * i] * (__uint_as_float(dp[2 * i]) - dv),
                                         pr[2 * i + 1] * (__uint_as_float(dp[2 * i + 1]) - dv));
-                tmem_st_x32(t_s, pk);
+                tmem_st_x16(t_s, pk);
             }
             tmem_wait_st();
             tc_fence_before_sync();
@@ -409,11 +433,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         B200ATTN_STAMP(tid == 0, 303);
         if (ok) {
             tc_fence_after_sync();
-            uint16_t* dqrow = p.dq + qoff;
+            uint16_t* dqrow = p.dq + qoff + part * (D / Cfg::kParts);
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
+            for (int c = 0; c < D / Cfg::kParts / 32; ++c) {
                 uint32_t v[32];
-                tmem_ld_x32(tmem + lane_base + Cfg::kColAcc + c * 32, v);
+                tmem_ld_x32(tmem + lane_base + Cfg::kColAcc + part * (D / Cfg::kParts) + c * 32, v);
                 tmem_wait_ld();
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
@@ -430,7 +454,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == Cfg::kMmaWarp) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, Cfg::kTmemCols);
     }
@@ -771,6 +795,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     uint64_t* bar_dp_full = bars + 3;
     uint64_t* bar_pds_full = bars + 4;
     uint64_t* bar_acc = bars + 5;
+    uint64_t* bar_dp_free = bars + 15;    // dP^T has been read into registers by every compute thread
     uint64_t* bar_full = bars + 6;        // [NST]
     uint64_t* bar_free = bars + 6 + NST;  // [NST]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
@@ -793,6 +818,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         mbar_init(&bar_s_full[1], 1);
         mbar_init(bar_dp_full, 1);
         mbar_init(bar_pds_full, Cfg::kComputeThreads);
+        mbar_init(bar_dp_free, Cfg::kComputeThreads);
         mbar_init(bar_acc, 1);
         for (int s = 0; s < NST; ++s) {
             mbar_init(&bar_full[s], 1);
@@ -889,15 +915,20 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         for (int it = 0; it < n_it && ok; ++it) {
             const int s = it % NST;
             const int buf = DBL ? (it & 1) : 0;
+            // dP^T of the next iteration as soon as the compute warps have read this one into registers
+            // (dS^T is written next to P^T inside the S buffer, so the dP block is free): the MMA round trip
+            // runs under their arithmetic.  (With a single S buffer, D = 128, the loads of the next iteration
+            // may still be in flight: there dP^T follows S^T below instead.)
+            if (DBL && it + 1 < n_it) {
+                ok = mbar_wait_warp(bar_dp_free, it & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+                if (!ok) break;
+                tc_fence_after_sync();
+                issue_dp(it + 1);
+            }
             ok = mbar_wait_warp(bar_pds_full, it & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
             if (!ok) break;
             B200ATTN_STAMP(lane == 0, 200 + 4 * it);
             tc_fence_after_sync();
-            // dP^T of the next iteration first: nothing of this iteration lives in the dP block any more
-            // (dS^T was written next to P^T inside the S buffer), so the compute warps get it early.
-            // (with a single S buffer, D = 128, the loads of the next iteration may still be in flight:
-            // there dP^T follows S^T below instead)
-            if (DBL && it + 1 < n_it) issue_dp(it + 1);
             if (elect_one()) {
                 // dV += P^T dO ; dK += dS^T Q   (P^T and dS^T sit side by side in S buffer `buf`)
                 issue_ts_over_rows<D>(tmem + Cfg::kColAcc0, tmem + Cfg::col_s(buf),
@@ -971,6 +1002,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                 uint32_t dp[32], pk[16];
                 tmem_ld_x32(tmem + lane_base + Cfg::kColDP + c0, dp);
                 tmem_wait_ld();
+                tc_fence_before_sync();
+                mbar_arrive(bar_dp_free);  // dP^T is in registers: the next product may overwrite the block
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
                     const float4 d4 = dv4[g];

@@ -190,7 +190,7 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk64, const CUtensorMap
     const unsigned dq_grid = (unsigned)(p.n_tiles * p.Hq * p.B);
     const cudaError_t e = kWide ? launch_pdl(attn_bwd_dq_wide_kernel<D>, dq_grid, 320, DqWideCfg<D>::kSmemBytes, st, tq, tk,
                                              tv, tdo, tdq, p)
-                                : launch_pdl(attn_bwd_dq_kernel<D>, dq_grid, 192, DqCfg<D>::kSmemBytes, st, tq, tk64, tv64,
+                                : launch_pdl(attn_bwd_dq_kernel<D>, dq_grid, DqCfg<D>::kThreads, DqCfg<D>::kSmemBytes, st, tq, tk64, tv64,
                                              tdo, p);
     if (e != cudaSuccess) {
         cudaGetLastError();

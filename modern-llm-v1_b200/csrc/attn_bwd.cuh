@@ -124,31 +124,35 @@ __device__ __forceinline__ void stage_row_chunk(uint8_t* tile, int row, int col,
 }
 
 // ---------------------------------------------------------------------------------------
-// dQ pass: one CTA per (128-row query tile, query head, batch), walking 64-key tiles.
-// It also does the preprocess step for its rows, D = rowsum(O * dO) and L * log2(e)
-// (flash_attn_compute_D_kernel, llm/src/model/flash_attn.cu:150-172), and leaves both in the
-// workspace for the dK/dV pass, which therefore has to run after this kernel.
+// dQ pass (D = 64): persistent CTAs, two per SM.  A CTA walks a static list of work items
+// (item = one 128-row query tile of one (batch, query head); items are ordered heaviest first and
+// dealt round-robin), and every pipeline keeps running across item boundaries: the K/V ring
+// prefetches the next item's tiles, the MMA warp issues the next item's first products while the
+// compute warps write the previous item's dQ rows.  The O tile travels with Q and dO, so the
+// preprocess D = rowsum(O * dO) (flash_attn_compute_D_kernel, llm/src/model/flash_attn.cu:150-172)
+// is shared-memory work at the head of each item; D and L * log2(e) are also left in the workspace
+// for the dK/dV pass, which therefore has to run after this kernel.
 //
 // Roles (320 threads): warps 0-7 compute (thread owns query row (warp % 4) * 32 + lane == TMEM lane
 // and the 32 key columns of its part warp / 4), warp 8 TMA producer, warp 9 TMEM allocation + MMA
-// issue (converged warps, elected lane).
-// TMEM: S buffer 0 [0,64), S buffer 1 [64,128) (dS as BF16 over the first 32 columns of the
-// tile's S buffer), dP [128,192), dQ accumulator [192,192+D).  D = 64 needs 256 columns, so two CTAs share an SM.
+// issue (converged warps, one elected lane issues).
+// TMEM (256 columns): S buffer 0 [0,64), S buffer 1 [64,128) (dS as BF16 over the first 16 columns
+// of each part's range), dP [128,192), dQ accumulator [192,256).
 // ---------------------------------------------------------------------------------------
 template <int D>
 struct DqCfg {
     static constexpr int kKeys = 64;
-    static constexpr int kStages = (D == 64) ? 4 : 2;
+    static constexpr int kStages = 3;
     static constexpr int kQTileBytes = 128 * D * 2;
     static constexpr int kQBoxBytes = 128 * 64 * 2;
     static constexpr int kKVTileBytes = kKeys * D * 2;
     static constexpr int kKVBoxBytes = kKeys * 64 * 2;
     static constexpr int kBoxes = D / 64;
-    static constexpr int kSmemBytes = 2 * kQTileBytes + 2 * kStages * kKVTileBytes + 256 + 1024;
-    static constexpr int kTmemCols = (D == 64) ? 256 : 512;
-    static constexpr int kCtasPerSm = (D == 64) ? 2 : 1;
+    static constexpr int kSmemBytes = 3 * kQTileBytes + 2 * kStages * kKVTileBytes + 512 + 1024;  // Q, dO, O + ring
+    static constexpr int kTmemCols = 256;
+    static constexpr int kCtasPerSm = 2;
     static constexpr int kColS0 = 0, kColS1 = 64, kColDP = 128, kColAcc = 192;
-    static constexpr int kParts = 2;                 // compute warpgroups, each owns 64 / kParts key columns
+    static constexpr int kParts = 2;
     static constexpr int kPartCols = kKeys / kParts;  // 32
     static constexpr int kComputeThreads = 128 * kParts;
     static constexpr int kThreads = kComputeThreads + 64;
@@ -159,80 +163,65 @@ template <int D>
 __global__ void __launch_bounds__(DqCfg<D>::kThreads, DqCfg<D>::kCtasPerSm)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                   const BwdParams p) {
+                   const __grid_constant__ CUtensorMap tmO, const BwdParams p) {
     using Cfg = DqCfg<D>;
     constexpr int NST = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;
     uint8_t* sdO = sQ + Cfg::kQTileBytes;
-    uint8_t* sK = sdO + Cfg::kQTileBytes;        // [NST]
+    uint8_t* sO = sdO + Cfg::kQTileBytes;
+    uint8_t* sK = sO + Cfg::kQTileBytes;         // [NST]
     uint8_t* sV = sK + NST * Cfg::kKVTileBytes;  // [NST]
     uint64_t* bars = reinterpret_cast<uint64_t*>(sV + NST * Cfg::kKVTileBytes);
-    uint64_t* bar_q = bars + 0;
-    uint64_t* bar_s_full = bars + 1;  // [2]
-    uint64_t* bar_dp_full = bars + 3;
-    uint64_t* bar_ds_full = bars + 4;
-    uint64_t* bar_acc = bars + 5;
-    uint64_t* bar_dp_free = bars + 15;       // dP has been read into registers by every compute thread
-    uint64_t* bar_kv_full = bars + 6;        // [NST]
-    uint64_t* bar_kv_free = bars + 6 + NST;  // [NST]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
+    uint64_t* bar_q = bars + 0;         // Q, dO, O of an item have landed            (phase: item)
+    uint64_t* bar_q_free = bars + 1;    // every MMA reading Q, dO of an item is done (phase: item)
+    uint64_t* bar_s_full = bars + 2;    // [2] per S buffer                            (phase: tile / 2)
+    uint64_t* bar_ds_full = bars + 4;   // [2] per S buffer: dS written               (phase: tile / 2)
+    uint64_t* bar_dp_full = bars + 6;   //                                             (phase: tile)
+    uint64_t* bar_dp_free = bars + 7;   // dP read into registers                      (phase: tile)
+    uint64_t* bar_acc = bars + 8;       // dQ accumulator of an item complete          (phase: item)
+    uint64_t* bar_acc_free = bars + 9;  // dQ accumulator read by the epilogue         (phase: item)
+    uint64_t* bar_o_free = bars + 10;   // the O tile has been read by the preprocess  (phase: item)
+    uint64_t* bar_kv_full = bars + 14;        // [NST]
+    uint64_t* bar_kv_free = bars + 14 + NST;  // [NST]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14 + 2 * NST);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 15 + 2 * NST);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // 1-D grid ordered by work: all CTAs of the heaviest query tile come first
     const int n_bh = p.B * p.Hq;
-    const int qt = p.n_tiles - 1 - int(blockIdx.x) / n_bh;
-    const int h = (int(blockIdx.x) % n_bh) % p.Hq, b = (int(blockIdx.x) % n_bh) / p.Hq;
-    const int hk = h / p.group;
-    const int q0 = qt * 128;
-    const int k_end = min(p.T, q0 + 128);
-    const int n_kv = (k_end + Cfg::kKeys - 1) / Cfg::kKeys;
+    const int n_items = p.n_tiles * n_bh;
+    // item id -> (query tile, head, batch); ids are ordered by work, heaviest query tile first
+    auto item_qt = [&](int id) { return p.n_tiles - 1 - id / n_bh; };
+    auto item_h = [&](int id) { return (id % n_bh) % p.Hq; };
+    auto item_b = [&](int id) { return (id % n_bh) / p.Hq; };
+    auto item_nkv = [&](int id) { return (min(p.T, item_qt(id) * 128 + 128) + Cfg::kKeys - 1) / Cfg::kKeys; };
 
-    B200ATTN_TRACE_BEGIN();
-    B200ATTN_STAMP(tid == 0, 300);
-    // Set-up with one CTA-wide barrier (see the forward kernel).
     grid_dep_launch();
     if (warp == Cfg::kProducerWarp && lane == 0) {
         tma_prefetch_desc(&tmQ);
         tma_prefetch_desc(&tmK);
         tma_prefetch_desc(&tmV);
         tma_prefetch_desc(&tmdO);
+        tma_prefetch_desc(&tmO);
         mbar_init(bar_q, 1);
-        mbar_init(&bar_s_full[0], 1);
-        mbar_init(&bar_s_full[1], 1);
+        mbar_init(bar_q_free, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bar_s_full[i], 1);
+            mbar_init(&bar_ds_full[i], Cfg::kComputeThreads);
+        }
         mbar_init(bar_dp_full, 1);
-        mbar_init(bar_ds_full, Cfg::kComputeThreads);
         mbar_init(bar_dp_free, Cfg::kComputeThreads);
         mbar_init(bar_acc, 1);
+        mbar_init(bar_acc_free, Cfg::kComputeThreads);
+        mbar_init(bar_o_free, Cfg::kComputeThreads);
         for (int s = 0; s < NST; ++s) {
             mbar_init(&bar_kv_full[s], 1);
             mbar_init(&bar_kv_free[s], 1);
         }
         fence_mbar_init();
         grid_dep_wait();  // first global access of this CTA comes next
-        const int failed = *reinterpret_cast<volatile int*>(p.status);
-        *abort_flag = failed;
-        if (!failed) {
-            mbar_arrive_expect_tx(bar_q, 2 * Cfg::kQTileBytes);
-#pragma unroll
-            for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
-                tma_load_4d(sQ + bx * Cfg::kQBoxBytes, &tmQ, bar_q, bx * 64, q0, h, b);
-                tma_load_4d(sdO + bx * Cfg::kQBoxBytes, &tmdO, bar_q, bx * 64, q0, h, b);
-            }
-            const int n_pre = n_kv < NST ? n_kv : NST;
-            for (int j = 0; j < n_pre; ++j) {
-                mbar_arrive_expect_tx(&bar_kv_full[j], 2 * Cfg::kKVTileBytes);
-#pragma unroll
-                for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
-                    tma_load_4d(sK + j * Cfg::kKVTileBytes + bx * Cfg::kKVBoxBytes, &tmK, &bar_kv_full[j], bx * 64,
-                                j * Cfg::kKeys, hk, b);
-                    tma_load_4d(sV + j * Cfg::kKVTileBytes + bx * Cfg::kKVBoxBytes, &tmV, &bar_kv_full[j], bx * 64,
-                                j * Cfg::kKeys, hk, b);
-                }
-            }
-        }
+        *abort_flag = *reinterpret_cast<volatile int*>(p.status);
     }
     if (warp == Cfg::kMmaWarp) {
         tmem_alloc(tmem_slot, Cfg::kTmemCols);
@@ -243,28 +232,45 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    const bool failed_early = (*abort_flag != 0);
-    B200ATTN_STAMP(tid == 0, 301);
 
-    if (failed_early) {
-        // nothing was started; fall through to the teardown
+    if (*abort_flag != 0) {
+        // an earlier CTA already failed: fall through to the teardown
     } else if (warp == Cfg::kProducerWarp) {
-        // ------------------------------------------------------------------ producer (tiles >= NST)
-        for (int j = NST; j < n_kv; ++j) {
-            const int s = j % NST;
-            if (!mbar_wait_warp(&bar_kv_free[s], ((j / NST) - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE))
-                break;
+        // ------------------------------------------------------------------ producer
+        int g = 0;  // tiles issued so far by this CTA (ring position)
+        int n = 0;
+        bool ok = true;
+        for (int id = blockIdx.x; id < n_items && ok; id += gridDim.x, ++n) {
+            const int qt = item_qt(id), h = item_h(id), b = item_b(id), hk = h / p.group, n_kv = item_nkv(id);
+            if (n > 0) ok = mbar_wait_warp(bar_q_free, (n - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
+            if (ok && n > 0) ok = mbar_wait_warp(bar_o_free, (n - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
+            if (!ok) break;
             if (elect_one()) {
-                mbar_arrive_expect_tx(&bar_kv_full[s], 2 * Cfg::kKVTileBytes);
+                mbar_arrive_expect_tx(bar_q, 3 * Cfg::kQTileBytes);
 #pragma unroll
                 for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
-                    tma_load_4d(sK + s * Cfg::kKVTileBytes + bx * Cfg::kKVBoxBytes, &tmK, &bar_kv_full[s], bx * 64,
-                                j * Cfg::kKeys, hk, b);
-                    tma_load_4d(sV + s * Cfg::kKVTileBytes + bx * Cfg::kKVBoxBytes, &tmV, &bar_kv_full[s], bx * 64,
-                                j * Cfg::kKeys, hk, b);
+                    tma_load_4d(sQ + bx * Cfg::kQBoxBytes, &tmQ, bar_q, bx * 64, qt * 128, h, b);
+                    tma_load_4d(sdO + bx * Cfg::kQBoxBytes, &tmdO, bar_q, bx * 64, qt * 128, h, b);
+                    tma_load_4d(sO + bx * Cfg::kQBoxBytes, &tmO, bar_q, bx * 64, qt * 128, h, b);
                 }
             }
             __syncwarp();
+            for (int j = 0; j < n_kv; ++j, ++g) {
+                const int s = g % NST;
+                if (g >= NST) ok = mbar_wait_warp(&bar_kv_free[s], ((g / NST) - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
+                if (!ok) break;
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(&bar_kv_full[s], 2 * Cfg::kKVTileBytes);
+#pragma unroll
+                    for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
+                        tma_load_4d(sK + s * Cfg::kKVTileBytes + bx * Cfg::kKVBoxBytes, &tmK, &bar_kv_full[s], bx * 64,
+                                    j * Cfg::kKeys, hk, b);
+                        tma_load_4d(sV + s * Cfg::kKVTileBytes + bx * Cfg::kKVBoxBytes, &tmV, &bar_kv_full[s], bx * 64,
+                                    j * Cfg::kKeys, hk, b);
+                    }
+                }
+                __syncwarp();
+            }
         }
     } else if (warp == Cfg::kMmaWarp) {
         // ------------------------------------------------------------------ MMA issuer
@@ -272,25 +278,27 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
         const uint64_t q_desc = make_sdesc_sw128(smem_u32(sQ), 16, 1024);
         const uint64_t do_desc = make_sdesc_sw128(smem_u32(sdO), 16, 1024);
-        bool ok = mbar_wait_warp(bar_q, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-        auto issue_s = [&](int j) -> bool {  // S(j) = Q K_j^T into S buffer j & 1
-            const int s = j % NST;
-            if (!mbar_wait_warp(&bar_kv_full[s], (j / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD))
+        // g numbers this CTA's key tiles across all its items: ring stage g % NST, S buffer g & 1
+        auto issue_s = [&](int g) -> bool {  // S(g) = Q K^T
+            const int s = g % NST;
+            if (!mbar_wait_warp(&bar_kv_full[s], (g / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD))
                 return false;
             tc_fence_after_sync();
             const uint64_t k_desc = make_sdesc_sw128(smem_u32(sK + s * Cfg::kKVTileBytes), 16, 1024);
             if (elect_one()) {
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks)
-                    umma_ss(tmem + ((j & 1) ? Cfg::kColS1 : Cfg::kColS0), q_desc + kmajor_step(ks, Cfg::kQBoxBytes),
+                    umma_ss(tmem + ((g & 1) ? Cfg::kColS1 : Cfg::kColS0), q_desc + kmajor_step(ks, Cfg::kQBoxBytes),
                             k_desc + kmajor_step(ks, Cfg::kKVBoxBytes), idesc_s, ks > 0);
-                umma_commit(&bar_s_full[j & 1]);
+                umma_commit(&bar_s_full[g & 1]);
             }
             __syncwarp();
             return true;
         };
-        auto issue_dp = [&](int j) {  // dP(j) = dO V_j^T; tile j's loads have landed (S(j) was issued)
-            const int s = j % NST;
+        // dP(g) = dO V^T; tile g's loads have landed (S(g) was issued).  `last` = last tile of the item:
+        // after it no MMA reads Q or dO of the item any more.
+        auto issue_dp = [&](int g, bool last) {
+            const int s = g % NST;
             const uint64_t v_desc = make_sdesc_sw128(smem_u32(sV + s * Cfg::kKVTileBytes), 16, 1024);
             if (elect_one()) {
 #pragma unroll
@@ -298,155 +306,163 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     umma_ss(tmem + Cfg::kColDP, do_desc + kmajor_step(ks, Cfg::kQBoxBytes),
                             v_desc + kmajor_step(ks, Cfg::kKVBoxBytes), idesc_s, ks > 0);
                 umma_commit(bar_dp_full);
+                if (last) umma_commit(bar_q_free);
             }
             __syncwarp();
         };
-        if (ok) ok = issue_s(0);
-        if (ok) issue_dp(0);
-        if (ok && n_kv > 1) ok = issue_s(1);
-        for (int j = 0; j < n_kv && ok; ++j) {
-            const int s = j % NST;
-            // dP of the next tile as soon as the compute warps have read dP_j into registers (dS_j goes
-            // into S buffer j & 1, so the dP block is free): the MMA round trip then runs under their
-            // arithmetic instead of after it
-            if (j + 1 < n_kv) {
-                ok = mbar_wait_warp(bar_dp_free, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
-                if (!ok) break;
-                tc_fence_after_sync();
-                issue_dp(j + 1);
-            }
-            ok = mbar_wait_warp(bar_ds_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+        int g0 = 0, n = 0;
+        bool ok = true;
+        for (int id = blockIdx.x; id < n_items && ok; id += gridDim.x, ++n) {
+            const int n_kv = item_nkv(id);
+            ok = mbar_wait_warp(bar_q, n & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+            if (ok) ok = issue_s(g0);
+            // the dP block still holds the previous item's last dP until the compute warps have read it
+            if (ok && g0 > 0) ok = mbar_wait_warp(bar_dp_free, (g0 - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
             if (!ok) break;
             tc_fence_after_sync();
-            const uint64_t kmn_desc = make_sdesc_sw128(smem_u32(sK + s * Cfg::kKVTileBytes), Cfg::kKVBoxBytes, 1024);
-            if (elect_one()) {
-                // dQ += dS_j K_j : 64 keys = 4 K steps, dS in the first 32 columns of S buffer j & 1
-#pragma unroll
-                for (int ks = 0; ks < Cfg::kKeys / 16; ++ks) {
-                    // part q keeps its BF16 dS values in the first kPartCols / 2 columns of its own range
-                    constexpr int kStepsPerPart = Cfg::kPartCols / 16;
-                    const uint32_t a_col = ((j & 1) ? Cfg::kColS1 : Cfg::kColS0) + (ks / kStepsPerPart) * Cfg::kPartCols +
-                                           (ks % kStepsPerPart) * 8;
-                    umma_ts(tmem + Cfg::kColAcc, tmem + a_col, kmn_desc + uint64_t(ks * 128), idesc_acc,
-                            (j > 0) || (ks > 0));
+            issue_dp(g0, n_kv == 1);
+            if (n_kv > 1) ok = issue_s(g0 + 1);
+            for (int j = 0; j < n_kv && ok; ++j) {
+                const int g = g0 + j;
+                const int s = g % NST;
+                if (j + 1 < n_kv) {
+                    // next dP as soon as this one has been read into registers
+                    ok = mbar_wait_warp(bar_dp_free, g & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_dp(g + 1, j + 2 == n_kv);
                 }
-                umma_commit(&bar_kv_free[s]);
+                ok = mbar_wait_warp(&bar_ds_full[g & 1], uint32_t(g >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+                if (!ok) break;
+                // the accumulator still belongs to the previous item's epilogue until it has been read
+                if (j == 0 && n > 0) {
+                    ok = mbar_wait_warp(bar_acc_free, (n - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+                    if (!ok) break;
+                }
+                tc_fence_after_sync();
+                const uint64_t kmn_desc = make_sdesc_sw128(smem_u32(sK + s * Cfg::kKVTileBytes), Cfg::kKVBoxBytes, 1024);
+                if (elect_one()) {
+                    // dQ += dS K : 64 keys = 4 K steps; part q keeps its BF16 dS in the first 16 columns of its range
+#pragma unroll
+                    for (int ks = 0; ks < Cfg::kKeys / 16; ++ks) {
+                        constexpr int kStepsPerPart = Cfg::kPartCols / 16;
+                        const uint32_t a_col = ((g & 1) ? Cfg::kColS1 : Cfg::kColS0) + (ks / kStepsPerPart) * Cfg::kPartCols +
+                                               (ks % kStepsPerPart) * 8;
+                        umma_ts(tmem + Cfg::kColAcc, tmem + a_col, kmn_desc + uint64_t(ks * 128), idesc_acc,
+                                (j > 0) || (ks > 0));
+                    }
+                    umma_commit(&bar_kv_free[s]);
+                    if (j + 1 == n_kv) umma_commit(bar_acc);
+                }
+                __syncwarp();
+                if (j + 2 < n_kv) ok = issue_s(g + 2);
             }
-            __syncwarp();
-            if (j + 2 < n_kv) ok = issue_s(j + 2);
+            g0 += n_kv;
         }
-        if (elect_one()) umma_commit(bar_acc);
-        __syncwarp();
+        // drain: nothing may be in flight when TMEM is freed
+        if (ok && n > 0) mbar_wait_warp(bar_acc, (n - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
     } else {
         // ------------------------------------------------------------------ compute
         const int w4 = warp & 3, part = warp >> 2;
         const int row = w4 * 32 + lane;  // query row in the tile == TMEM lane
         const uint32_t lane_base = uint32_t(w4 * 32) << 16;
         const int c0 = part * Cfg::kPartCols;  // first key column of this thread's part
-        const bool in_range = q0 + row < p.T;
-        const size_t vrow = (size_t(b) * p.Hq + h) * p.Tpad + q0 + row;
-        const size_t qoff = size_t(b) * p.q_sb + size_t(h) * p.q_sh + size_t(q0 + row) * p.q_st;
-        // Preprocess for the warp's 32 rows, under the latency of the first loads: D = rowsum(O * dO).
-        // The warp reads whole rows with coalesced 16-byte loads (D/8 lanes per row), reduces with
-        // shuffles and hands every row's sum to the lane that owns the row.
-        float lse2 = INFINITY;  // exp2(x - inf) = 0: padding query rows contribute nothing
-        float dv = 0.f;
-        {
-            constexpr int LPR = D / 8;     // lanes per row
-            constexpr int RPP = 32 / LPR;  // rows per pass
-            const size_t tile_off = size_t(b) * p.q_sb + size_t(h) * p.q_sh;
-#pragma unroll
-            for (int i = 0; i < LPR; ++i) {
-                const int r = q0 + w4 * 32 + i * RPP + lane / LPR;  // global query row read by this lane
-                float acc = 0.f;
-                if (r < p.T) {
-                    const size_t off = tile_off + size_t(r) * p.q_st + (lane % LPR) * 8;
-                    const uint4 a = *reinterpret_cast<const uint4*>(p.o + off);
-                    const uint4 g = *reinterpret_cast<const uint4*>(p.dout + off);
-                    const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
-                    const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        acc = fmaf(__uint_as_float(aw[e] << 16), __uint_as_float(gw[e] << 16), acc);
-                        acc = fmaf(__uint_as_float(aw[e] & 0xffff0000u), __uint_as_float(gw[e] & 0xffff0000u), acc);
-                    }
-                }
-#pragma unroll
-                for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-                const float v = __shfl_sync(0xffffffffu, acc, (lane % RPP) * LPR);
-                if (lane / RPP == i) dv = v;
-            }
-            if (in_range) lse2 = p.lse[(size_t(b) * p.Hq + h) * p.T + q0 + row] * 1.4426950408889634f;
-        }
-        if (part == 0) {
-            p.lse2_w[vrow] = lse2;
-            p.dvec_w[vrow] = dv;
-        }
-        B200ATTN_STAMP(tid == 0, 302);
+        int g0 = 0, n = 0;
         bool ok = true;
-        for (int j = 0; j < n_kv; ++j) {
-            const uint32_t t_s = tmem + lane_base + ((j & 1) ? Cfg::kColS1 : Cfg::kColS0) + c0;
-            ok = mbar_wait_warp(&bar_s_full[j & 1], uint32_t(j >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+        for (int id = blockIdx.x; id < n_items && ok; id += gridDim.x, ++n) {
+            const int qt = item_qt(id), h = item_h(id), b = item_b(id), n_kv = item_nkv(id);
+            const int q0 = qt * 128;
+            // preprocess of this row from the tiles in shared memory: D = rowsum(O * dO); L * log2(e)
+            const bool in_range = q0 + row < p.T;
+            const float lse2 = in_range ? p.lse[(size_t(b) * p.Hq + h) * p.T + q0 + row] * 1.4426950408889634f
+                                        : INFINITY;  // exp2(x - inf) = 0: padding query rows contribute nothing
+            ok = mbar_wait_warp(bar_q, n & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
             if (!ok) break;
-            B200ATTN_STAMP(tid == 0, 308 + 4 * j);
-            tc_fence_after_sync();
-            // phase A: P from S
-            float pr[32];
-            {
-                uint32_t sv[32];
-                tmem_ld_x32(t_s, sv);
-                tmem_wait_ld();
+            float dv = 0.f;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) pr[i] = ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse2));
-            }
-            const int kbase = j * Cfg::kKeys;
-            if (kbase + Cfg::kKeys - 1 > q0) {
-                const int lim = q0 + row - kbase - c0;  // columns i <= lim of this part are visible
+            for (int c = 0; c < D / 8; ++c) {
+                const uint32_t off = (c >> 3) * Cfg::kQBoxBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4);
+                const uint4 a = *reinterpret_cast<const uint4*>(sO + off);
+                const uint4 gq = *reinterpret_cast<const uint4*>(sdO + off);
+                const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+                const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w};
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (i > lim) pr[i] = 0.f;
+                for (int e = 0; e < 4; ++e) {
+                    dv = fmaf(__uint_as_float(aw[e] << 16), __uint_as_float(gw[e] << 16), dv);
+                    dv = fmaf(__uint_as_float(aw[e] & 0xffff0000u), __uint_as_float(gw[e] & 0xffff0000u), dv);
+                }
             }
-            ok = mbar_wait_warp(bar_dp_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
-            if (!ok) break;
-            B200ATTN_STAMP(tid == 0, 309 + 4 * j);
-            tc_fence_after_sync();
-            // phase B: dS = P (dP - D), written as BF16 over the part's first 16 columns of the S buffer
-            {
-                uint32_t dp[32], pk[16];
-                tmem_ld_x32(tmem + lane_base + Cfg::kColDP + c0, dp);
-                tmem_wait_ld();
+            mbar_arrive(bar_o_free);  // the O tile may be overwritten by the next item's load
+            if (part == 0) {
+                const size_t vrow = (size_t(b) * p.Hq + h) * p.Tpad + q0 + row;
+                p.lse2_w[vrow] = lse2;
+                p.dvec_w[vrow] = in_range ? dv : 0.f;
+            }
+            for (int j = 0; j < n_kv; ++j) {
+                const int g = g0 + j;
+                const uint32_t t_s = tmem + lane_base + ((g & 1) ? Cfg::kColS1 : Cfg::kColS0) + c0;
+                ok = mbar_wait_warp(&bar_s_full[g & 1], uint32_t(g >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+                if (!ok) break;
+                tc_fence_after_sync();
+                // phase A: P from S
+                float pr[32];
+                {
+                    uint32_t sv[32];
+                    tmem_ld_x32(t_s, sv);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) pr[i] = ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse2));
+                }
+                const int kbase = j * Cfg::kKeys;
+                if (kbase + Cfg::kKeys - 1 > q0) {
+                    const int lim = q0 + row - kbase - c0;  // columns i <= lim of this part are visible
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (i > lim) pr[i] = 0.f;
+                }
+                ok = mbar_wait_warp(bar_dp_full, g & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+                if (!ok) break;
+                tc_fence_after_sync();
+                // phase B: dS = P (dP - D), written as BF16 over the part's first 16 columns of the S buffer
+                {
+                    uint32_t dp[32], pk[16];
+                    tmem_ld_x32(tmem + lane_base + Cfg::kColDP + c0, dp);
+                    tmem_wait_ld();
+                    tc_fence_before_sync();
+                    mbar_arrive(bar_dp_free);  // dP is in registers: the next dP may overwrite the block
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        pk[i] = pack_bf16x2(pr[2 * i] * (__uint_as_float(dp[2 * i]) - dv),
+                                            pr[2 * i + 1] * (__uint_as_float(dp[2 * i + 1]) - dv));
+                    tmem_st_x16(t_s, pk);
+                }
+                tmem_wait_st();
                 tc_fence_before_sync();
-                mbar_arrive(bar_dp_free);  // dP_j is in registers: the next dP may overwrite the block
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    pk[i] = pack_bf16x2(pr[2 * i] * (__uint_as_float(dp[2 * i]) - dv),
-                                        pr[2 * i + 1] * (__uint_as_float(dp[2 * i + 1]) - dv));
-                tmem_st_x16(t_s, pk);
+                mbar_arrive(&bar_ds_full[g & 1]);
             }
-            tmem_wait_st();
-            tc_fence_before_sync();
-            mbar_arrive(bar_ds_full);
-            B200ATTN_STAMP(tid == 0, 310 + 4 * j);
-        }
-        if (ok) ok = mbar_wait(bar_acc, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
-        ok = __all_sync(0xffffffffu, ok);
-        B200ATTN_STAMP(tid == 0, 303);
-        if (ok) {
+            if (!ok) break;
+            g0 += n_kv;
+            // epilogue of the item: dQ rows (times scale) -> BF16 -> global memory; each part writes D / 2 columns
+            ok = mbar_wait_warp(bar_acc, n & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+            if (!ok) break;
             tc_fence_after_sync();
-            uint16_t* dqrow = p.dq + qoff + part * (D / Cfg::kParts);
+            constexpr int kCols = D / Cfg::kParts;
+            uint32_t v[kCols];
 #pragma unroll
-            for (int c = 0; c < D / Cfg::kParts / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld_x32(tmem + lane_base + Cfg::kColAcc + part * (D / Cfg::kParts) + c * 32, v);
-                tmem_wait_ld();
+            for (int c = 0; c < kCols / 32; ++c) tmem_ld_x32(tmem + lane_base + Cfg::kColAcc + part * kCols + c * 32, &v[c * 32]);
+            tmem_wait_ld();
+            tc_fence_before_sync();
+            mbar_arrive(bar_acc_free);  // the MMA warp may start the next item's accumulation
+            if (q0 + row < p.T) {
+                uint16_t* dqrow = p.dq + size_t(b) * p.q_sb + size_t(h) * p.q_sh + size_t(q0 + row) * p.q_st + part * kCols;
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
+                for (int gq = 0; gq < kCols / 8; ++gq) {
                     uint4 w;
-                    w.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]) * p.scale, __uint_as_float(v[g * 8 + 1]) * p.scale);
-                    w.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * p.scale, __uint_as_float(v[g * 8 + 3]) * p.scale);
-                    w.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * p.scale, __uint_as_float(v[g * 8 + 5]) * p.scale);
-                    w.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * p.scale, __uint_as_float(v[g * 8 + 7]) * p.scale);
-                    if (in_range) *reinterpret_cast<uint4*>(dqrow + c * 32 + g * 8) = w;
+                    w.x = pack_bf16x2(__uint_as_float(v[gq * 8 + 0]) * p.scale, __uint_as_float(v[gq * 8 + 1]) * p.scale);
+                    w.y = pack_bf16x2(__uint_as_float(v[gq * 8 + 2]) * p.scale, __uint_as_float(v[gq * 8 + 3]) * p.scale);
+                    w.z = pack_bf16x2(__uint_as_float(v[gq * 8 + 4]) * p.scale, __uint_as_float(v[gq * 8 + 5]) * p.scale);
+                    w.w = pack_bf16x2(__uint_as_float(v[gq * 8 + 6]) * p.scale, __uint_as_float(v[gq * 8 + 7]) * p.scale);
+                    *reinterpret_cast<uint4*>(dqrow + gq * 8) = w;
                 }
             }
         }
@@ -458,8 +474,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tc_fence_after_sync();
         tmem_dealloc(tmem, Cfg::kTmemCols);
     }
-    B200ATTN_STAMP(tid == 0, 304);
-    B200ATTN_TRACE_END();
 }
 
 // ---------------------------------------------------------------------------------------

@@ -45,6 +45,19 @@ int* status_ptr(int* err) {
     return g_status_ptr[dev];
 }
 
+// SM count of the current device (cached per device).
+int sm_count() {
+    static int cached[kMaxDevices] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 struct Strides {
     long long t, h, b;  // element strides
 };
@@ -175,8 +188,8 @@ inline void record_bwd_event(int i, cudaStream_t st) {
 
 template <int D>
 int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk64, const CUtensorMap& tv64, const CUtensorMap& tk,
-               const CUtensorMap& tv, const CUtensorMap& tdo, const CUtensorMap& tdq, const CUtensorMap& tdk,
-               const CUtensorMap& tdv, const BwdParams& p, cudaStream_t st) {
+               const CUtensorMap& tv, const CUtensorMap& tdo, const CUtensorMap& to, const CUtensorMap& tdq,
+               const CUtensorMap& tdk, const CUtensorMap& tdv, const BwdParams& p, cudaStream_t st) {
     static bool dq_set[kMaxDevices] = {false}, dkdv_set[kMaxDevices] = {false};
     // D = 64: 64-key tiles, two CTAs per SM.  D = 128: 128-key tiles, one CTA per SM (tensor-pipe bound).
     constexpr bool kWide = (D == 128);
@@ -187,11 +200,17 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk64, const CUtensorMap
     if (rc) return rc;
     record_bwd_event(0, st);
     // the dQ pass also writes the two per-row vectors the dK/dV pass reads
-    const unsigned dq_grid = (unsigned)(p.n_tiles * p.Hq * p.B);
+    const unsigned dq_items = (unsigned)(p.n_tiles * p.Hq * p.B);
+    // the D = 64 kernel is persistent: two CTAs per SM walk the item list
+    unsigned dq_grid = dq_items;
+    if (!kWide) {
+        const unsigned resident = 2u * (unsigned)sm_count();
+        if (dq_grid > resident) dq_grid = resident;
+    }
     const cudaError_t e = kWide ? launch_pdl(attn_bwd_dq_wide_kernel<D>, dq_grid, 320, DqWideCfg<D>::kSmemBytes, st, tq, tk,
                                              tv, tdo, tdq, p)
                                 : launch_pdl(attn_bwd_dq_kernel<D>, dq_grid, DqCfg<D>::kThreads, DqCfg<D>::kSmemBytes, st, tq, tk64, tv64,
-                                             tdo, p);
+                                             tdo, to, p);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return B200ATTN_ERR_CUDA;
@@ -238,13 +257,14 @@ extern "C" int b200attn_bwd(const void* q, const void* k, const void* v, const v
     int* status = status_ptr(&rc);
     if (!status) return rc;
     const Strides sq = strides_for(layout, Hq, T, D), sk = strides_for(layout, Hkv, T, D);
-    CUtensorMap tq, tk, tv, tk64, tv64, tdo, tdq, tdk, tdv;
+    CUtensorMap tq, tk, tv, tk64, tv64, tdo, to, tdq, tdk, tdv;
     if (!make_tmap_bf16_4d(&tq, q, D, T, Hq, B, sq.t, sq.h, sq.b, 128) ||
         !make_tmap_bf16_4d(&tk, k, D, T, Hkv, B, sk.t, sk.h, sk.b, 128) ||
         !make_tmap_bf16_4d(&tv, v, D, T, Hkv, B, sk.t, sk.h, sk.b, 128) ||
         !make_tmap_bf16_4d(&tk64, k, D, T, Hkv, B, sk.t, sk.h, sk.b, 64) ||
         !make_tmap_bf16_4d(&tv64, v, D, T, Hkv, B, sk.t, sk.h, sk.b, 64) ||
         !make_tmap_bf16_4d(&tdo, dout, D, T, Hq, B, sq.t, sq.h, sq.b, 128) ||
+        !make_tmap_bf16_4d(&to, o, D, T, Hq, B, sq.t, sq.h, sq.b, 128) ||
         !make_tmap_bf16_4d(&tdq, dq, D, T, Hq, B, sq.t, sq.h, sq.b, 128) ||
         !make_tmap_bf16_4d(&tdk, dk, D, T, Hkv, B, sk.t, sk.h, sk.b, 128) ||
         !make_tmap_bf16_4d(&tdv, dv, D, T, Hkv, B, sk.t, sk.h, sk.b, 128))
@@ -274,8 +294,8 @@ extern "C" int b200attn_bwd(const void* q, const void* k, const void* v, const v
     p.q_sb = sq.b;
     p.status = status;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return D == 64 ? launch_bwd<64>(tq, tk64, tv64, tk, tv, tdo, tdq, tdk, tdv, p, st)
-                   : launch_bwd<128>(tq, tk64, tv64, tk, tv, tdo, tdq, tdk, tdv, p, st);
+    return D == 64 ? launch_bwd<64>(tq, tk64, tv64, tk, tv, tdo, to, tdq, tdk, tdv, p, st)
+                   : launch_bwd<128>(tq, tk64, tv64, tk, tv, tdo, to, tdq, tdk, tdv, p, st);
 }
 
 // ---------------------------------------------------------------------------------------

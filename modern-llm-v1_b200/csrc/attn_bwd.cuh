@@ -240,7 +240,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         int g = 0;  // tiles issued so far by this CTA (ring position)
         int n = 0;
         bool ok = true;
-        for (int id = blockIdx.x; id < n_items && ok; id += gridDim.x, ++n) {
+        for (int id; ok && (id = persistent_item(n, int(blockIdx.x), int(gridDim.x))) < n_items; ++n) {
             const int qt = item_qt(id), h = item_h(id), b = item_b(id), hk = h / p.group, n_kv = item_nkv(id);
             if (n > 0) ok = mbar_wait_warp(bar_q_free, (n - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
             if (ok && n > 0) ok = mbar_wait_warp(bar_o_free, (n - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
@@ -312,7 +312,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         };
         int g0 = 0, n = 0;
         bool ok = true;
-        for (int id = blockIdx.x; id < n_items && ok; id += gridDim.x, ++n) {
+        for (int id; ok && (id = persistent_item(n, int(blockIdx.x), int(gridDim.x))) < n_items; ++n) {
             const int n_kv = item_nkv(id);
             ok = mbar_wait_warp(bar_q, n & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
             if (ok) ok = issue_s(g0);
@@ -369,7 +369,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const int c0 = part * Cfg::kPartCols;  // first key column of this thread's part
         int g0 = 0, n = 0;
         bool ok = true;
-        for (int id = blockIdx.x; id < n_items && ok; id += gridDim.x, ++n) {
+        for (int id; ok && (id = persistent_item(n, int(blockIdx.x), int(gridDim.x))) < n_items; ++n) {
             const int qt = item_qt(id), h = item_h(id), b = item_b(id), n_kv = item_nkv(id);
             const int q0 = qt * 128;
             // preprocess of this row from the tiles in shared memory: D = rowsum(O * dO); L * log2(e)

@@ -3,10 +3,13 @@
 // reference's flash_attn_forward (llm/src/model/flash_attn.h:25-28,
 // llm/src/model/flash_attn.cu:28-131), computed tile-wise on the tensor cores.
 //
-// One CTA owns one 128-row query tile of one (batch, query head) and walks 64-key tiles of
-// K/V up to the diagonal (tiles above it are never loaded).  GQA is an index: the K/V tensor
-// maps are addressed with h_kv = h_q / group (llm/src/model/attention.cu:406), nothing is
-// replicated.
+// Persistent CTAs, two per SM.  A CTA walks a static list of work items (item = one 128-row
+// query tile of one (batch, query head); items are ordered heaviest first and dealt
+// round-robin) and, per item, the 64-key tiles of K/V up to the diagonal (tiles above it are
+// never loaded).  Every pipeline keeps running across item boundaries: the K/V ring prefetches
+// the next item's tiles and the MMA warp issues the next item's first Q K^T products while the
+// softmax warps write the previous item's output rows.  GQA is an index: the K/V tensor maps are
+// addressed with h_kv = h_q / group (llm/src/model/attention.cu:406), nothing is replicated.
 //
 // Roles (256 threads = two warpgroups, so that setmaxnreg can move registers from the
 // second group to the first):
@@ -16,9 +19,8 @@
 //   warps 6-7  idle (they only donate registers)
 // TMEM (256 columns): S buffer 0 [0,64), S buffer 1 [64,128) as FP32, each re-used as P
 //   (BF16 pairs, 32 columns); O accumulator FP32 [128,128+D).
-// With two S buffers the product Q K^T of tile j+1 is issued before the softmax of tile j
-// ends, and P V of tile j runs under the softmax of tile j+1.  Two CTAs are resident per
-// SM, so prologue and epilogue of one CTA hide under the main loop of the other.
+// With two S buffers the product Q K^T of tile g+1 is issued before the softmax of tile g
+// ends, and P V of tile g runs under the softmax of tile g+1.
 #pragma once
 
 #include "ptx.cuh"
@@ -40,13 +42,14 @@ template <int D>
 struct FwdCfg {
     static constexpr int kKeys = 64;                  // keys per K/V tile
     static constexpr int kStages = (D == 64) ? 4 : 2;
+    static constexpr int kQBufs = (D == 64) ? 2 : 1;  // Q tiles in shared memory (the next item's Q is prefetched)
     static constexpr int kQTileBytes = 128 * D * 2;
-    static constexpr int kQBoxBytes = 128 * 64 * 2;   // Q/O TMA box: 128 rows x 64 bf16
+    static constexpr int kQBoxBytes = 128 * 64 * 2;   // Q TMA box: 128 rows x 64 bf16
     static constexpr int kKVTileBytes = kKeys * D * 2;
     static constexpr int kKVBoxBytes = kKeys * 64 * 2;  // K/V TMA box: 64 rows x 64 bf16
     static constexpr int kBoxes = D / 64;
     static constexpr int kBarBytes = 256;
-    static constexpr int kSmemBytes = kQTileBytes + 2 * kStages * kKVTileBytes + kBarBytes + 1024;
+    static constexpr int kSmemBytes = kQBufs * kQTileBytes + 2 * kStages * kKVTileBytes + kBarBytes + 1024;
     static constexpr int kTmemCols = 256;
     static constexpr int kColS0 = 0;
     static constexpr int kColS1 = 64;
@@ -63,56 +66,58 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
     using Cfg = FwdCfg<D>;
     constexpr int NST = Cfg::kStages;
+    constexpr int NQB = Cfg::kQBufs;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;
-    uint8_t* sK = sQ + Cfg::kQTileBytes;
+    uint8_t* sK = sQ + NQB * Cfg::kQTileBytes;
     uint8_t* sV = sK + NST * Cfg::kKVTileBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sV + NST * Cfg::kKVTileBytes);
-    uint64_t* bar_q = bars + 0;
-    uint64_t* bar_s_full = bars + 1;   // [2]
-    uint64_t* bar_p_full = bars + 3;   // [2]
-    uint64_t* bar_pv_done = bars + 5;
-    uint64_t* bar_drain = bars + 6;
-    uint64_t* bar_k_full = bars + 7;            // [NST]
-    uint64_t* bar_k_free = bars + 7 + NST;      // [NST]
-    uint64_t* bar_v_full = bars + 7 + 2 * NST;  // [NST]
-    uint64_t* bar_v_free = bars + 7 + 3 * NST;  // [NST]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 25);
+    uint64_t* bar_q = bars + 0;        // [2] per Q buffer: Q of an item has landed              (phase: item / NQB)
+    uint64_t* bar_q_free = bars + 2;   // [2] per Q buffer: every Q K^T product of the item done (phase: item / NQB)
+    uint64_t* bar_s_full = bars + 4;   // [2] per S buffer                                        (phase: tile / 2)
+    uint64_t* bar_p_full = bars + 6;   // [2] per S buffer: P written, O rescaled                 (phase: tile / 2)
+    uint64_t* bar_pv_done = bars + 8;  // P V of a tile is complete                               (phase: tile)
+    uint64_t* bar_o_done = bars + 9;   // O of an item is complete                                (phase: item)
+    uint64_t* bar_o_free = bars + 10;  // O has been read by the epilogue                         (phase: item)
+    uint64_t* bar_k_full = bars + 11;            // [NST]
+    uint64_t* bar_k_free = bars + 11 + NST;      // [NST]
+    uint64_t* bar_v_full = bars + 11 + 2 * NST;  // [NST]
+    uint64_t* bar_v_free = bars + 11 + 3 * NST;  // [NST]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 28);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 29);
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
 
-    // 1-D grid ordered by work: all CTAs of the heaviest query tile (most key tiles) come first.
+    // item id -> (query tile, head, batch); ids are ordered by work, heaviest query tile first, and dealt
+    // to the CTAs in rounds of alternating direction so that every CTA gets a similar amount of work
     const int n_bh = p.B * p.Hq;
-    const int qt = p.n_qtiles - 1 - int(blockIdx.x) / n_bh;
-    const int bh = int(blockIdx.x) % n_bh;
-    const int h = bh % p.Hq;
-    const int b = bh / p.Hq;
-    const int hk = h / p.group;
-    const int q0 = qt * 128;
-    const int k_end = min(p.T, q0 + 128);                  // keys [0, k_end) are visible to this tile
-    const int n_kv = (k_end + Cfg::kKeys - 1) / Cfg::kKeys; // 64-key tiles to walk
+    const int n_items = p.n_qtiles * n_bh;
+    auto item_id = [&](int n) { return persistent_item(n, int(blockIdx.x), int(gridDim.x)); };
+    auto item_qt = [&](int id) { return p.n_qtiles - 1 - id / n_bh; };
+    auto item_h = [&](int id) { return (id % n_bh) % p.Hq; };
+    auto item_b = [&](int id) { return (id % n_bh) / p.Hq; };
+    auto item_nkv = [&](int id) { return (min(p.T, item_qt(id) * 128 + 128) + Cfg::kKeys - 1) / Cfg::kKeys; };
 
-    B200ATTN_STAMP(tid == 0, 0);
     B200ATTN_TRACE_BEGIN();
-    // Set-up with one CTA-wide barrier: one lane of the producer warp reads the device status word
-    // (an earlier CTA may already have failed), initialises every mbarrier and immediately starts
-    // the first loads, while the MMA warp allocates TMEM.
+    // Set-up with one CTA-wide barrier: one lane of the producer warp initialises every mbarrier while
+    // the MMA warp allocates TMEM; nothing touches global memory before grid_dep_wait().
     grid_dep_launch();
     if (warp == 4 && lane == 0) {
         tma_prefetch_desc(&tmQ);
         tma_prefetch_desc(&tmK);
         tma_prefetch_desc(&tmV);
-        mbar_init(bar_q, 1);
-        mbar_init(&bar_s_full[0], 1);
-        mbar_init(&bar_s_full[1], 1);
-        mbar_init(&bar_p_full[0], 128);
-        mbar_init(&bar_p_full[1], 128);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bar_q[i], 1);
+            mbar_init(&bar_q_free[i], 1);
+            mbar_init(&bar_s_full[i], 1);
+            mbar_init(&bar_p_full[i], 128);
+        }
         mbar_init(bar_pv_done, 1);
-        mbar_init(bar_drain, 1);
+        mbar_init(bar_o_done, 1);
+        mbar_init(bar_o_free, 128);
         for (int s = 0; s < NST; ++s) {
             mbar_init(&bar_k_full[s], 1);
             mbar_init(&bar_k_free[s], 1);
@@ -121,27 +126,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         fence_mbar_init();
         grid_dep_wait();  // first global access of this CTA comes next
-        const int failed = *reinterpret_cast<volatile int*>(p.status);
-        *abort_flag = failed;
-        if (!failed) {
-            mbar_arrive_expect_tx(bar_q, Cfg::kQTileBytes);
-#pragma unroll
-            for (int bx = 0; bx < Cfg::kBoxes; ++bx)
-                tma_load_4d(sQ + bx * Cfg::kQBoxBytes, &tmQ, bar_q, bx * 64, q0, h, b);
-            const int n_pre = n_kv < NST ? n_kv : NST;
-            for (int j = 0; j < n_pre; ++j) {
-                mbar_arrive_expect_tx(&bar_k_full[j], Cfg::kKVTileBytes);
-#pragma unroll
-                for (int bx = 0; bx < Cfg::kBoxes; ++bx)
-                    tma_load_4d(sK + j * Cfg::kKVTileBytes + bx * Cfg::kKVBoxBytes, &tmK, &bar_k_full[j], bx * 64,
-                                j * Cfg::kKeys, hk, b);
-                mbar_arrive_expect_tx(&bar_v_full[j], Cfg::kKVTileBytes);
-#pragma unroll
-                for (int bx = 0; bx < Cfg::kBoxes; ++bx)
-                    tma_load_4d(sV + j * Cfg::kKVTileBytes + bx * Cfg::kKVBoxBytes, &tmV, &bar_v_full[j], bx * 64,
-                                j * Cfg::kKeys, hk, b);
-            }
-        }
+        *abort_flag = *reinterpret_cast<volatile int*>(p.status);
     }
     if (warp == 5) {
         tmem_alloc(tmem_slot, Cfg::kTmemCols);
@@ -152,206 +137,268 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    const bool failed_early = (*abort_flag != 0);
-    B200ATTN_STAMP(tid == 0, 1);
 
-    if (failed_early) {
-        // nothing was started; fall through to the teardown
-    } else
-    if (warp >= 6) {
+    if (*abort_flag != 0) {
+        // an earlier CTA already failed: fall through to the teardown
+    } else if (warp >= 6) {
         reg_dealloc<88>();  // idle warps
     } else if (warp == 4) {
         // ------------------------------------------------------------------ producer
-        // All 32 lanes run the loop; one elected lane issues the copies.
         reg_dealloc<88>();
-        for (int j = NST; j < n_kv; ++j) {  // tiles 0..NST-1 were issued during set-up
-            const int s = j % NST;
-            const uint32_t use = uint32_t(j / NST);
-            if (!mbar_wait_warp(&bar_k_free[s], (use - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE)) break;
+        int g = 0, n = 0;  // g: key tiles issued so far by this CTA (ring position)
+        bool ok = true;
+        for (int id; ok && (id = item_id(n)) < n_items; ++n) {
+            const int qt = item_qt(id), h = item_h(id), b = item_b(id), hk = h / p.group, n_kv = item_nkv(id);
+            const int qb = n % NQB;
+            if (n >= NQB)
+                ok = mbar_wait_warp(&bar_q_free[qb], uint32_t(n / NQB - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
+            if (!ok) break;
             if (elect_one()) {
-                mbar_arrive_expect_tx(&bar_k_full[s], Cfg::kKVTileBytes);
+                mbar_arrive_expect_tx(&bar_q[qb], Cfg::kQTileBytes);
 #pragma unroll
                 for (int bx = 0; bx < Cfg::kBoxes; ++bx)
-                    tma_load_4d(sK + s * Cfg::kKVTileBytes + bx * Cfg::kKVBoxBytes, &tmK, &bar_k_full[s], bx * 64,
-                                j * Cfg::kKeys, hk, b);
+                    tma_load_4d(sQ + qb * Cfg::kQTileBytes + bx * Cfg::kQBoxBytes, &tmQ, &bar_q[qb], bx * 64, qt * 128, h, b);
             }
             __syncwarp();
-            if (!mbar_wait_warp(&bar_v_free[s], (use - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE)) break;
-            if (elect_one()) {
-                mbar_arrive_expect_tx(&bar_v_full[s], Cfg::kKVTileBytes);
+            for (int j = 0; j < n_kv; ++j, ++g) {
+                const int s = g % NST;
+                const uint32_t use = uint32_t(g / NST);
+                if (g >= NST) ok = mbar_wait_warp(&bar_k_free[s], (use - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
+                if (!ok) break;
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(&bar_k_full[s], Cfg::kKVTileBytes);
 #pragma unroll
-                for (int bx = 0; bx < Cfg::kBoxes; ++bx)
-                    tma_load_4d(sV + s * Cfg::kKVTileBytes + bx * Cfg::kKVBoxBytes, &tmV, &bar_v_full[s], bx * 64,
-                                j * Cfg::kKeys, hk, b);
+                    for (int bx = 0; bx < Cfg::kBoxes; ++bx)
+                        tma_load_4d(sK + s * Cfg::kKVTileBytes + bx * Cfg::kKVBoxBytes, &tmK, &bar_k_full[s], bx * 64,
+                                    j * Cfg::kKeys, hk, b);
+                }
+                __syncwarp();
+                if (g >= NST) ok = mbar_wait_warp(&bar_v_free[s], (use - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
+                if (!ok) break;
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(&bar_v_full[s], Cfg::kKVTileBytes);
+#pragma unroll
+                    for (int bx = 0; bx < Cfg::kBoxes; ++bx)
+                        tma_load_4d(sV + s * Cfg::kKVTileBytes + bx * Cfg::kKVBoxBytes, &tmV, &bar_v_full[s], bx * 64,
+                                    j * Cfg::kKeys, hk, b);
+                }
+                __syncwarp();
             }
-            __syncwarp();
         }
     } else if (warp == 5) {
         // ------------------------------------------------------------------ MMA issuer
-        // All 32 lanes run the loop; one elected lane issues.
         reg_dealloc<88>();
         constexpr uint32_t idesc_s = make_idesc_bf16(128, Cfg::kKeys, 0, 0);
         constexpr uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);
-        const uint64_t q_desc = make_sdesc_sw128(smem_u32(sQ), 16, 1024);
-        bool ok = mbar_wait_warp(bar_q, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-        // S(j) = Q K_j^T into S buffer j & 1
-        auto issue_s = [&](int j) -> bool {
-            const int s = j % NST;
-            if (!mbar_wait_warp(&bar_k_full[s], uint32_t(j / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD))
-                return false;
+        // This CTA's key tiles are numbered g = 0, 1, ... across all its items: ring stage g % NST,
+        // S buffer g & 1.  Two cursors walk that sequence: `sc` for the products Q K^T, which runs
+        // two tiles ahead of `pc` for the products P V, also across an item boundary.
+        struct Cursor {
+            int id, n, j, n_kv, g;  // item id, items before it on this CTA, tile in item, tiles of item, global tile
+        };
+        Cursor sc{item_id(0), 0, 0, 0, 0};
+        if (sc.id < n_items) sc.n_kv = item_nkv(sc.id);
+        bool ok = true;
+        auto issue_next_s = [&]() {
+            if (sc.id >= n_items) return;
+            const int s = sc.g % NST, qb = sc.n % NQB;
+            if (sc.j == 0) ok = mbar_wait_warp(&bar_q[qb], uint32_t(sc.n / NQB) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+            if (ok) ok = mbar_wait_warp(&bar_k_full[s], uint32_t(sc.g / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+            if (!ok) return;
             tc_fence_after_sync();
+            const uint64_t q_desc = make_sdesc_sw128(smem_u32(sQ + qb * Cfg::kQTileBytes), 16, 1024);
             const uint64_t k_desc = make_sdesc_sw128(smem_u32(sK + s * Cfg::kKVTileBytes), 16, 1024);
+            const bool last = sc.j + 1 == sc.n_kv;  // no later MMA reads this item's Q
             if (elect_one()) {
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks)
-                    umma_ss(tmem + ((j & 1) ? Cfg::kColS1 : Cfg::kColS0), q_desc + kmajor_step(ks, Cfg::kQBoxBytes),
+                    umma_ss(tmem + ((sc.g & 1) ? Cfg::kColS1 : Cfg::kColS0), q_desc + kmajor_step(ks, Cfg::kQBoxBytes),
                             k_desc + kmajor_step(ks, Cfg::kKVBoxBytes), idesc_s, ks > 0);
-                umma_commit(&bar_s_full[j & 1]);
+                umma_commit(&bar_s_full[sc.g & 1]);
                 umma_commit(&bar_k_free[s]);
+                if (last) umma_commit(&bar_q_free[qb]);
             }
             __syncwarp();
-            return true;
+            ++sc.g;
+            if (++sc.j == sc.n_kv) {
+                sc.id = item_id(++sc.n);
+                sc.j = 0;
+                sc.n_kv = sc.id < n_items ? item_nkv(sc.id) : 0;
+            }
         };
-        if (ok) ok = issue_s(0);
-        if (ok && n_kv > 1) ok = issue_s(1);
-        for (int j = 0; j < n_kv && ok; ++j) {
-            const int s = j % NST;
-            ok = mbar_wait_warp(&bar_p_full[j & 1], uint32_t(j >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
-            if (!ok) break;
-            ok = mbar_wait_warp(&bar_v_full[s], uint32_t(j / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-            if (!ok) break;
-            tc_fence_after_sync();
-            const uint64_t v_desc = make_sdesc_sw128(smem_u32(sV + s * Cfg::kKVTileBytes), Cfg::kKVBoxBytes, 1024);
-            if (elect_one()) {
-                // O += P_j V_j : 64 keys = 4 K steps; P lives in the first 32 columns of its S buffer
+        issue_next_s();
+        if (ok) issue_next_s();
+        int g = 0, n = 0;
+        for (int id; ok && (id = item_id(n)) < n_items; ++n) {
+            const int n_kv = item_nkv(id);
+            for (int j = 0; j < n_kv && ok; ++j, ++g) {
+                const int s = g % NST;
+                ok = mbar_wait_warp(&bar_p_full[g & 1], uint32_t(g >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+                if (!ok) break;
+                // the accumulator belongs to the previous item's epilogue until it has been read
+                if (j == 0 && n > 0) {
+                    ok = mbar_wait_warp(bar_o_free, uint32_t(n - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+                    if (!ok) break;
+                }
+                ok = mbar_wait_warp(&bar_v_full[s], uint32_t(g / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint64_t v_desc = make_sdesc_sw128(smem_u32(sV + s * Cfg::kKVTileBytes), Cfg::kKVBoxBytes, 1024);
+                if (elect_one()) {
+                    // O += P V : 64 keys = 4 K steps; P lives in the first 32 columns of its S buffer
 #pragma unroll
-                for (int ks = 0; ks < Cfg::kKeys / 16; ++ks)
-                    umma_ts(tmem + Cfg::kColO, tmem + ((j & 1) ? Cfg::kColS1 : Cfg::kColS0) + ks * 8,
-                            v_desc + uint64_t(ks * 128), idesc_o, (j > 0) || (ks > 0));
-                umma_commit(bar_pv_done);
-                umma_commit(&bar_v_free[s]);
+                    for (int ks = 0; ks < Cfg::kKeys / 16; ++ks)
+                        umma_ts(tmem + Cfg::kColO, tmem + ((g & 1) ? Cfg::kColS1 : Cfg::kColS0) + ks * 8,
+                                v_desc + uint64_t(ks * 128), idesc_o, (j > 0) || (ks > 0));
+                    umma_commit(bar_pv_done);
+                    umma_commit(&bar_v_free[s]);
+                    if (j + 1 == n_kv) umma_commit(bar_o_done);
+                }
+                __syncwarp();
+                issue_next_s();  // tile g + 2: its S buffer was read by the P V just issued
             }
-            __syncwarp();
-            if (j + 2 < n_kv) ok = issue_s(j + 2);
         }
-        // Every MMA issued above has completed once this barrier fires; TMEM may then be freed.
-        if (elect_one()) umma_commit(bar_drain);
-        __syncwarp();
-        mbar_wait_warp(bar_drain, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+        // nothing may be in flight when TMEM is freed: the last commit covers every MMA issued above
+        if (ok && n > 0) mbar_wait_warp(bar_o_done, uint32_t(n - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
     } else {
         // ------------------------------------------------------------------ softmax + epilogue
         reg_alloc<168>();
         const int row = tid;                                   // query row inside the tile == TMEM lane
         const uint32_t lane_base = uint32_t(warp * 32) << 16;  // this warp's TMEM lane quadrant
         const uint32_t t_o = tmem + lane_base + Cfg::kColO;
-        float m_ref = -INFINITY;  // exponent reference (a past row maximum), raw score units
-        float l = 0.f;            // running sum of exp2((s - m_ref) * scale_log2)
         bool ok = true;
-        for (int j = 0; j < n_kv; ++j) {
-            const uint32_t t_s = tmem + lane_base + ((j & 1) ? Cfg::kColS1 : Cfg::kColS0);
-            ok = mbar_wait_warp(&bar_s_full[j & 1], uint32_t(j >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
-            if (!ok) break;
-            B200ATTN_STAMP(tid == 0, 8 + 4 * j);
-            tc_fence_after_sync();
-            uint32_t sr[64];
-            tmem_ld_x32(t_s, &sr[0]);
-            tmem_ld_x32(t_s + 32, &sr[32]);
-            tmem_wait_ld();
-            const int kbase = j * Cfg::kKeys;  // first key of this tile
-            if (kbase + Cfg::kKeys - 1 > q0) {
-                // tile touches the diagonal: key kbase + c is visible to query q0 + row iff it is <= the query
-                const int lim = q0 + row - kbase;  // columns c <= lim are visible
-#pragma unroll
-                for (int c = 0; c < 64; ++c)
-                    if (c > lim) sr[c] = 0xff800000u;  // -inf
-            }
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < 64; c += 4) {
-                mx0 = fmaxf(mx0, __uint_as_float(sr[c + 0]));
-                mx1 = fmaxf(mx1, __uint_as_float(sr[c + 1]));
-                mx2 = fmaxf(mx2, __uint_as_float(sr[c + 2]));
-                mx3 = fmaxf(mx3, __uint_as_float(sr[c + 3]));
-            }
-            const float m_new = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m_ref);
-            float alpha = 1.f;
-            if ((m_new - m_ref) * p.scale_log2 > kRescaleThresholdLog2) {  // also true for m_ref == -inf
-                alpha = ex2_approx((m_ref - m_new) * p.scale_log2);
-                m_ref = m_new;
-            }
-            const float neg_m = -m_ref * p.scale_log2;
-            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 16; i += 2) {
-                    const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c * 32 + 2 * i + 0]), p.scale_log2, neg_m));
-                    const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c * 32 + 2 * i + 1]), p.scale_log2, neg_m));
-                    const float p2 = ex2_approx(fmaf(__uint_as_float(sr[c * 32 + 2 * i + 2]), p.scale_log2, neg_m));
-                    const float p3 = ex2_approx(fmaf(__uint_as_float(sr[c * 32 + 2 * i + 3]), p.scale_log2, neg_m));
-                    sum0 += p0;
-                    sum1 += p1;
-                    sum2 += p2;
-                    sum3 += p3;
-                    pk[i + 0] = pack_bf16x2(p0, p1);
-                    pk[i + 1] = pack_bf16x2(p2, p3);
-                }
-                tmem_st_x16(t_s + c * 16, pk);
-            }
-            l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));
-            B200ATTN_STAMP(tid == 0, 9 + 4 * j);
-            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-                // O must hold P V of tile j-1 before it is rescaled
-                ok = mbar_wait_warp(bar_pv_done, uint32_t(j - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
-                if (!ok) break;
-                tc_fence_after_sync();
-#pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
-                    uint32_t orr[32];
-                    tmem_ld_x32(t_o + c * 32, orr);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
-                    tmem_st_x32(t_o + c * 32, orr);
-                }
-            }
-            tmem_wait_st();
-            tc_fence_before_sync();
-            mbar_arrive(&bar_p_full[j & 1]);
-            B200ATTN_STAMP(tid == 0, 10 + 4 * j);
-        }
-        // All MMAs of this CTA are complete when the drain barrier fires.  (bar_pv_done cannot be used
-        // here: P V of the last TWO tiles may still be in flight, and a parity wait is only
-        // unambiguous when the waiter is at most one phase behind.)
-        if (ok) ok = mbar_wait(bar_drain, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
-        ok = __all_sync(0xffffffffu, ok);
-        B200ATTN_STAMP(tid == 0, 2);
-        if (ok) {
+        // Epilogue of one item: O / l -> BF16 -> global memory, logsumexp.  (bar_pv_done cannot be used for
+        // "O is complete": P V of the last TWO tiles may still be in flight, and a parity wait is only
+        // unambiguous when the waiter is at most one phase behind; bar_o_done completes once per item.)
+        auto epilogue = [&](int n_item, int q0, int b, int h, float m_ref, float l) -> bool {
+            if (!mbar_wait_warp(bar_o_done, uint32_t(n_item) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA)) return false;
             tc_fence_after_sync();
             const float inv_l = 1.f / l;
-            // O row -> BF16 -> global memory: every thread owns one contiguous row of D elements
             const bool in_range = q0 + row < p.T;
             uint16_t* orow = p.o + size_t(b) * p.o_sb + size_t(h) * p.o_sh + size_t(q0 + row) * p.o_st;
+            // every thread owns one contiguous row of D elements, written 64 columns at a time
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                uint32_t orr[32];
-                tmem_ld_x32(t_o + c * 32, orr);
-                tmem_wait_ld();
+            for (int hh = 0; hh < D / 64; ++hh) {
+                uint32_t ow[32];  // 64 columns as BF16 pairs
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {  // 4 chunks of 8 columns (16 bytes)
-                    uint4 w;
-                    w.x = pack_bf16x2(__uint_as_float(orr[g * 8 + 0]) * inv_l, __uint_as_float(orr[g * 8 + 1]) * inv_l);
-                    w.y = pack_bf16x2(__uint_as_float(orr[g * 8 + 2]) * inv_l, __uint_as_float(orr[g * 8 + 3]) * inv_l);
-                    w.z = pack_bf16x2(__uint_as_float(orr[g * 8 + 4]) * inv_l, __uint_as_float(orr[g * 8 + 5]) * inv_l);
-                    w.w = pack_bf16x2(__uint_as_float(orr[g * 8 + 6]) * inv_l, __uint_as_float(orr[g * 8 + 7]) * inv_l);
-                    if (in_range) *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = w;
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t orr[32];
+                    tmem_ld_x32(t_o + hh * 64 + c * 32, orr);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        ow[c * 16 + i] = pack_bf16x2(__uint_as_float(orr[2 * i]) * inv_l, __uint_as_float(orr[2 * i + 1]) * inv_l);
+                }
+                if (hh + 1 == D / 64) {
+                    // the accumulator has been read: the next item's first P V may overwrite it
+                    tc_fence_before_sync();
+                    mbar_arrive(bar_o_free);
+                }
+                if (in_range) {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        *reinterpret_cast<uint4*>(orow + hh * 64 + c * 8) =
+                            make_uint4(ow[c * 4], ow[c * 4 + 1], ow[c * 4 + 2], ow[c * 4 + 3]);
                 }
             }
             if (in_range) p.lse[(size_t(b) * p.Hq + h) * p.T + q0 + row] = m_ref * p.scale + logf(l);
+            return true;
+        };
+        // The epilogue of an item is deferred until the softmax of the next item's first tile has been handed
+        // to the MMA warp: the wait for the item's last P V then overlaps useful work.
+        bool pending = false;
+        int pend_q0 = 0, pend_b = 0, pend_h = 0;
+        float pend_m = 0.f, pend_l = 1.f;
+        int g = 0, n = 0;
+        for (int id; ok && (id = item_id(n)) < n_items; ++n) {
+            const int qt = item_qt(id), h = item_h(id), b = item_b(id), n_kv = item_nkv(id);
+            const int q0 = qt * 128;
+            float m_ref = -INFINITY;  // exponent reference (a past row maximum), raw score units
+            float l = 0.f;            // running sum of exp2((s - m_ref) * scale_log2)
+            for (int j = 0; j < n_kv; ++j, ++g) {
+                const uint32_t t_s = tmem + lane_base + ((g & 1) ? Cfg::kColS1 : Cfg::kColS0);
+                ok = mbar_wait_warp(&bar_s_full[g & 1], uint32_t(g >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+                if (!ok) break;
+                tc_fence_after_sync();
+                uint32_t sr[64];
+                tmem_ld_x32(t_s, &sr[0]);
+                tmem_ld_x32(t_s + 32, &sr[32]);
+                tmem_wait_ld();
+                const int kbase = j * Cfg::kKeys;  // first key of this tile
+                if (kbase + Cfg::kKeys - 1 > q0) {
+                    // tile touches the diagonal: key kbase + c is visible to query q0 + row iff it is <= the query
+                    const int lim = q0 + row - kbase;  // columns c <= lim are visible
+#pragma unroll
+                    for (int c = 0; c < 64; ++c)
+                        if (c > lim) sr[c] = 0xff800000u;  // -inf
+                }
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 64; c += 4) {
+                    mx0 = fmaxf(mx0, __uint_as_float(sr[c + 0]));
+                    mx1 = fmaxf(mx1, __uint_as_float(sr[c + 1]));
+                    mx2 = fmaxf(mx2, __uint_as_float(sr[c + 2]));
+                    mx3 = fmaxf(mx3, __uint_as_float(sr[c + 3]));
+                }
+                const float m_new = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m_ref);
+                float alpha = 1.f;
+                if ((m_new - m_ref) * p.scale_log2 > kRescaleThresholdLog2) {  // also true for m_ref == -inf
+                    alpha = ex2_approx((m_ref - m_new) * p.scale_log2);
+                    m_ref = m_new;
+                }
+                const float neg_m = -m_ref * p.scale_log2;
+                float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; i += 2) {
+                        const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c * 32 + 2 * i + 0]), p.scale_log2, neg_m));
+                        const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c * 32 + 2 * i + 1]), p.scale_log2, neg_m));
+                        const float p2 = ex2_approx(fmaf(__uint_as_float(sr[c * 32 + 2 * i + 2]), p.scale_log2, neg_m));
+                        const float p3 = ex2_approx(fmaf(__uint_as_float(sr[c * 32 + 2 * i + 3]), p.scale_log2, neg_m));
+                        sum0 += p0;
+                        sum1 += p1;
+                        sum2 += p2;
+                        sum3 += p3;
+                        pk[i + 0] = pack_bf16x2(p0, p1);
+                        pk[i + 1] = pack_bf16x2(p2, p3);
+                    }
+                    tmem_st_x16(t_s + c * 16, pk);
+                }
+                l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));
+                if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                    // O must hold P V of the previous tile before it is rescaled.  (At most one phase of
+                    // this barrier is outstanding here: P V of this tile cannot start before this
+                    // warp has arrived on bar_p_full below.)
+                    ok = mbar_wait_warp(bar_pv_done, uint32_t(g - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t orr[32];
+                        tmem_ld_x32(t_o + c * 32, orr);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+                        tmem_st_x32(t_o + c * 32, orr);
+                    }
+                }
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(&bar_p_full[g & 1]);
+                if (j == 0 && pending) {
+                    ok = epilogue(n - 1, pend_q0, pend_b, pend_h, pend_m, pend_l);
+                    pending = false;
+                    if (!ok) break;
+                }
+            }
+            if (!ok) break;
+            pending = true;
+            pend_q0 = q0, pend_b = b, pend_h = h, pend_m = m_ref, pend_l = l;
         }
+        if (ok && pending) epilogue(n - 1, pend_q0, pend_b, pend_h, pend_m, pend_l);
         tc_fence_before_sync();
-        B200ATTN_STAMP(tid == 0, 4);
     }
 
     // teardown: every role falls through to here, also after a wait that gave up

@@ -119,7 +119,9 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
         }
         attr_set[dev] = true;
     }
-    const unsigned grid = (unsigned)p.n_qtiles * (unsigned)p.Hq * (unsigned)p.B;
+    // persistent CTAs, two per SM, each walking a heaviest-first list of (query tile, head, batch) items
+    const long long items = (long long)p.n_qtiles * p.Hq * p.B;
+    const unsigned grid = (unsigned)std::min<long long>(items, 2LL * sm_count());
     if (launch_pdl(attn_fwd_kernel<D>, grid, 256, Cfg::kSmemBytes, st, tq, tk, tv, p) != cudaSuccess) {
         cudaGetLastError();
         return B200ATTN_ERR_CUDA;

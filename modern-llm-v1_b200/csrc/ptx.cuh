@@ -193,6 +193,14 @@ __device__ __forceinline__ uint64_t make_sdesc_sw128(uint32_t smem_addr, uint32_
 __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// Work distribution of the persistent kernels: items are numbered by decreasing cost and dealt to the
+// CTAs in rounds, every other round in reverse CTA order, so that the CTA that got the most expensive
+// item of one round gets the cheapest of the next.  Returns the id of the n-th item of CTA `cta`; the
+// first id >= the number of items ends that CTA's list.
+__device__ __forceinline__ int persistent_item(int n, int cta, int n_ctas) {
+    return n * n_ctas + ((n & 1) ? n_ctas - 1 - cta : cta);
+}
+
 // Elects one lane of a fully converged warp.  The MMA and TMA issuing warps run their loops
 // with all 32 lanes (so that addresses and descriptors stay in the uniform datapath) and
 // guard only the issuing instructions with this.

@@ -46,6 +46,7 @@ struct BwdParams {
     uint16_t* dq;           // q layout
     long long q_st, q_sh, q_sb;  // element strides of the q layout: token, head, batch
     int* status;
+    int* sched;  // two words of the device-wide item counter of the persistent dQ pass (see ptx.cuh)
 };
 
 template <int D>
@@ -148,7 +149,7 @@ struct DqCfg {
     static constexpr int kKVTileBytes = kKeys * D * 2;
     static constexpr int kKVBoxBytes = kKeys * 64 * 2;
     static constexpr int kBoxes = D / 64;
-    static constexpr int kSmemBytes = 3 * kQTileBytes + 2 * kStages * kKVTileBytes + 512 + 1024;  // Q, dO, O + ring
+    static constexpr int kSmemBytes = 3 * kQTileBytes + 2 * kStages * kKVTileBytes + 512 + 1024;  // Q, dO, O + ring + barriers
     static constexpr int kTmemCols = 256;
     static constexpr int kCtasPerSm = 2;
     static constexpr int kColS0 = 0, kColS1 = 64, kColDP = 128, kColAcc = 192;
@@ -187,6 +188,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     uint64_t* bar_kv_free = bars + 14 + NST;  // [NST]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14 + 2 * NST);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 15 + 2 * NST);
+    uint64_t* bar_item = bars + 24;     // [kItemRing] item ids handed out by the producer
+    volatile int* item_ring = reinterpret_cast<volatile int*>(bars + 24 + kItemRing);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_bh = p.B * p.Hq;
@@ -196,7 +199,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     auto item_h = [&](int id) { return (id % n_bh) % p.Hq; };
     auto item_b = [&](int id) { return (id % n_bh) / p.Hq; };
     auto item_nkv = [&](int id) { return (min(p.T, item_qt(id) * 128 + 128) + Cfg::kKeys - 1) / Cfg::kKeys; };
+    auto get_item = [&](int n) { return item_get(bar_item, item_ring, n, abort_flag, p.status); };
 
+    B200ATTN_TRACE_BEGIN(1);
     grid_dep_launch();
     if (warp == Cfg::kProducerWarp && lane == 0) {
         tma_prefetch_desc(&tmQ);
@@ -219,6 +224,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             mbar_init(&bar_kv_full[s], 1);
             mbar_init(&bar_kv_free[s], 1);
         }
+        for (int i = 0; i < kItemRing; ++i) mbar_init(&bar_item[i], 1);
         fence_mbar_init();
         grid_dep_wait();  // first global access of this CTA comes next
         *abort_flag = *reinterpret_cast<volatile int*>(p.status);
@@ -238,10 +244,20 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     } else if (warp == Cfg::kProducerWarp) {
         // ------------------------------------------------------------------ producer
         int g = 0;  // tiles issued so far by this CTA (ring position)
-        int n = 0;
         bool ok = true;
-        for (int id; ok && (id = persistent_item(n, int(blockIdx.x), int(gridDim.x))) < n_items; ++n) {
+        int id = blockIdx.x;  // the first item needs no fetch
+        int id_next = 0;      // lane 0: the id fetched for the next item
+        if (lane == 0) {
+            item_publish(bar_item, item_ring, 0, id);
+            id_next = sched_fetch(p.sched, 1, int(blockIdx.x), int(gridDim.x));
+        }
+        __syncwarp();
+        for (int n = 0; ok; ++n) {
             const int qt = item_qt(id), h = item_h(id), b = item_b(id), hk = h / p.group, n_kv = item_nkv(id);
+            // the next item is taken and announced shortly before this item's loads end, but not before the
+            // ring has been filled for this item
+            const int j_next = max(min(n_kv, NST) - 1, n_kv - 2);
+            int id_new = n_items;
             if (n > 0) ok = mbar_wait_warp(bar_q_free, (n - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
             if (ok && n > 0) ok = mbar_wait_warp(bar_o_free, (n - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
             if (!ok) break;
@@ -270,8 +286,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     }
                 }
                 __syncwarp();
+                if (j == j_next) {
+                    id_new = __shfl_sync(0xffffffffu, id_next, 0);
+                    if (lane == 0) {
+                        item_publish(bar_item, item_ring, n + 1, id_new < n_items ? id_new : -1);
+                        if (id_new < n_items) id_next = sched_fetch(p.sched, n + 2, int(blockIdx.x), int(gridDim.x));
+                    }
+                    __syncwarp();
+                }
             }
+            if (!ok || id_new >= n_items) break;
+            id = id_new;
         }
+        if (ok && lane == 0) sched_finish(p.sched, int(gridDim.x));
     } else if (warp == Cfg::kMmaWarp) {
         // ------------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc_s = make_idesc_bf16(128, Cfg::kKeys, 0, 0);
@@ -312,9 +339,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         };
         int g0 = 0, n = 0;
         bool ok = true;
-        for (int id; ok && (id = persistent_item(n, int(blockIdx.x), int(gridDim.x))) < n_items; ++n) {
+        for (int id; ok && (id = get_item(n)) >= 0; ++n) {
             const int n_kv = item_nkv(id);
+            B200ATTN_STAMP(lane == 0, 440 + 2 * n);
             ok = mbar_wait_warp(bar_q, n & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+            B200ATTN_STAMP(lane == 0, 441 + 2 * n);
             if (ok) ok = issue_s(g0);
             // the dP block still holds the previous item's last dP until the compute warps have read it
             if (ok && g0 > 0) ok = mbar_wait_warp(bar_dp_free, (g0 - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
@@ -329,11 +358,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     // next dP as soon as this one has been read into registers
                     ok = mbar_wait_warp(bar_dp_free, g & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
                     if (!ok) break;
+                    B200ATTN_STAMP(lane == 0, 240 + 8 * g + 4);
                     tc_fence_after_sync();
                     issue_dp(g + 1, j + 2 == n_kv);
                 }
                 ok = mbar_wait_warp(&bar_ds_full[g & 1], uint32_t(g >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
                 if (!ok) break;
+                B200ATTN_STAMP(lane == 0, 240 + 8 * g + 5);
                 // the accumulator still belongs to the previous item's epilogue until it has been read
                 if (j == 0 && n > 0) {
                     ok = mbar_wait_warp(bar_acc_free, (n - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
@@ -355,7 +386,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     if (j + 1 == n_kv) umma_commit(bar_acc);
                 }
                 __syncwarp();
+                B200ATTN_STAMP(lane == 0, 240 + 8 * g + 6);
                 if (j + 2 < n_kv) ok = issue_s(g + 2);
+                B200ATTN_STAMP(lane == 0, 240 + 8 * g + 7);
             }
             g0 += n_kv;
         }
@@ -369,15 +402,17 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const int c0 = part * Cfg::kPartCols;  // first key column of this thread's part
         int g0 = 0, n = 0;
         bool ok = true;
-        for (int id; ok && (id = persistent_item(n, int(blockIdx.x), int(gridDim.x))) < n_items; ++n) {
+        for (int id; ok && (id = get_item(n)) >= 0; ++n) {
             const int qt = item_qt(id), h = item_h(id), b = item_b(id), n_kv = item_nkv(id);
             const int q0 = qt * 128;
             // preprocess of this row from the tiles in shared memory: D = rowsum(O * dO); L * log2(e)
             const bool in_range = q0 + row < p.T;
             const float lse2 = in_range ? p.lse[(size_t(b) * p.Hq + h) * p.T + q0 + row] * 1.4426950408889634f
                                         : INFINITY;  // exp2(x - inf) = 0: padding query rows contribute nothing
+            B200ATTN_STAMP(tid == 0, 400 + 4 * n + 0);
             ok = mbar_wait_warp(bar_q, n & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
             if (!ok) break;
+            B200ATTN_STAMP(tid == 0, 400 + 4 * n + 1);
             float dv = 0.f;
 #pragma unroll
             for (int c = 0; c < D / 8; ++c) {
@@ -403,6 +438,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 const uint32_t t_s = tmem + lane_base + ((g & 1) ? Cfg::kColS1 : Cfg::kColS0) + c0;
                 ok = mbar_wait_warp(&bar_s_full[g & 1], uint32_t(g >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
                 if (!ok) break;
+                B200ATTN_STAMP(tid == 0, 240 + 8 * g + 0);
                 tc_fence_after_sync();
                 // phase A: P from S
                 float pr[32];
@@ -420,8 +456,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     for (int i = 0; i < 32; ++i)
                         if (i > lim) pr[i] = 0.f;
                 }
+                B200ATTN_STAMP(tid == 0, 240 + 8 * g + 1);
                 ok = mbar_wait_warp(bar_dp_full, g & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
                 if (!ok) break;
+                B200ATTN_STAMP(tid == 0, 240 + 8 * g + 2);
                 tc_fence_after_sync();
                 // phase B: dS = P (dP - D), written as BF16 over the part's first 16 columns of the S buffer
                 {
@@ -439,12 +477,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 tmem_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(&bar_ds_full[g & 1]);
+                B200ATTN_STAMP(tid == 0, 240 + 8 * g + 3);
             }
             if (!ok) break;
             g0 += n_kv;
             // epilogue of the item: dQ rows (times scale) -> BF16 -> global memory; each part writes D / 2 columns
             ok = mbar_wait_warp(bar_acc, n & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
             if (!ok) break;
+            B200ATTN_STAMP(tid == 0, 400 + 4 * n + 2);
             tc_fence_after_sync();
             constexpr int kCols = D / Cfg::kParts;
             uint32_t v[kCols];
@@ -465,6 +505,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     *reinterpret_cast<uint4*>(dqrow + gq * 8) = w;
                 }
             }
+            B200ATTN_STAMP(tid == 0, 400 + 4 * n + 3);
         }
     }
 
@@ -474,6 +515,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tc_fence_after_sync();
         tmem_dealloc(tmem, Cfg::kTmemCols);
     }
+    B200ATTN_TRACE_END(1);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -546,6 +588,7 @@ attn_bwd_dq_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     const int q0 = qt * 128;
     const int n_kv = qt + 1;
 
+    B200ATTN_TRACE_BEGIN(1);
     // launched with programmatic stream serialization: wait for the previous kernel before any global access
     grid_dep_launch();
     grid_dep_wait();
@@ -779,6 +822,7 @@ attn_bwd_dq_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         tc_fence_after_sync();
         tmem_dealloc(tmem, Cfg::kTmemCols);
     }
+    B200ATTN_TRACE_END(1);
 }
 
 
@@ -823,6 +867,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     const int hk = (int(blockIdx.x) % n_bh) % p.Hkv, b = (int(blockIdx.x) % n_bh) / p.Hkv;
     const int k0 = kt * 128;
     const int n_i = p.n_tiles - kt;  // query tiles kt .. n_tiles-1
+    B200ATTN_TRACE_BEGIN(2);
     const int n_it = p.group * n_i;  // times the query heads of the group
 
     grid_dep_launch();
@@ -1074,6 +1119,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         tc_fence_after_sync();
         tmem_dealloc(tmem, Cfg::kTmemCols);
     }
+    B200ATTN_TRACE_END(2);
 }
 
 }  // namespace b200attn

@@ -4,8 +4,8 @@
 // llm/src/model/flash_attn.cu:28-131), computed tile-wise on the tensor cores.
 //
 // Persistent CTAs, two per SM.  A CTA walks a static list of work items (item = one 128-row
-// query tile of one (batch, query head); items are ordered heaviest first and dealt
-// round-robin) and, per item, the 64-key tiles of K/V up to the diagonal (tiles above it are
+// query tile of one (batch, query head); items are ordered heaviest first and dealt in rounds of
+// alternating direction) and, per item, the 64-key tiles of K/V up to the diagonal (tiles above it are
 // never loaded).  Every pipeline keeps running across item boundaries: the K/V ring prefetches
 // the next item's tiles and the MMA warp issues the next item's first Q K^T products while the
 // softmax warps write the previous item's output rows.  GQA is an index: the K/V tensor maps are
@@ -17,10 +17,11 @@
 //   warp  4    TMA producer (converged warp, one elected lane issues)
 //   warp  5    TMEM allocation and tcgen05.mma issue (converged warp, one elected lane issues)
 //   warps 6-7  idle (they only donate registers)
-// TMEM (256 columns): S buffer 0 [0,64), S buffer 1 [64,128) as FP32, each re-used as P
-//   (BF16 pairs, 32 columns); O accumulator FP32 [128,128+D).
-// With two S buffers the product Q K^T of tile g+1 is issued before the softmax of tile g
-// ends, and P V of tile g runs under the softmax of tile g+1.
+// TMEM (256 columns): S buffers of 64 FP32 columns, three for D = 64 and two for D = 128, each
+//   re-used as P (BF16 pairs, 32 columns); the O accumulator (FP32, D columns) behind them.
+// The MMA warp's work is a chain softmax(g) -> P V(g) -> Q K^T(g + buffers) -> softmax(g + buffers);
+// with several S buffers the products Q K^T run that many tiles ahead of the softmax, and P V of
+// tile g runs under the softmax of tile g+1.
 #pragma once
 
 #include "ptx.cuh"
@@ -36,6 +37,7 @@ struct FwdParams {
     uint16_t* o;       // output, BF16
     long long o_st, o_sh, o_sb;  // element strides of o: token, head, batch
     int* status;       // device status word
+    int* sched;        // two words of the device-wide item counter (see ptx.cuh)
 };
 
 template <int D>
@@ -48,12 +50,17 @@ struct FwdCfg {
     static constexpr int kKVTileBytes = kKeys * D * 2;
     static constexpr int kKVBoxBytes = kKeys * 64 * 2;  // K/V TMA box: 64 rows x 64 bf16
     static constexpr int kBoxes = D / 64;
-    static constexpr int kBarBytes = 256;
+    static constexpr int kBarBytes = 384;
     static constexpr int kSmemBytes = kQBufs * kQTileBytes + 2 * kStages * kKVTileBytes + kBarBytes + 1024;
     static constexpr int kTmemCols = 256;
-    static constexpr int kColS0 = 0;
-    static constexpr int kColS1 = 64;
-    static constexpr int kColO = 128;
+    // S buffers: three for D = 64 (all 256 columns used), two for D = 128
+#ifdef B200ATTN_FWD_SBUFS
+    static constexpr int kSBufs = B200ATTN_FWD_SBUFS;
+#else
+    static constexpr int kSBufs = (D == 64) ? 3 : 2;
+#endif
+    static constexpr int kColO = kSBufs * 64;
+    __host__ __device__ static constexpr int col_s(int buf) { return buf * 64; }
 };
 
 // log2 of the growth of the row maximum that is tolerated before O and the row
@@ -67,6 +74,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     using Cfg = FwdCfg<D>;
     constexpr int NST = Cfg::kStages;
     constexpr int NQB = Cfg::kQBufs;
+    constexpr int NSB = Cfg::kSBufs;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;
@@ -75,33 +83,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint64_t* bars = reinterpret_cast<uint64_t*>(sV + NST * Cfg::kKVTileBytes);
     uint64_t* bar_q = bars + 0;        // [2] per Q buffer: Q of an item has landed              (phase: item / NQB)
     uint64_t* bar_q_free = bars + 2;   // [2] per Q buffer: every Q K^T product of the item done (phase: item / NQB)
-    uint64_t* bar_s_full = bars + 4;   // [2] per S buffer                                        (phase: tile / 2)
-    uint64_t* bar_p_full = bars + 6;   // [2] per S buffer: P written, O rescaled                 (phase: tile / 2)
-    uint64_t* bar_pv_done = bars + 8;  // P V of a tile is complete                               (phase: tile)
-    uint64_t* bar_o_done = bars + 9;   // O of an item is complete                                (phase: item)
-    uint64_t* bar_o_free = bars + 10;  // O has been read by the epilogue                         (phase: item)
-    uint64_t* bar_k_full = bars + 11;            // [NST]
-    uint64_t* bar_k_free = bars + 11 + NST;      // [NST]
-    uint64_t* bar_v_full = bars + 11 + 2 * NST;  // [NST]
-    uint64_t* bar_v_free = bars + 11 + 3 * NST;  // [NST]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 28);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 29);
+    uint64_t* bar_s_full = bars + 4;   // [NSB] per S buffer                                      (phase: tile / NSB)
+    uint64_t* bar_p_full = bars + 7;   // [NSB] per S buffer: P written, O rescaled               (phase: tile / NSB)
+    uint64_t* bar_pv_done = bars + 10; // P V of a tile is complete                               (phase: tile)
+    uint64_t* bar_o_done = bars + 11;  // O of an item is complete                                (phase: item)
+    uint64_t* bar_o_free = bars + 12;  // O has been read by the epilogue                         (phase: item)
+    uint64_t* bar_k_full = bars + 13;            // [NST]
+    uint64_t* bar_k_free = bars + 13 + NST;      // [NST]
+    uint64_t* bar_v_full = bars + 13 + 2 * NST;  // [NST]
+    uint64_t* bar_v_free = bars + 13 + 3 * NST;  // [NST]
+    uint64_t* bar_item = bars + 32;    // [kItemRing] item ids handed out by the producer
+    volatile int* item_ring = reinterpret_cast<volatile int*>(bars + 32 + kItemRing);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 30);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 31);
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
 
-    // item id -> (query tile, head, batch); ids are ordered by work, heaviest query tile first, and dealt
-    // to the CTAs in rounds of alternating direction so that every CTA gets a similar amount of work
+    // item id -> (query tile, head, batch); ids are ordered by work, heaviest query tile first
     const int n_bh = p.B * p.Hq;
     const int n_items = p.n_qtiles * n_bh;
-    auto item_id = [&](int n) { return persistent_item(n, int(blockIdx.x), int(gridDim.x)); };
+    auto get_item = [&](int n) { return item_get(bar_item, item_ring, n, abort_flag, p.status); };
     auto item_qt = [&](int id) { return p.n_qtiles - 1 - id / n_bh; };
     auto item_h = [&](int id) { return (id % n_bh) % p.Hq; };
     auto item_b = [&](int id) { return (id % n_bh) / p.Hq; };
     auto item_nkv = [&](int id) { return (min(p.T, item_qt(id) * 128 + 128) + Cfg::kKeys - 1) / Cfg::kKeys; };
 
-    B200ATTN_TRACE_BEGIN();
+    B200ATTN_TRACE_BEGIN(0);
     // Set-up with one CTA-wide barrier: one lane of the producer warp initialises every mbarrier while
     // the MMA warp allocates TMEM; nothing touches global memory before grid_dep_wait().
     grid_dep_launch();
@@ -112,6 +121,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bar_q[i], 1);
             mbar_init(&bar_q_free[i], 1);
+        }
+        for (int i = 0; i < NSB; ++i) {
             mbar_init(&bar_s_full[i], 1);
             mbar_init(&bar_p_full[i], 128);
         }
@@ -124,6 +135,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             mbar_init(&bar_v_full[s], 1);
             mbar_init(&bar_v_free[s], 1);
         }
+        for (int i = 0; i < kItemRing; ++i) mbar_init(&bar_item[i], 1);
         fence_mbar_init();
         grid_dep_wait();  // first global access of this CTA comes next
         *abort_flag = *reinterpret_cast<volatile int*>(p.status);
@@ -145,21 +157,42 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     } else if (warp == 4) {
         // ------------------------------------------------------------------ producer
         reg_dealloc<88>();
-        int g = 0, n = 0;  // g: key tiles issued so far by this CTA (ring position)
+        int g = 0;  // key tiles issued so far by this CTA (ring position)
         bool ok = true;
-        for (int id; ok && (id = item_id(n)) < n_items; ++n) {
-            const int qt = item_qt(id), h = item_h(id), b = item_b(id), hk = h / p.group, n_kv = item_nkv(id);
+        int id_next = 0;  // lane 0: the id fetched for the item after the next Q load
+        // Q of this CTA's n-th item (item id `id`) into Q buffer n % NQB
+        auto load_q = [&](int n, int id) {
             const int qb = n % NQB;
             if (n >= NQB)
                 ok = mbar_wait_warp(&bar_q_free[qb], uint32_t(n / NQB - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
-            if (!ok) break;
+            if (!ok) return;
             if (elect_one()) {
                 mbar_arrive_expect_tx(&bar_q[qb], Cfg::kQTileBytes);
 #pragma unroll
                 for (int bx = 0; bx < Cfg::kBoxes; ++bx)
-                    tma_load_4d(sQ + qb * Cfg::kQTileBytes + bx * Cfg::kQBoxBytes, &tmQ, &bar_q[qb], bx * 64, qt * 128, h, b);
+                    tma_load_4d(sQ + qb * Cfg::kQTileBytes + bx * Cfg::kQBoxBytes, &tmQ, &bar_q[qb], bx * 64,
+                                item_qt(id) * 128, item_h(id), item_b(id));
             }
             __syncwarp();
+        };
+        int id = blockIdx.x;  // the first item needs no fetch
+        if (lane == 0) {
+            item_publish(bar_item, item_ring, 0, id);
+            id_next = sched_fetch(p.sched, 1, int(blockIdx.x), int(gridDim.x));
+        }
+        __syncwarp();
+        load_q(0, id);
+        for (int n = 0; ok; ++n) {
+            const int h = item_h(id), b = item_b(id), hk = h / p.group, n_kv = item_nkv(id);
+            // The next item is taken, announced and its Q requested a few tiles before this item's loads end
+            // (late, so that a CTA commits itself to little work ahead, but not before the ring has been
+            // filled for this item); with one Q buffer, after this item's last tile (it is free only then).
+#ifdef B200ATTN_EARLY_FETCH
+            const int j_next = NQB > 1 ? min(n_kv, NST) - 1 : n_kv - 1;
+#else
+            const int j_next = NQB > 1 ? max(min(n_kv, NST) - 1, n_kv - 3) : n_kv - 1;
+#endif
+            int id_new = n_items;
             for (int j = 0; j < n_kv; ++j, ++g) {
                 const int s = g % NST;
                 const uint32_t use = uint32_t(g / NST);
@@ -183,24 +216,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                     j * Cfg::kKeys, hk, b);
                 }
                 __syncwarp();
+                if (j == j_next) {
+                    id_new = __shfl_sync(0xffffffffu, id_next, 0);
+                    const bool more = id_new < n_items;
+                    if (lane == 0) {
+                        item_publish(bar_item, item_ring, n + 1, more ? id_new : -1);
+                        if (more) id_next = sched_fetch(p.sched, n + 2, int(blockIdx.x), int(gridDim.x));
+                    }
+                    __syncwarp();
+                    if (more) load_q(n + 1, id_new);
+                    if (!ok) break;
+                }
             }
+            if (!ok || id_new >= n_items) break;
+            id = id_new;
         }
+        if (ok && lane == 0) sched_finish(p.sched, int(gridDim.x));
     } else if (warp == 5) {
         // ------------------------------------------------------------------ MMA issuer
         reg_dealloc<88>();
         constexpr uint32_t idesc_s = make_idesc_bf16(128, Cfg::kKeys, 0, 0);
         constexpr uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);
         // This CTA's key tiles are numbered g = 0, 1, ... across all its items: ring stage g % NST,
-        // S buffer g & 1.  Two cursors walk that sequence: `sc` for the products Q K^T, which runs
-        // two tiles ahead of `pc` for the products P V, also across an item boundary.
+        // S buffer g % NSB.  The cursor `sc` walks that sequence for the products Q K^T, NSB tiles ahead
+        // of the loop below that issues the products P V, also across item boundaries.
         struct Cursor {
             int id, n, j, n_kv, g;  // item id, items before it on this CTA, tile in item, tiles of item, global tile
         };
-        Cursor sc{item_id(0), 0, 0, 0, 0};
-        if (sc.id < n_items) sc.n_kv = item_nkv(sc.id);
+        Cursor sc{get_item(0), 0, 0, 0, 0};
+        if (sc.id >= 0) sc.n_kv = item_nkv(sc.id);
         bool ok = true;
         auto issue_next_s = [&]() {
-            if (sc.id >= n_items) return;
+            if (sc.id < 0) return;
             const int s = sc.g % NST, qb = sc.n % NQB;
             if (sc.j == 0) ok = mbar_wait_warp(&bar_q[qb], uint32_t(sc.n / NQB) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
             if (ok) ok = mbar_wait_warp(&bar_k_full[s], uint32_t(sc.g / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
@@ -212,29 +259,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (elect_one()) {
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks)
-                    umma_ss(tmem + ((sc.g & 1) ? Cfg::kColS1 : Cfg::kColS0), q_desc + kmajor_step(ks, Cfg::kQBoxBytes),
+                    umma_ss(tmem + Cfg::col_s(sc.g % NSB), q_desc + kmajor_step(ks, Cfg::kQBoxBytes),
                             k_desc + kmajor_step(ks, Cfg::kKVBoxBytes), idesc_s, ks > 0);
-                umma_commit(&bar_s_full[sc.g & 1]);
+                umma_commit(&bar_s_full[sc.g % NSB]);
                 umma_commit(&bar_k_free[s]);
                 if (last) umma_commit(&bar_q_free[qb]);
             }
             __syncwarp();
             ++sc.g;
             if (++sc.j == sc.n_kv) {
-                sc.id = item_id(++sc.n);
+                sc.id = get_item(++sc.n);
                 sc.j = 0;
-                sc.n_kv = sc.id < n_items ? item_nkv(sc.id) : 0;
+                sc.n_kv = sc.id >= 0 ? item_nkv(sc.id) : 0;
             }
         };
-        issue_next_s();
-        if (ok) issue_next_s();
+        for (int i = 0; i < NSB && ok; ++i) issue_next_s();
         int g = 0, n = 0;
-        for (int id; ok && (id = item_id(n)) < n_items; ++n) {
+        // (this warp has already waited for the ring entry of item n: the cursor above is never behind)
+        for (int id; ok && (id = item_ring[n % kItemRing]) >= 0; ++n) {
             const int n_kv = item_nkv(id);
             for (int j = 0; j < n_kv && ok; ++j, ++g) {
                 const int s = g % NST;
-                ok = mbar_wait_warp(&bar_p_full[g & 1], uint32_t(g >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+                ok = mbar_wait_warp(&bar_p_full[g % NSB], uint32_t(g / NSB) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
                 if (!ok) break;
+                B200ATTN_STAMP(lane == 0, 16 + 8 * g + 4);
                 // the accumulator belongs to the previous item's epilogue until it has been read
                 if (j == 0 && n > 0) {
                     ok = mbar_wait_warp(bar_o_free, uint32_t(n - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
@@ -248,14 +296,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     // O += P V : 64 keys = 4 K steps; P lives in the first 32 columns of its S buffer
 #pragma unroll
                     for (int ks = 0; ks < Cfg::kKeys / 16; ++ks)
-                        umma_ts(tmem + Cfg::kColO, tmem + ((g & 1) ? Cfg::kColS1 : Cfg::kColS0) + ks * 8,
+                        umma_ts(tmem + Cfg::kColO, tmem + Cfg::col_s(g % NSB) + ks * 8,
                                 v_desc + uint64_t(ks * 128), idesc_o, (j > 0) || (ks > 0));
                     umma_commit(bar_pv_done);
                     umma_commit(&bar_v_free[s]);
                     if (j + 1 == n_kv) umma_commit(bar_o_done);
                 }
                 __syncwarp();
-                issue_next_s();  // tile g + 2: its S buffer was read by the P V just issued
+                B200ATTN_STAMP(lane == 0, 16 + 8 * g + 5);
+                issue_next_s();  // tile g + NSB: its S buffer was read by the P V just issued
+                B200ATTN_STAMP(lane == 0, 16 + 8 * g + 6);
             }
         }
         // nothing may be in flight when TMEM is freed: the last commit covers every MMA issued above
@@ -271,7 +321,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         // "O is complete": P V of the last TWO tiles may still be in flight, and a parity wait is only
         // unambiguous when the waiter is at most one phase behind; bar_o_done completes once per item.)
         auto epilogue = [&](int n_item, int q0, int b, int h, float m_ref, float l) -> bool {
+            B200ATTN_STAMP(tid == 0, 400 + 4 * n_item + 0);
             if (!mbar_wait_warp(bar_o_done, uint32_t(n_item) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA)) return false;
+            B200ATTN_STAMP(tid == 0, 400 + 4 * n_item + 1);
             tc_fence_after_sync();
             const float inv_l = 1.f / l;
             const bool in_range = q0 + row < p.T;
@@ -302,6 +354,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 }
             }
             if (in_range) p.lse[(size_t(b) * p.Hq + h) * p.T + q0 + row] = m_ref * p.scale + logf(l);
+            B200ATTN_STAMP(tid == 0, 400 + 4 * n_item + 2);
             return true;
         };
         // The epilogue of an item is deferred until the softmax of the next item's first tile has been handed
@@ -310,15 +363,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         int pend_q0 = 0, pend_b = 0, pend_h = 0;
         float pend_m = 0.f, pend_l = 1.f;
         int g = 0, n = 0;
-        for (int id; ok && (id = item_id(n)) < n_items; ++n) {
+        for (int id; ok && (id = get_item(n)) >= 0; ++n) {
             const int qt = item_qt(id), h = item_h(id), b = item_b(id), n_kv = item_nkv(id);
             const int q0 = qt * 128;
             float m_ref = -INFINITY;  // exponent reference (a past row maximum), raw score units
             float l = 0.f;            // running sum of exp2((s - m_ref) * scale_log2)
             for (int j = 0; j < n_kv; ++j, ++g) {
-                const uint32_t t_s = tmem + lane_base + ((g & 1) ? Cfg::kColS1 : Cfg::kColS0);
-                ok = mbar_wait_warp(&bar_s_full[g & 1], uint32_t(g >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+                const uint32_t t_s = tmem + lane_base + Cfg::col_s(g % NSB);
+                ok = mbar_wait_warp(&bar_s_full[g % NSB], uint32_t(g / NSB) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
                 if (!ok) break;
+                B200ATTN_STAMP(tid == 0, 16 + 8 * g + 0);
                 tc_fence_after_sync();
                 uint32_t sr[64];
                 tmem_ld_x32(t_s, &sr[0]);
@@ -367,6 +421,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     tmem_st_x16(t_s + c * 16, pk);
                 }
                 l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));
+                B200ATTN_STAMP(tid == 0, 16 + 8 * g + 1);
                 if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
                     // O must hold P V of the previous tile before it is rescaled.  (At most one phase of
                     // this barrier is outstanding here: P V of this tile cannot start before this
@@ -386,7 +441,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 }
                 tmem_wait_st();
                 tc_fence_before_sync();
-                mbar_arrive(&bar_p_full[g & 1]);
+                mbar_arrive(&bar_p_full[g % NSB]);
+                B200ATTN_STAMP(tid == 0, 16 + 8 * g + 2);
                 if (j == 0 && pending) {
                     ok = epilogue(n - 1, pend_q0, pend_b, pend_h, pend_m, pend_l);
                     pending = false;
@@ -408,7 +464,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_after_sync();
         tmem_dealloc(tmem, Cfg::kTmemCols);
     }
-    B200ATTN_TRACE_END();
+    B200ATTN_TRACE_END(0);
 }
 
 }  // namespace b200attn

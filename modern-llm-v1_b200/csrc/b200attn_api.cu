@@ -3,8 +3,12 @@
 #include "../../include/b200attn.h"
 
 #include <cuda_runtime.h>
+
+#include <algorithm>
+#include <atomic>
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "attn_bwd.cuh"
 #include "attn_decode.cuh"
@@ -20,6 +24,19 @@ __device__ int g_status_word;
 
 constexpr int kMaxDevices = 64;
 int* g_status_ptr[kMaxDevices] = {nullptr};
+
+// Item counters of the persistent kernels (two words per launch, see ptx.cuh), also in the device
+// image (zero at load).  A kernel leaves its two words zero again when it ends, so one pair would do
+// for launches that follow each other on one stream; consecutive launches take consecutive pairs so
+// that launches running at the same time on different streams do not share one.  (Two launches
+// kSchedSlots launches apart that overlap in time, or one captured graph replayed concurrently with
+// itself, would share a pair: serialise those.)  A kernel that gave up on a wait may leave its pair
+// non-zero; b200attn_last_device_status clears all pairs when it reports such a failure, and until
+// then every kernel exits at once because the status word is set.
+constexpr int kSchedSlots = 64;
+__device__ int g_sched_words[2 * kSchedSlots];
+int* g_sched_ptr[kMaxDevices] = {nullptr};
+std::atomic<unsigned> g_sched_seq{0};
 
 // Returns the device address of the status word of the current device (resolved once per device).
 int* status_ptr(int* err) {
@@ -40,9 +57,32 @@ int* status_ptr(int* err) {
             *err = B200ATTN_ERR_CUDA;
             return nullptr;
         }
+        void* sp = nullptr;
+        if (cudaGetSymbolAddress(&sp, g_sched_words) != cudaSuccess) {
+            cudaGetLastError();
+            *err = B200ATTN_ERR_NO_DEVICE;
+            return nullptr;
+        }
+        g_sched_ptr[dev] = static_cast<int*>(sp);
         g_status_ptr[dev] = static_cast<int*>(p);
     }
     return g_status_ptr[dev];
+}
+
+// The counter pair for the next launch of a persistent kernel on the current device (status_ptr()
+// has resolved the device's addresses before).
+// Returns nullptr when the items should be dealt statically: with only a few items per CTA a static
+// deal in rounds of alternating direction balances better than first come, first served, because a CTA
+// takes its next item before it has finished the current one.  (B200ATTN_ITEMS=static|dynamic overrides.)
+int* next_sched_pair(long long n_items, unsigned n_ctas) {
+    static const int forced = [] {
+        const char* e = getenv("B200ATTN_ITEMS");
+        return !e ? 0 : (e[0] == 's' ? 1 : (e[0] == 'd' ? 2 : 0));
+    }();
+    if (forced == 1 || (forced == 0 && n_items < 4LL * n_ctas)) return nullptr;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return g_sched_ptr[dev] + 2 * (g_sched_seq.fetch_add(1, std::memory_order_relaxed) % kSchedSlots);
 }
 
 // SM count of the current device (cached per device).
@@ -122,7 +162,9 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
     // persistent CTAs, two per SM, each walking a heaviest-first list of (query tile, head, batch) items
     const long long items = (long long)p.n_qtiles * p.Hq * p.B;
     const unsigned grid = (unsigned)std::min<long long>(items, 2LL * sm_count());
-    if (launch_pdl(attn_fwd_kernel<D>, grid, 256, Cfg::kSmemBytes, st, tq, tk, tv, p) != cudaSuccess) {
+    FwdParams pl = p;
+    pl.sched = next_sched_pair(items, grid);
+    if (launch_pdl(attn_fwd_kernel<D>, grid, 256, Cfg::kSmemBytes, st, tq, tk, tv, pl) != cudaSuccess) {
         cudaGetLastError();
         return B200ATTN_ERR_CUDA;
     }
@@ -160,6 +202,7 @@ extern "C" int b200attn_fwd(const void* q, const void* k, const void* v, void* o
     p.o_sh = sq.h;
     p.o_sb = sq.b;
     p.status = status;
+    p.sched = nullptr;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return D == 64 ? launch_fwd<64>(tq, tk, tv, p, st) : launch_fwd<128>(tq, tk, tv, p, st);
 }
@@ -209,10 +252,12 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk64, const CUtensorMap
         const unsigned resident = 2u * (unsigned)sm_count();
         if (dq_grid > resident) dq_grid = resident;
     }
+    BwdParams pq = p;
+    if (!kWide) pq.sched = next_sched_pair(dq_items, dq_grid);
     const cudaError_t e = kWide ? launch_pdl(attn_bwd_dq_wide_kernel<D>, dq_grid, 320, DqWideCfg<D>::kSmemBytes, st, tq, tk,
                                              tv, tdo, tdq, p)
                                 : launch_pdl(attn_bwd_dq_kernel<D>, dq_grid, DqCfg<D>::kThreads, DqCfg<D>::kSmemBytes, st, tq, tk64, tv64,
-                                             tdo, to, p);
+                                             tdo, to, pq);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return B200ATTN_ERR_CUDA;
@@ -295,6 +340,7 @@ extern "C" int b200attn_bwd(const void* q, const void* k, const void* v, const v
     p.q_sh = sq.h;
     p.q_sb = sq.b;
     p.status = status;
+    p.sched = nullptr;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return D == 64 ? launch_bwd<64>(tq, tk64, tv64, tk, tv, tdo, to, tdq, tdk, tdv, p, st)
                    : launch_bwd<128>(tq, tk64, tv64, tk, tv, tdo, to, tdq, tdk, tdv, p, st);
@@ -458,6 +504,12 @@ extern "C" int b200attn_last_device_status(void* stream) {
     int host = 0;
     if (cudaMemcpy(&host, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return B200ATTN_ERR_CUDA;
     if (host != 0) {
+        // a kernel that gave up may have left its item counters behind: wait for everything else on the
+        // device (kernels exit at once while the status word is set), then clear counters and status
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceSynchronize();
+        cudaMemset(g_sched_ptr[dev], 0, sizeof(int) * 2 * kSchedSlots);
         cudaMemset(status, 0, sizeof(int));
         return host;
     }

@@ -193,13 +193,6 @@ __device__ __forceinline__ uint64_t make_sdesc_sw128(uint32_t smem_addr, uint32_
 __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-// Work distribution of the persistent kernels: items are numbered by decreasing cost and dealt to the
-// CTAs in rounds, every other round in reverse CTA order, so that the CTA that got the most expensive
-// item of one round gets the cheapest of the next.  Returns the id of the n-th item of CTA `cta`; the
-// first id >= the number of items ends that CTA's list.
-__device__ __forceinline__ int persistent_item(int n, int cta, int n_ctas) {
-    return n * n_ctas + ((n & 1) ? n_ctas - 1 - cta : cta);
-}
 
 // Elects one lane of a fully converged warp.  The MMA and TMA issuing warps run their loops
 // with all 32 lanes (so that addresses and descriptors stay in the uniform datapath) and
@@ -220,6 +213,51 @@ __device__ __forceinline__ bool elect_one() {
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
                                                int code) {
     return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, code));
+}
+
+// ---------------------------------------------------------------------------
+// Work distribution of the persistent kernels.  Items are numbered by decreasing cost.  A CTA
+// starts with item blockIdx.x; every further item comes from a device-wide counter (sched[0]), so
+// that whichever CTA is free takes the most expensive item left.  The producer warp of a CTA
+// fetches the ids one item ahead and hands them to the other warps through a ring of kItemRing
+// entries in shared memory, one mbarrier per entry; the entry of the CTA's n-th item is n % kItemRing
+// and completes phase n / kItemRing of its barrier.  (No warp is ever more than a few items behind
+// the producer, because the producer's loads wait for the buffers those warps release, so an entry
+// is never rewritten before every warp has read it, and a waiter is never more than one phase
+// behind.)  An id of -1 ends the list.  When a CTA's list has ended it counts itself in sched[1]; the
+// last CTA to do so clears both words for the next launch that uses them.
+// ---------------------------------------------------------------------------
+constexpr int kItemRing = 8;
+
+// Producer, lane 0 only: hand item `id` (or -1) to the CTA as its n-th item.
+__device__ __forceinline__ void item_publish(uint64_t* bar_item, volatile int* ring, int n, int id) {
+    ring[n % kItemRing] = id;
+    mbar_arrive(&bar_item[n % kItemRing]);  // release: the id is visible to whoever sees the phase complete
+}
+// Any warp: the id of this CTA's n-th item, -1 at the end of the list or after a wait that gave up.
+__device__ __forceinline__ int item_get(uint64_t* bar_item, volatile int* ring, int n, volatile int* abort_flag,
+                                        int* status) {
+    if (!mbar_wait_warp(&bar_item[n % kItemRing], uint32_t(n / kItemRing) & 1, abort_flag, status, DEV_WAIT_TIMEOUT_LOAD))
+        return -1;
+    return ring[n % kItemRing];
+}
+// Producer, lane 0 only: the id of this CTA's n-th item (n >= 1) from the device-wide counter (ids below
+// n_ctas are the CTAs' first items).  Without a counter (sched == nullptr) the items are dealt statically
+// in rounds, every other round in reverse CTA order, so that the CTA that got the most expensive item
+// of one round gets the cheapest of the next.
+__device__ __forceinline__ int sched_fetch(int* sched, int n, int cta, int n_ctas) {
+    if (sched == nullptr) return n * n_ctas + ((n & 1) ? n_ctas - 1 - cta : cta);
+    return n_ctas + atomicAdd(&sched[0], 1);
+}
+// Producer, lane 0 only, after its last sched_fetch: count this CTA; the last one resets the counters.
+__device__ __forceinline__ void sched_finish(int* sched, int n_ctas) {
+    if (sched == nullptr) return;
+    __threadfence();
+    if (atomicAdd(&sched[1], 1) == n_ctas - 1) {
+        __threadfence();
+        sched[0] = 0;
+        sched[1] = 0;
+    }
 }
 
 // Descriptor offset (in the 16-byte units of the start-address field) of K step `ks` of a
@@ -348,7 +386,8 @@ __device__ long long g_probe[512];
         if ((cond) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (idx) < 512) \
             g_probe[(idx)] = clock64();                                                \
     } while (0)
-// Per-CTA trace: SM id and begin/end times (ns) of every CTA of a launch (first 8192 CTAs).
+// Per-CTA trace: SM id and begin/end times (ns) of the first 2048 CTAs of a launch, kept per kernel
+// (k = 0 forward, 1 dQ pass, 2 dK/dV pass).
 __device__ unsigned long long g_trace[8192 * 3];
 __device__ __forceinline__ unsigned long long b200attn_globaltimer() {
     unsigned long long t;
@@ -360,25 +399,25 @@ __device__ __forceinline__ unsigned b200attn_smid() {
     asm volatile("mov.u32 %0, %%smid;" : "=r"(r));
     return r;
 }
-#define B200ATTN_TRACE_BEGIN()                                                                      \
+#define B200ATTN_TRACE_BEGIN(k)                                                                     \
     do {                                                                                            \
-        const unsigned lin_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);       \
-        if (threadIdx.x == 0 && lin_ < 8192) {                                                      \
+        const unsigned lin_ = (k) * 2048 + blockIdx.x;                                              \
+        if (threadIdx.x == 0 && blockIdx.x < 2048) {                                                \
             g_trace[lin_ * 3 + 0] = b200attn_smid();                                                \
             g_trace[lin_ * 3 + 1] = b200attn_globaltimer();                                         \
         }                                                                                           \
     } while (0)
-#define B200ATTN_TRACE_END()                                                                        \
+#define B200ATTN_TRACE_END(k)                                                                       \
     do {                                                                                            \
-        const unsigned lin_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);       \
-        if (threadIdx.x == 0 && lin_ < 8192) g_trace[lin_ * 3 + 2] = b200attn_globaltimer();        \
+        const unsigned lin_ = (k) * 2048 + blockIdx.x;                                              \
+        if (threadIdx.x == 0 && blockIdx.x < 2048) g_trace[lin_ * 3 + 2] = b200attn_globaltimer();  \
     } while (0)
 #else
-#define B200ATTN_TRACE_BEGIN() \
-    do {                       \
+#define B200ATTN_TRACE_BEGIN(k) \
+    do {                        \
     } while (0)
-#define B200ATTN_TRACE_END() \
-    do {                     \
+#define B200ATTN_TRACE_END(k) \
+    do {                      \
     } while (0)
 #define B200ATTN_STAMP(cond, idx) \
     do {                          \

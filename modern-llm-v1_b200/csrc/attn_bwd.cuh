@@ -46,7 +46,11 @@ struct BwdParams {
     uint16_t* dq;           // q layout
     long long q_st, q_sh, q_sb;  // element strides of the q layout: token, head, batch
     int* status;
-    int* sched;  // two words of the device-wide item counter of the persistent dQ pass (see ptx.cuh)
+    uint16_t* dk;           // k layout
+    uint16_t* dv;           // k layout
+    long long k_st, k_sh, k_sb;  // element strides of the k layout: token, head, batch
+    int* sched;   // two words of the device-wide item counter of the persistent dQ pass (see ptx.cuh), or nullptr
+    int* sched2;  // the same for the dK/dV pass
 };
 
 template <int D>
@@ -57,12 +61,14 @@ struct BwdCfg {
     static constexpr int kBoxBytes = 128 * 64 * 2;
     static constexpr int kBoxes = D / 64;
     static constexpr int kVecBytes = kStages * 2 * 512;  // per stage (lse2, dvec) of 128 rows
-    static constexpr int kBarBytes = 256;
+    static constexpr int kBarBytes = 512;
+    static constexpr int kKvBufs = kDoubleS ? 2 : 1;       // K/V tile pairs in shared memory (the next item's are prefetched)
+    static constexpr int kOutTiles = kDoubleS ? 2 : 0;     // staging tiles for dV, dK (D = 128 has no room: direct stores)
     static constexpr int kParts = 4;                       // compute warpgroups: each owns 128 / kParts score columns
     static constexpr int kPartCols = 128 / kParts;         // 32
     static constexpr int kComputeThreads = 128 * kParts;   // 512
     static constexpr int kThreads = kComputeThreads + 64;  // + producer warp + MMA warp
-    static constexpr int kSmemBytes = (2 + 2 * kStages) * kTileBytes + kVecBytes + kBarBytes + 1024;
+    static constexpr int kSmemBytes = (2 * kKvBufs + 2 * kStages + kOutTiles) * kTileBytes + kVecBytes + kBarBytes + 1024;
     static constexpr int kTmemCols = 512;
     static constexpr int kColS0 = 0;
     static constexpr int kColS1 = kDoubleS ? 128 : 0;
@@ -202,7 +208,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     auto get_item = [&](int n) { return item_get(bar_item, item_ring, n, abort_flag, p.status); };
 
     B200ATTN_TRACE_BEGIN(1);
-    grid_dep_launch();
     if (warp == Cfg::kProducerWarp && lane == 0) {
         tma_prefetch_desc(&tmQ);
         tma_prefetch_desc(&tmK);
@@ -573,10 +578,10 @@ attn_bwd_dq_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     uint64_t* bar_q = bars + 0;
     uint64_t* bar_s_full = bars + 1;   // [2] one per S buffer
     uint64_t* bar_dp_full = bars + 3;
-    uint64_t* bar_ds_full = bars + 4;
-    uint64_t* bar_acc = bars + 5;
-    uint64_t* bar_kv_full = bars + 6;          // [NST]
-    uint64_t* bar_kv_free = bars + 6 + NST;    // [NST]
+    uint64_t* bar_ds_full = bars + 4;  // [2] by tile parity (a parity wait must never be two phases behind)
+    uint64_t* bar_acc = bars + 6;
+    uint64_t* bar_kv_full = bars + 7;          // [NST]
+    uint64_t* bar_kv_free = bars + 7 + NST;    // [NST]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
 
@@ -602,7 +607,8 @@ attn_bwd_dq_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         mbar_init(&bar_s_full[0], 1);
         mbar_init(&bar_s_full[1], 1);
         mbar_init(bar_dp_full, 1);
-        mbar_init(bar_ds_full, 256);
+        mbar_init(&bar_ds_full[0], 256);
+        mbar_init(&bar_ds_full[1], 256);
         mbar_init(bar_acc, 1);
         for (int s = 0; s < NST; ++s) {
             mbar_init(&bar_kv_full[s], 1);
@@ -687,7 +693,7 @@ attn_bwd_dq_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         if (ok && DBL && n_kv > 1) ok = issue_s(1);
         for (int j = 0; j < n_kv && ok; ++j) {
             const int s = j % NST;
-            ok = mbar_wait_warp(bar_ds_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+            ok = mbar_wait_warp(&bar_ds_full[j & 1], uint32_t(j >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
             if (!ok) break;
             tc_fence_after_sync();
             if (elect_one()) {
@@ -790,7 +796,7 @@ attn_bwd_dq_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
             }
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(bar_ds_full);
+            mbar_arrive(&bar_ds_full[j & 1]);
         }
         if (ok) ok = mbar_wait(bar_acc, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
         ok = __all_sync(0xffffffffu, ok);
@@ -827,8 +833,12 @@ attn_bwd_dq_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 
 
 // ---------------------------------------------------------------------------------------
-// dK/dV pass: one CTA per (key tile, KV head, batch); loops over the query heads of the
-// group and, for each, over the query tiles at or below the diagonal.
+// dK/dV pass: persistent CTAs, one per SM.  An item is one 128-key tile of one (batch, KV head); its
+// units are the (query head of the group, 128-query tile at or below the diagonal) pairs, each a
+// 128 x 128 block of scores.  Items are ordered heaviest first (key tile 0 sees every query tile) and
+// handed out as described in ptx.cuh.  All pipelines run across item boundaries: the next item's K and V
+// tiles (second buffer, D = 64) and its first Q / dO tiles are loaded, and its first S^T and dP^T
+// products issued, while the compute warps still drain the accumulators of the previous item.
 // ---------------------------------------------------------------------------------------
 template <int D>
 __global__ void __launch_bounds__(BwdCfg<D>::kThreads, 1)
@@ -838,57 +848,47 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                      const BwdParams p) {
     using Cfg = BwdCfg<D>;
     constexpr int NST = Cfg::kStages;
+    constexpr int NKV = Cfg::kKvBufs;
     constexpr bool DBL = Cfg::kDoubleS;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sK = smem;
-    uint8_t* sV = sK + Cfg::kTileBytes;
-    uint8_t* sQ = sV + Cfg::kTileBytes;         // [NST]
+    uint8_t* sK = smem;                         // [NKV]
+    uint8_t* sV = sK + NKV * Cfg::kTileBytes;   // [NKV]
+    uint8_t* sQ = sV + NKV * Cfg::kTileBytes;   // [NST]
     uint8_t* sdO = sQ + NST * Cfg::kTileBytes;  // [NST]
-    float* sLse = reinterpret_cast<float*>(sdO + NST * Cfg::kTileBytes);  // [NST][128]
+    uint8_t* sOut = sdO + NST * Cfg::kTileBytes;  // [2] staging of dV and dK for the TMA store (D = 64 only)
+    float* sLse = reinterpret_cast<float*>(sOut + Cfg::kOutTiles * Cfg::kTileBytes);  // [NST][128]
     float* sDv = sLse + NST * 128;                                         // [NST][128]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sdO + NST * Cfg::kTileBytes + Cfg::kVecBytes);
-    uint64_t* bar_kv = bars + 0;
-    uint64_t* bar_s_full = bars + 1;  // [2]
-    uint64_t* bar_dp_full = bars + 3;
-    uint64_t* bar_pds_full = bars + 4;
-    uint64_t* bar_acc = bars + 5;
-    uint64_t* bar_dp_free = bars + 15;    // dP^T has been read into registers by every compute thread
-    uint64_t* bar_full = bars + 6;        // [NST]
-    uint64_t* bar_free = bars + 6 + NST;  // [NST]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 17);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sOut + Cfg::kOutTiles * Cfg::kTileBytes + Cfg::kVecBytes);
+    uint64_t* bar_kv = bars + 0;        // [2] per K/V buffer: K, V of an item have landed      (phase: item / NKV)
+    uint64_t* bar_kv_free = bars + 2;   // [2] per K/V buffer: every MMA reading them is done   (phase: item / NKV)
+    uint64_t* bar_s_full = bars + 4;    // [2] per S buffer                                      (phase: unit / 2 or unit)
+    uint64_t* bar_dp_full = bars + 6;   //                                                       (phase: unit)
+    uint64_t* bar_dp_free = bars + 7;   // dP^T has been read into registers                     (phase: unit)
+    uint64_t* bar_pds_full = bars + 8;  // [2] by unit parity: P^T and dS^T written              (phase: unit / 2)
+    uint64_t* bar_acc = bars + 10;      // accumulators of an item complete                      (phase: item)
+    uint64_t* bar_acc_free = bars + 11; // accumulators read by the epilogue                     (phase: item)
+    uint64_t* bar_full = bars + 12;        // [NST] Q, dO and the two row vectors of a unit have landed
+    uint64_t* bar_free = bars + 12 + NST;  // [NST]
+    uint64_t* bar_out_free = bars + 20;  // the TMA store of the previous item has read the staging tiles (phase: item)
+    uint64_t* bar_out_full = bars + 21;  // every compute thread has staged its part of dV / dK        (phase: item)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 19);
+    uint64_t* bar_item = bars + 24;     // [kItemRing] item ids handed out by the producer
+    volatile int* item_ring = reinterpret_cast<volatile int*>(bars + 24 + kItemRing);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr int kProducerWarp = Cfg::kParts * 4, kMmaWarp = Cfg::kParts * 4 + 1;
-    // 1-D grid ordered by work: key tile 0 has the most query tiles below it, so all its CTAs come first
+    // item id -> (key tile, KV head, batch); ids are ordered by work: key tile 0 has the most query tiles below it
     const int n_bh = p.B * p.Hkv;
-    const int kt = int(blockIdx.x) / n_bh;
-    const int hk = (int(blockIdx.x) % n_bh) % p.Hkv, b = (int(blockIdx.x) % n_bh) / p.Hkv;
-    const int k0 = kt * 128;
-    const int n_i = p.n_tiles - kt;  // query tiles kt .. n_tiles-1
-    B200ATTN_TRACE_BEGIN(2);
-    const int n_it = p.group * n_i;  // times the query heads of the group
+    const int n_items = p.n_tiles * n_bh;
+    auto item_kt = [&](int id) { return id / n_bh; };
+    auto item_hk = [&](int id) { return (id % n_bh) % p.Hkv; };
+    auto item_b = [&](int id) { return (id % n_bh) / p.Hkv; };
+    auto item_units = [&](int id) { return p.group * (p.n_tiles - item_kt(id)); };
+    auto get_item = [&](int n) { return item_get(bar_item, item_ring, n, abort_flag, p.status); };
 
-    grid_dep_launch();
-    if (tid == 0) {
-        mbar_init(bar_kv, 1);
-        mbar_init(&bar_s_full[0], 1);
-        mbar_init(&bar_s_full[1], 1);
-        mbar_init(bar_dp_full, 1);
-        mbar_init(bar_pds_full, Cfg::kComputeThreads);
-        mbar_init(bar_dp_free, Cfg::kComputeThreads);
-        mbar_init(bar_acc, 1);
-        for (int s = 0; s < NST; ++s) {
-            mbar_init(&bar_full[s], 1);
-            mbar_init(&bar_free[s], 1);
-        }
-        fence_mbar_init();
-    }
-    if (warp == kMmaWarp) {
-        tmem_alloc(tmem_slot, Cfg::kTmemCols);
-        tmem_relinquish();
-    }
+    B200ATTN_TRACE_BEGIN(2);
     if (warp == kProducerWarp && lane == 0) {
         tma_prefetch_desc(&tmK);
         tma_prefetch_desc(&tmV);
@@ -896,121 +896,221 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         tma_prefetch_desc(&tmdO);
         tma_prefetch_desc(&tmdK);
         tma_prefetch_desc(&tmdV);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bar_kv[i], 1);
+            mbar_init(&bar_kv_free[i], 1);
+            mbar_init(&bar_s_full[i], 1);
+            mbar_init(&bar_pds_full[i], Cfg::kComputeThreads);
+        }
+        mbar_init(bar_dp_full, 1);
+        mbar_init(bar_dp_free, Cfg::kComputeThreads);
+        mbar_init(bar_acc, 1);
+        mbar_init(bar_acc_free, Cfg::kComputeThreads);
+        mbar_init(bar_out_free, 1);
+        mbar_init(bar_out_full, Cfg::kComputeThreads);
+        for (int s = 0; s < NST; ++s) {
+            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_free[s], 1);
+        }
+        for (int i = 0; i < kItemRing; ++i) mbar_init(&bar_item[i], 1);
+        fence_mbar_init();
+        // Everything above touched no global memory.  From here on the previous kernel of the stream
+        // (the dQ pass, which writes the two per-row vectors) must have completed.
+        grid_dep_wait();
+        *abort_flag = *reinterpret_cast<volatile int*>(p.status);
     }
+    if (warp == kMmaWarp) {
+        tmem_alloc(tmem_slot, Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    grid_dep_wait();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    // Everything above touched no global memory.  From here on the previous kernel of the stream
-    // (the dQ pass, which writes the two per-row vectors) must have completed.
-    grid_dep_wait();
-    if (tid == 0) *abort_flag = *reinterpret_cast<volatile int*>(p.status);
-    __syncthreads();
 
     if (*abort_flag != 0) {
         // an earlier CTA already failed: fall through to the teardown
     } else if (warp == kProducerWarp) {
         // ------------------------------------------------------------------ producer (whole warp, one lane issues)
-        if (elect_one()) {
-            mbar_arrive_expect_tx(bar_kv, 2 * Cfg::kTileBytes);
-#pragma unroll
-            for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
-                tma_load_4d(sK + bx * Cfg::kBoxBytes, &tmK, bar_kv, bx * 64, k0, hk, b);
-                tma_load_4d(sV + bx * Cfg::kBoxBytes, &tmV, bar_kv, bx * 64, k0, hk, b);
-            }
+        int u = 0;  // units issued so far by this CTA (ring position)
+        bool ok = true;
+        int id = blockIdx.x;  // the first item needs no fetch
+        int id_next = 0;      // lane 0: the id fetched for the next item
+        if (lane == 0) {
+            item_publish(bar_item, item_ring, 0, id);
+            id_next = sched_fetch(p.sched2, 1, int(blockIdx.x), int(gridDim.x));
         }
         __syncwarp();
-        for (int it = 0; it < n_it; ++it) {
-            const int s = it % NST;
-            const int h = hk * p.group + it / n_i;
-            const int i = kt + it % n_i;
-            if (it >= NST &&
-                !mbar_wait_warp(&bar_free[s], ((it / NST) - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE))
-                break;
+        for (int n = 0; ok; ++n) {
+            const int kt = item_kt(id), hk = item_hk(id), b = item_b(id), k0 = kt * 128;
+            const int n_i = p.n_tiles - kt, n_it = p.group * n_i;
+            const int kb = n % NKV;
+            if (n >= NKV) ok = mbar_wait_warp(&bar_kv_free[kb], uint32_t(n / NKV - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
+            if (!ok) break;
             if (elect_one()) {
-                mbar_arrive_expect_tx(&bar_full[s], 2 * Cfg::kTileBytes + 1024);
+                mbar_arrive_expect_tx(&bar_kv[kb], 2 * Cfg::kTileBytes);
 #pragma unroll
                 for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
-                    tma_load_4d(sQ + s * Cfg::kTileBytes + bx * Cfg::kBoxBytes, &tmQ, &bar_full[s], bx * 64, i * 128, h,
-                                b);
-                    tma_load_4d(sdO + s * Cfg::kTileBytes + bx * Cfg::kBoxBytes, &tmdO, &bar_full[s], bx * 64, i * 128,
-                                h, b);
+                    tma_load_4d(sK + kb * Cfg::kTileBytes + bx * Cfg::kBoxBytes, &tmK, &bar_kv[kb], bx * 64, k0, hk, b);
+                    tma_load_4d(sV + kb * Cfg::kTileBytes + bx * Cfg::kBoxBytes, &tmV, &bar_kv[kb], bx * 64, k0, hk, b);
                 }
-                const size_t voff = (size_t(b) * p.Hq + h) * p.Tpad + size_t(i) * 128;
-                bulk_load_1d(sLse + s * 128, p.lse2 + voff, 512, &bar_full[s]);
-                bulk_load_1d(sDv + s * 128, p.dvec + voff, 512, &bar_full[s]);
             }
             __syncwarp();
+            // the next item is taken and announced shortly before this item's loads end, but not before the
+            // ring has been filled for this item
+            const int j_next = max(min(n_it, NST) - 1, n_it - 2);
+            int id_new = n_items;
+            for (int it = 0; it < n_it; ++it, ++u) {
+                const int s = u % NST;
+                const int h = hk * p.group + it / n_i;
+                const int i = kt + it % n_i;
+                if (u >= NST) ok = mbar_wait_warp(&bar_free[s], uint32_t(u / NST - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
+                if (!ok) break;
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(&bar_full[s], 2 * Cfg::kTileBytes + 1024);
+#pragma unroll
+                    for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
+                        tma_load_4d(sQ + s * Cfg::kTileBytes + bx * Cfg::kBoxBytes, &tmQ, &bar_full[s], bx * 64, i * 128, h,
+                                    b);
+                        tma_load_4d(sdO + s * Cfg::kTileBytes + bx * Cfg::kBoxBytes, &tmdO, &bar_full[s], bx * 64, i * 128,
+                                    h, b);
+                    }
+                    const size_t voff = (size_t(b) * p.Hq + h) * p.Tpad + size_t(i) * 128;
+                    bulk_load_1d(sLse + s * 128, p.lse2 + voff, 512, &bar_full[s]);
+                    bulk_load_1d(sDv + s * 128, p.dvec + voff, 512, &bar_full[s]);
+                }
+                __syncwarp();
+                if (it == j_next) {
+                    id_new = __shfl_sync(0xffffffffu, id_next, 0);
+                    if (lane == 0) {
+                        item_publish(bar_item, item_ring, n + 1, id_new < n_items ? id_new : -1);
+                        if (id_new < n_items) id_next = sched_fetch(p.sched2, n + 2, int(blockIdx.x), int(gridDim.x));
+                    }
+                    __syncwarp();
+                }
+            }
+            if (!ok || id_new >= n_items) break;
+            id = id_new;
         }
+        if (ok && lane == 0) sched_finish(p.sched2, int(gridDim.x));
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------------ MMA issuer (whole warp, one lane issues)
         constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
         constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
-        const uint64_t k_desc = kmajor_desc<D>(sK), v_desc = kmajor_desc<D>(sV);
-        bool ok = mbar_wait_warp(bar_kv, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-        auto issue_s = [&](int it) -> bool {  // S^T(it) = K Q^T
-            const int s = it % NST;
-            if (!mbar_wait_warp(&bar_full[s], (it / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD)) return false;
+        // This CTA's units are numbered u = 0, 1, ... across all its items: ring stage u % NST, S buffer u & 1
+        // (two S buffers).  Three cursors walk that sequence: S^T = K Q^T runs two units ahead (one with a
+        // single S buffer) and dP^T = V dO^T one unit ahead of the products into the accumulators.
+        struct Cursor {
+            int n, it, n_it, u;  // items before this one on this CTA, unit in item, units of item (0: list ended), unit number
+        };
+        bool ok = true;
+        // `wait`: the first cursor to reach an item waits for its id; the others find it in the ring
+        auto cursor_start = [&](bool wait) {
+            const int id = wait ? get_item(0) : item_ring[0];
+            return Cursor{0, 0, id >= 0 ? item_units(id) : 0, 0};
+        };
+        auto cursor_next = [&](Cursor& c, bool wait) {
+            ++c.u;
+            if (++c.it == c.n_it) {
+                ++c.n;
+                c.it = 0;
+                const int id = wait ? get_item(c.n) : item_ring[c.n % kItemRing];
+                c.n_it = id >= 0 ? item_units(id) : 0;
+            }
+        };
+        auto issue_s = [&](const Cursor& c) {  // S^T(u) = K Q^T
+            const int s = c.u % NST, kb = c.n % NKV;
+            if (c.it == 0) ok = mbar_wait_warp(&bar_kv[kb], uint32_t(c.n / NKV) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+            if (ok) ok = mbar_wait_warp(&bar_full[s], uint32_t(c.u / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+            if (!ok) return;
             tc_fence_after_sync();
-            const int buf = DBL ? (it & 1) : 0;
+            const int buf = DBL ? (c.u & 1) : 0;
             if (elect_one()) {
-                issue_ss_over_headdim<D>(tmem + Cfg::col_s(buf), k_desc, kmajor_desc<D>(sQ + s * Cfg::kTileBytes), idesc_s);
+                issue_ss_over_headdim<D>(tmem + Cfg::col_s(buf), kmajor_desc<D>(sK + kb * Cfg::kTileBytes),
+                                         kmajor_desc<D>(sQ + s * Cfg::kTileBytes), idesc_s);
                 umma_commit(&bar_s_full[buf]);
             }
             __syncwarp();
-            return true;
         };
-        auto issue_dp = [&](int it) {  // dP^T(it) = V dO^T; the loads of `it` are known to be complete
-            const int s = it % NST;
+        // dP^T(u) = V dO^T; the loads of the unit are known to be complete (S^T of the unit was issued before).
+        // After the item's last unit no MMA reads its K and V any more.
+        auto issue_dp = [&](const Cursor& c) {
+            const int s = c.u % NST, kb = c.n % NKV;
             if (elect_one()) {
-                issue_ss_over_headdim<D>(tmem + Cfg::kColDP, v_desc, kmajor_desc<D>(sdO + s * Cfg::kTileBytes), idesc_s);
+                issue_ss_over_headdim<D>(tmem + Cfg::kColDP, kmajor_desc<D>(sV + kb * Cfg::kTileBytes),
+                                         kmajor_desc<D>(sdO + s * Cfg::kTileBytes), idesc_s);
                 umma_commit(bar_dp_full);
+                if (c.it + 1 == c.n_it) umma_commit(&bar_kv_free[kb]);
             }
             __syncwarp();
         };
-        if (ok) ok = issue_s(0);
-        if (ok) issue_dp(0);
-        if (ok && DBL && n_it > 1) ok = issue_s(1);
-        for (int it = 0; it < n_it && ok; ++it) {
-            const int s = it % NST;
-            const int buf = DBL ? (it & 1) : 0;
-            // dP^T of the next iteration as soon as the compute warps have read this one into registers
+        Cursor cs = cursor_start(true);
+        Cursor cd = cs, ca = cs;
+        if (cs.n_it > 0) {
+            issue_s(cs);
+            cursor_next(cs, true);
+            if (ok) {
+                issue_dp(cd);
+                cursor_next(cd, false);
+            }
+            if (ok && DBL && cs.n_it > 0) {
+                issue_s(cs);
+                cursor_next(cs, true);
+            }
+        }
+        int n_done = 0;  // items whose accumulators have been completed
+        while (ok && ca.n_it > 0) {
+            const int s = ca.u % NST;
+            const int buf = DBL ? (ca.u & 1) : 0;
+            // dP^T of the next unit as soon as the compute warps have read this one into registers
             // (dS^T is written next to P^T inside the S buffer, so the dP block is free): the MMA round trip
-            // runs under their arithmetic.  (With a single S buffer, D = 128, the loads of the next iteration
+            // runs under their arithmetic.  (With a single S buffer, D = 128, the loads of the next unit
             // may still be in flight: there dP^T follows S^T below instead.)
-            if (DBL && it + 1 < n_it) {
-                ok = mbar_wait_warp(bar_dp_free, it & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+            if (DBL && cd.n_it > 0) {
+                ok = mbar_wait_warp(bar_dp_free, uint32_t(ca.u) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
                 if (!ok) break;
                 tc_fence_after_sync();
-                issue_dp(it + 1);
+                issue_dp(cd);
+                cursor_next(cd, false);
             }
-            ok = mbar_wait_warp(bar_pds_full, it & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+            ok = mbar_wait_warp(&bar_pds_full[ca.u & 1], uint32_t(ca.u >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
             if (!ok) break;
-            B200ATTN_STAMP(lane == 0, 200 + 4 * it);
+            B200ATTN_STAMP(lane == 0, 16 + 8 * ca.u + 4);
+            // the accumulators belong to the previous item's epilogue until it has read them
+            if (ca.it == 0 && ca.n > 0) {
+                ok = mbar_wait_warp(bar_acc_free, uint32_t(ca.n - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+                if (!ok) break;
+            }
             tc_fence_after_sync();
             if (elect_one()) {
                 // dV += P^T dO ; dK += dS^T Q   (P^T and dS^T sit side by side in S buffer `buf`)
                 issue_ts_over_rows<D>(tmem + Cfg::kColAcc0, tmem + Cfg::col_s(buf),
-                                      mnmajor_desc<D>(sdO + s * Cfg::kTileBytes), idesc_acc, it > 0);
+                                      mnmajor_desc<D>(sdO + s * Cfg::kTileBytes), idesc_acc, ca.it > 0);
                 issue_ts_over_rows<D>(tmem + Cfg::kColAcc1, tmem + Cfg::col_s(buf) + Cfg::kPartCols / 2,
-                                      mnmajor_desc<D>(sQ + s * Cfg::kTileBytes), idesc_acc, it > 0);
+                                      mnmajor_desc<D>(sQ + s * Cfg::kTileBytes), idesc_acc, ca.it > 0);
                 umma_commit(&bar_free[s]);
+                if (ca.it + 1 == ca.n_it) umma_commit(bar_acc);
             }
             __syncwarp();
-            B200ATTN_STAMP(lane == 0, 201 + 4 * it);
-            if (!DBL && it + 1 < n_it) {
-                ok = issue_s(it + 1);
+            B200ATTN_STAMP(lane == 0, 16 + 8 * ca.u + 5);
+            if (ca.it + 1 == ca.n_it) ++n_done;
+            if (!DBL && cs.n_it > 0) {
+                issue_s(cs);
+                cursor_next(cs, true);
                 if (!ok) break;
-                issue_dp(it + 1);
+                issue_dp(cd);
+                cursor_next(cd, false);
             }
-            if (DBL && it + 2 < n_it) {
-                ok = issue_s(it + 2);
-                if (!ok) break;
+            if (DBL && cs.n_it > 0) {
+                issue_s(cs);
+                cursor_next(cs, true);
             }
-            B200ATTN_STAMP(lane == 0, 202 + 4 * it);
+            B200ATTN_STAMP(lane == 0, 16 + 8 * ca.u + 6);
+            cursor_next(ca, false);
         }
-        if (elect_one()) umma_commit(bar_acc);
-        __syncwarp();
+        // nothing may be in flight when TMEM is freed: the last commit covers every MMA issued above
+        if (ok && n_done > 0) mbar_wait_warp(bar_acc, uint32_t(n_done - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
     } else {
         // ------------------------------------------------------------------ compute
         const int w4 = warp & 3, part = warp >> 2;
@@ -1018,99 +1118,161 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         const uint32_t lane_base = uint32_t(w4 * 32) << 16;
         const int c0 = part * Cfg::kPartCols;  // first query column of this thread's part
         bool ok = true;
-        for (int it = 0; it < n_it; ++it) {
-            const int s = it % NST;
-            const int buf = DBL ? (it & 1) : 0;
-            const uint32_t s_par = DBL ? ((it >> 1) & 1) : (it & 1);
-            const bool diag = (it % n_i) == 0;
-            ok = mbar_wait_warp(&bar_s_full[buf], s_par, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
-            if (!ok) break;
-            B200ATTN_STAMP(tid == 0, 8 + 4 * it);
-            tc_fence_after_sync();
-            const float4* lse4 = reinterpret_cast<const float4*>(sLse + s * 128 + c0);
-            const float4* dv4 = reinterpret_cast<const float4*>(sDv + s * 128 + c0);
-            // phase A: P^T from S^T (kept in registers and stored over S^T as BF16)
-            float pr[32];
-            {
-                uint32_t sv[32], pk[16];
-                tmem_ld_x32(tmem + lane_base + Cfg::col_s(buf) + c0, sv);
-                tmem_wait_ld();
+        int u = 0, n = 0;
+        for (int id; ok && (id = get_item(n)) >= 0; ++n) {
+            const int n_i = p.n_tiles - item_kt(id);
+            // units of the item: for each query head of the group, the query tiles from the diagonal down
+            for (int it = p.group * n_i, i_in = 0; it > 0; --it, ++u, i_in = (i_in + 1 == n_i ? 0 : i_in + 1)) {
+                const int s = u % NST;
+                const int buf = DBL ? (u & 1) : 0;
+                const uint32_t s_par = DBL ? ((u >> 1) & 1) : (u & 1);
+                const bool diag = i_in == 0;
+                ok = mbar_wait_warp(&bar_s_full[buf], s_par, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+                if (!ok) break;
+                B200ATTN_STAMP(tid == 0, 16 + 8 * u + 0);
+                tc_fence_after_sync();
+                const float4* lse4 = reinterpret_cast<const float4*>(sLse + s * 128 + c0);
+                const float4* dv4 = reinterpret_cast<const float4*>(sDv + s * 128 + c0);
+                // phase A: P^T from S^T (kept in registers and stored over S^T as BF16), 16 columns at a time
+                float pr[32];
 #pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    const float4 l4 = lse4[g];
-                    pr[g * 4 + 0] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 0]), p.scale_log2, -l4.x));
-                    pr[g * 4 + 1] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 1]), p.scale_log2, -l4.y));
-                    pr[g * 4 + 2] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 2]), p.scale_log2, -l4.z));
-                    pr[g * 4 + 3] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 3]), p.scale_log2, -l4.w));
+                for (int hh = 0; hh < 2; ++hh) {
+                    uint32_t sv[16], pk[8];
+                    tmem_ld_x16(tmem + lane_base + Cfg::col_s(buf) + c0 + hh * 16, sv);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const float4 l4 = lse4[hh * 4 + g];
+                        float* q = &pr[hh * 16 + g * 4];
+                        q[0] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 0]), p.scale_log2, -l4.x));
+                        q[1] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 1]), p.scale_log2, -l4.y));
+                        q[2] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 2]), p.scale_log2, -l4.z));
+                        q[3] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 3]), p.scale_log2, -l4.w));
+                    }
+                    if (diag) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (c0 + hh * 16 + i < row) pr[hh * 16 + i] = 0.f;  // query above the key: masked
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) pk[i] = pack_bf16x2(pr[hh * 16 + 2 * i], pr[hh * 16 + 2 * i + 1]);
+                    tmem_st_x8(tmem + lane_base + Cfg::col_s(buf) + c0 + hh * 8, pk);
                 }
-                if (diag) {
+                B200ATTN_STAMP(tid == 0, 16 + 8 * u + 1);
+                ok = mbar_wait_warp(bar_dp_full, uint32_t(u) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+                if (!ok) break;
+                B200ATTN_STAMP(tid == 0, 16 + 8 * u + 2);
+                tc_fence_after_sync();
+                // phase B: dS^T = P^T (dP^T - D), stored as BF16 next to P^T in the S buffer
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (c0 + i < row) pr[i] = 0.f;  // query above the key: masked
+                for (int hh = 0; hh < 2; ++hh) {
+                    uint32_t dp[16], pk[8];
+                    tmem_ld_x16(tmem + lane_base + Cfg::kColDP + c0 + hh * 16, dp);
+                    tmem_wait_ld();
+                    if (hh == 1) {
+                        tc_fence_before_sync();
+                        mbar_arrive(bar_dp_free);  // dP^T is in registers: the next product may overwrite the block
+                    }
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const float4 d4 = dv4[hh * 4 + g];
+                        const float* q = &pr[hh * 16 + g * 4];
+                        pk[g * 2 + 0] = pack_bf16x2(q[0] * (__uint_as_float(dp[g * 4 + 0]) - d4.x),
+                                                    q[1] * (__uint_as_float(dp[g * 4 + 1]) - d4.y));
+                        pk[g * 2 + 1] = pack_bf16x2(q[2] * (__uint_as_float(dp[g * 4 + 2]) - d4.z),
+                                                    q[3] * (__uint_as_float(dp[g * 4 + 3]) - d4.w));
+                    }
+                    tmem_st_x8(tmem + lane_base + Cfg::col_s(buf) + c0 + Cfg::kPartCols / 2 + hh * 8, pk);
                 }
-#pragma unroll
-                for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(pr[2 * i], pr[2 * i + 1]);
-                tmem_st_x16(tmem + lane_base + Cfg::col_s(buf) + c0, pk);
-            }
-            ok = mbar_wait_warp(bar_dp_full, it & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
-            if (!ok) break;
-            B200ATTN_STAMP(tid == 0, 10 + 4 * it);
-            tc_fence_after_sync();
-            // phase B: dS^T = P^T (dP^T - D), stored as BF16 next to P^T in the S buffer
-            {
-                uint32_t dp[32], pk[16];
-                tmem_ld_x32(tmem + lane_base + Cfg::kColDP + c0, dp);
-                tmem_wait_ld();
+                tmem_wait_st();
                 tc_fence_before_sync();
-                mbar_arrive(bar_dp_free);  // dP^T is in registers: the next product may overwrite the block
-#pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    const float4 d4 = dv4[g];
-                    pk[g * 2 + 0] = pack_bf16x2(pr[g * 4 + 0] * (__uint_as_float(dp[g * 4 + 0]) - d4.x),
-                                                pr[g * 4 + 1] * (__uint_as_float(dp[g * 4 + 1]) - d4.y));
-                    pk[g * 2 + 1] = pack_bf16x2(pr[g * 4 + 2] * (__uint_as_float(dp[g * 4 + 2]) - d4.z),
-                                                pr[g * 4 + 3] * (__uint_as_float(dp[g * 4 + 3]) - d4.w));
-                }
-                tmem_st_x16(tmem + lane_base + Cfg::col_s(buf) + c0 + Cfg::kPartCols / 2, pk);
+                mbar_arrive(&bar_pds_full[u & 1]);
+                B200ATTN_STAMP(tid == 0, 16 + 8 * u + 3);
             }
-            tmem_wait_st();
-            tc_fence_before_sync();
-            mbar_arrive(bar_pds_full);
-            B200ATTN_STAMP(tid == 0, 9 + 4 * it);
-        }
-        if (ok) ok = mbar_wait(bar_acc, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
+            if (!ok) break;
+            // epilogue of the item: parts 0,1 write dV, parts 2,3 write dK (times scale); each part takes D / 2
+            // of the accumulator's columns of its key row, which is contiguous in global memory
+            B200ATTN_STAMP(tid == 0, 460 + 4 * n + 0);
+            ok = mbar_wait_warp(bar_acc, uint32_t(n) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+            if (!ok) break;
+            B200ATTN_STAMP(tid == 0, 460 + 4 * n + 1);
             tc_fence_after_sync();
-            // parts 0,1 drain dV into the first Q stage, parts 2,3 drain dK (times scale) into the first dO
-            // stage; each part takes D / 2 of the accumulator's columns
+            // (the values below are derived from copies the compiler cannot see through, so that it does not
+            // compute them ahead of the unit loop and keep them in registers there)
+            int part_e = part, id_e = id;
+            asm volatile("" : "+r"(part_e), "+r"(id_e));
             constexpr int kHalfParts = Cfg::kParts / 2;
             constexpr int kColsPerPart = D / kHalfParts;
-            const bool is_dk = part >= kHalfParts;
-            uint8_t* tile = is_dk ? sdO : sQ;
+            const bool is_dk = part_e >= kHalfParts;
             const uint32_t acc = is_dk ? Cfg::kColAcc1 : Cfg::kColAcc0;
             const float mul = is_dk ? p.scale : 1.f;
-            const int col0 = (part % kHalfParts) * kColsPerPart;
+            const int col0 = (part_e % kHalfParts) * kColsPerPart;
+            const int k0 = item_kt(id_e) * 128;
+            if constexpr (Cfg::kOutTiles > 0) {
+                // through shared memory and a TMA store, so that no compute thread waits on the memory system:
+                // the previous item's store must have read the staging tiles before they are rewritten
+                // (mbarriers with bounded waits rather than bar.sync: a warp that has given up never arrives)
+                if (tid == 0) {
+                    tma_store_wait_read0();
+                    mbar_arrive(bar_out_free);
+                }
+                ok = mbar_wait_warp(bar_out_free, uint32_t(n) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
+                if (!ok) break;
 #pragma unroll
-            for (int c = 0; c < kColsPerPart / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld_x32(tmem + lane_base + acc + col0 + c * 32, v);
-                tmem_wait_ld();
-                stage_row_chunk<D>(tile, row, col0 + c * 32, v, mul);
-            }
-            fence_proxy_async_smem();
-        }
-        tc_fence_before_sync();
-        named_bar_sync(1, Cfg::kComputeThreads);
-        if (ok && tid == 0) {
+                for (int c = 0; c < kColsPerPart / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_x32(tmem + lane_base + acc + col0 + c * 32, v);
+                    tmem_wait_ld();
+                    if (c + 1 == kColsPerPart / 32) {
+                        tc_fence_before_sync();
+                        mbar_arrive(bar_acc_free);  // the MMA warp may start the next item's accumulation
+                    }
+                    stage_row_chunk<D>(sOut + (is_dk ? Cfg::kTileBytes : 0), row, col0 + c * 32, v, mul);
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(bar_out_full);
+                if (warp == 0) {
+                    ok = mbar_wait_warp(bar_out_full, uint32_t(n) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
+                    if (!ok) break;
+                }
+                if (tid == 0) {
 #pragma unroll
-            for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
-                tma_store_4d(&tmdV, sQ + bx * Cfg::kBoxBytes, bx * 64, k0, hk, b);
-                tma_store_4d(&tmdK, sdO + bx * Cfg::kBoxBytes, bx * 64, k0, hk, b);
+                    for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
+                        tma_store_4d(&tmdV, sOut + bx * Cfg::kBoxBytes, bx * 64, k0, item_hk(id_e), item_b(id_e));
+                        tma_store_4d(&tmdK, sOut + Cfg::kTileBytes + bx * Cfg::kBoxBytes, bx * 64, k0, item_hk(id_e), item_b(id_e));
+                    }
+                    tma_store_commit();
+                }
+            } else {
+                const bool in_range = k0 + row < p.T;
+                uint16_t* out = (is_dk ? p.dk : p.dv) + size_t(item_b(id_e)) * p.k_sb + size_t(item_hk(id_e)) * p.k_sh +
+                                size_t(k0 + row) * p.k_st + col0;
+#pragma unroll
+                for (int c = 0; c < kColsPerPart / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_x32(tmem + lane_base + acc + col0 + c * 32, v);
+                    tmem_wait_ld();
+                    if (c + 1 == kColsPerPart / 32) {
+                        tc_fence_before_sync();
+                        mbar_arrive(bar_acc_free);  // the MMA warp may start the next item's accumulation
+                    }
+                    if (in_range) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            uint4 w;
+                            w.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]) * mul, __uint_as_float(v[g * 8 + 1]) * mul);
+                            w.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * mul, __uint_as_float(v[g * 8 + 3]) * mul);
+                            w.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * mul, __uint_as_float(v[g * 8 + 5]) * mul);
+                            w.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * mul, __uint_as_float(v[g * 8 + 7]) * mul);
+                            *reinterpret_cast<uint4*>(out + c * 32 + g * 8) = w;
+                        }
+                    }
+                }
             }
-            tma_store_commit();
-            tma_store_wait_read0();
+            B200ATTN_STAMP(tid == 0, 460 + 4 * n + 2);
         }
+        // the staging tiles must outlive the last store's reads
+        if (Cfg::kOutTiles > 0 && tid == 0) tma_store_wait_read0();
     }
 
     tc_fence_before_sync();

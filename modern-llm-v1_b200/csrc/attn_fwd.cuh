@@ -54,11 +54,7 @@ struct FwdCfg {
     static constexpr int kSmemBytes = kQBufs * kQTileBytes + 2 * kStages * kKVTileBytes + kBarBytes + 1024;
     static constexpr int kTmemCols = 256;
     // S buffers: three for D = 64 (all 256 columns used), two for D = 128
-#ifdef B200ATTN_FWD_SBUFS
-    static constexpr int kSBufs = B200ATTN_FWD_SBUFS;
-#else
     static constexpr int kSBufs = (D == 64) ? 3 : 2;
-#endif
     static constexpr int kColO = kSBufs * 64;
     __host__ __device__ static constexpr int col_s(int buf) { return buf * 64; }
 };
@@ -113,7 +109,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     B200ATTN_TRACE_BEGIN(0);
     // Set-up with one CTA-wide barrier: one lane of the producer warp initialises every mbarrier while
     // the MMA warp allocates TMEM; nothing touches global memory before grid_dep_wait().
-    grid_dep_launch();
     if (warp == 4 && lane == 0) {
         tma_prefetch_desc(&tmQ);
         tma_prefetch_desc(&tmK);
@@ -187,11 +182,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             // The next item is taken, announced and its Q requested a few tiles before this item's loads end
             // (late, so that a CTA commits itself to little work ahead, but not before the ring has been
             // filled for this item); with one Q buffer, after this item's last tile (it is free only then).
-#ifdef B200ATTN_EARLY_FETCH
-            const int j_next = NQB > 1 ? min(n_kv, NST) - 1 : n_kv - 1;
-#else
             const int j_next = NQB > 1 ? max(min(n_kv, NST) - 1, n_kv - 3) : n_kv - 1;
-#endif
             int id_new = n_items;
             for (int j = 0; j < n_kv; ++j, ++g) {
                 const int s = g % NST;
@@ -320,12 +311,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         // Epilogue of one item: O / l -> BF16 -> global memory, logsumexp.  (bar_pv_done cannot be used for
         // "O is complete": P V of the last TWO tiles may still be in flight, and a parity wait is only
         // unambiguous when the waiter is at most one phase behind; bar_o_done completes once per item.)
-        auto epilogue = [&](int n_item, int q0, int b, int h, float m_ref, float l) -> bool {
+        auto epilogue = [&](int n_item, int id, float m_ref, float l) -> bool {
             B200ATTN_STAMP(tid == 0, 400 + 4 * n_item + 0);
             if (!mbar_wait_warp(bar_o_done, uint32_t(n_item) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA)) return false;
             B200ATTN_STAMP(tid == 0, 400 + 4 * n_item + 1);
             tc_fence_after_sync();
             const float inv_l = 1.f / l;
+            const int q0 = item_qt(id) * 128, b = item_b(id), h = item_h(id);
             const bool in_range = q0 + row < p.T;
             uint16_t* orow = p.o + size_t(b) * p.o_sb + size_t(h) * p.o_sh + size_t(q0 + row) * p.o_st;
             // every thread owns one contiguous row of D elements, written 64 columns at a time
@@ -346,6 +338,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     tc_fence_before_sync();
                     mbar_arrive(bar_o_free);
                 }
+                B200ATTN_STAMP(tid == 0, 440 + 4 * n_item + 0);
                 if (in_range) {
 #pragma unroll
                     for (int c = 0; c < 8; ++c)
@@ -353,6 +346,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                             make_uint4(ow[c * 4], ow[c * 4 + 1], ow[c * 4 + 2], ow[c * 4 + 3]);
                 }
             }
+            B200ATTN_STAMP(tid == 0, 440 + 4 * n_item + 1);
             if (in_range) p.lse[(size_t(b) * p.Hq + h) * p.T + q0 + row] = m_ref * p.scale + logf(l);
             B200ATTN_STAMP(tid == 0, 400 + 4 * n_item + 2);
             return true;
@@ -360,7 +354,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         // The epilogue of an item is deferred until the softmax of the next item's first tile has been handed
         // to the MMA warp: the wait for the item's last P V then overlaps useful work.
         bool pending = false;
-        int pend_q0 = 0, pend_b = 0, pend_h = 0;
+        int pend_id = 0;
         float pend_m = 0.f, pend_l = 1.f;
         int g = 0, n = 0;
         for (int id; ok && (id = get_item(n)) >= 0; ++n) {
@@ -444,16 +438,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 mbar_arrive(&bar_p_full[g % NSB]);
                 B200ATTN_STAMP(tid == 0, 16 + 8 * g + 2);
                 if (j == 0 && pending) {
-                    ok = epilogue(n - 1, pend_q0, pend_b, pend_h, pend_m, pend_l);
+                    ok = epilogue(n - 1, pend_id, pend_m, pend_l);
                     pending = false;
                     if (!ok) break;
                 }
             }
             if (!ok) break;
             pending = true;
-            pend_q0 = q0, pend_b = b, pend_h = h, pend_m = m_ref, pend_l = l;
+            pend_id = id, pend_m = m_ref, pend_l = l;
         }
-        if (ok && pending) epilogue(n - 1, pend_q0, pend_b, pend_h, pend_m, pend_l);
+        if (ok && pending) epilogue(n - 1, pend_id, pend_m, pend_l);
         tc_fence_before_sync();
     }
 

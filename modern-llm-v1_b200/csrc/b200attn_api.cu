@@ -263,8 +263,13 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk64, const CUtensorMap
         return B200ATTN_ERR_CUDA;
     }
     record_bwd_event(1, st);
-    if (launch_pdl(attn_bwd_dkdv_kernel<D>, (unsigned)(p.n_tiles * p.Hkv * p.B), BwdCfg<D>::kThreads,
-                   BwdCfg<D>::kSmemBytes, st, tk, tv, tq, tdo, tdk, tdv, p) != cudaSuccess) {
+    // the dK/dV pass is persistent too: one CTA per SM walks the list of (key tile, KV head, batch) items
+    const unsigned kv_items = (unsigned)(p.n_tiles * p.Hkv * p.B);
+    const unsigned kv_grid = std::min(kv_items, (unsigned)sm_count());
+    BwdParams pk = p;
+    pk.sched2 = next_sched_pair(kv_items, kv_grid);
+    if (launch_pdl(attn_bwd_dkdv_kernel<D>, kv_grid, BwdCfg<D>::kThreads, BwdCfg<D>::kSmemBytes, st, tk, tv, tq, tdo,
+                   tdk, tdv, pk) != cudaSuccess) {
         cudaGetLastError();
         return B200ATTN_ERR_CUDA;
     }
@@ -339,8 +344,14 @@ extern "C" int b200attn_bwd(const void* q, const void* k, const void* v, const v
     p.q_st = sq.t;
     p.q_sh = sq.h;
     p.q_sb = sq.b;
+    p.dk = static_cast<uint16_t*>(dk);
+    p.dv = static_cast<uint16_t*>(dv);
+    p.k_st = sk.t;
+    p.k_sh = sk.h;
+    p.k_sb = sk.b;
     p.status = status;
     p.sched = nullptr;
+    p.sched2 = nullptr;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return D == 64 ? launch_bwd<64>(tq, tk64, tv64, tk, tv, tdo, to, tdq, tdk, tdv, p, st)
                    : launch_bwd<128>(tq, tk64, tv64, tk, tv, tdo, to, tdq, tdk, tdv, p, st);
@@ -548,6 +559,11 @@ extern "C" int b200attn_debug_read_probe(long long* host, int n) {
 extern "C" int b200attn_debug_read_trace(unsigned long long* host, int n_ctas) {
     if (n_ctas > 8192) n_ctas = 8192;
     return cudaMemcpyFromSymbol(host, b200attn::g_trace, sizeof(unsigned long long) * 3 * n_ctas) == cudaSuccess
+               ? 0 : B200ATTN_ERR_CUDA;
+}
+extern "C" int b200attn_debug_read_trace_clk(long long* host, int n_ctas) {
+    if (n_ctas > 8192) n_ctas = 8192;
+    return cudaMemcpyFromSymbol(host, b200attn::g_trace_clk, sizeof(long long) * 2 * n_ctas) == cudaSuccess
                ? 0 : B200ATTN_ERR_CUDA;
 }
 #endif

@@ -189,7 +189,11 @@ __device__ __forceinline__ uint64_t make_sdesc_sw128(uint32_t smem_addr, uint32_
 // grid_dep_launch() lets the NEXT kernel start its own set-up early; grid_dep_wait() blocks
 // until the PREVIOUS kernel has completed and its writes are visible.  Every kernel here does
 // its set-up (barriers, TMEM, tensor-map prefetch) first and calls grid_dep_wait() before its
-// first access to global memory, so only set-up and launch latency overlap.
+// first access to global memory, so only set-up and launch latency overlap.  The persistent
+// kernels do not call grid_dep_launch(): all their CTAs start at once, so the call would release
+// the next kernel at this one's very beginning, and a dependent grid queued behind a kernel for
+// its whole run time measured slower (2 %) than one released as the CTAs exit, which is what
+// happens without the call.
 __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
@@ -389,6 +393,7 @@ __device__ long long g_probe[512];
 // Per-CTA trace: SM id and begin/end times (ns) of the first 2048 CTAs of a launch, kept per kernel
 // (k = 0 forward, 1 dQ pass, 2 dK/dV pass).
 __device__ unsigned long long g_trace[8192 * 3];
+__device__ long long g_trace_clk[8192 * 2];  // clock64() at the same two points
 __device__ __forceinline__ unsigned long long b200attn_globaltimer() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -405,12 +410,16 @@ __device__ __forceinline__ unsigned b200attn_smid() {
         if (threadIdx.x == 0 && blockIdx.x < 2048) {                                                \
             g_trace[lin_ * 3 + 0] = b200attn_smid();                                                \
             g_trace[lin_ * 3 + 1] = b200attn_globaltimer();                                         \
+            g_trace_clk[lin_ * 2 + 0] = clock64();                                                  \
         }                                                                                           \
     } while (0)
 #define B200ATTN_TRACE_END(k)                                                                       \
     do {                                                                                            \
         const unsigned lin_ = (k) * 2048 + blockIdx.x;                                              \
-        if (threadIdx.x == 0 && blockIdx.x < 2048) g_trace[lin_ * 3 + 2] = b200attn_globaltimer();  \
+        if (threadIdx.x == 0 && blockIdx.x < 2048) {                                                \
+            g_trace[lin_ * 3 + 2] = b200attn_globaltimer();                                         \
+            g_trace_clk[lin_ * 2 + 1] = clock64();                                                  \
+        }                                                                                           \
     } while (0)
 #else
 #define B200ATTN_TRACE_BEGIN(k) \

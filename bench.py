@@ -35,7 +35,9 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 
 # DRAM traffic of the dominant kernel per launch at the default workload, from the committed ncu
 # summary (profiles/); None until a capture exists for the current kernel.
-NCU_TRAFFIC_BYTES = {"c2_50m_train": 46674176}  # dQ pass: dram read + write, profiles/attn_fwd_bwd_c2_50m_train.md
+# (dram read + write per launch of each kernel, profiles/attn_fwd_bwd_c2_50m_train.md)
+NCU_TRAFFIC_BYTES = {"c2_50m_train": {"attn_fwd_kernel": 21031936, "attn_bwd_dq_kernel": 46682112,
+                                      "attn_bwd_dkdv_kernel": 34404864}}
 
 
 def load_peaks():
@@ -470,7 +472,7 @@ def main():
     achieved = kflops[dom] / (kt[dom] * 1e-3) / 1e12
     roofline = {
         "bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-        "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(cfg.name),
+        "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(cfg.name, {}).get(dom),
         "peak_source": f"bf16_tflops_sustained of {peaks['_source']} (kernel timed inside a long loop); burst "
                        f"{peaks['bf16_tflops']}",
         "flops_per_launch": kflops[dom], "ms_per_launch": kt[dom],

@@ -1,0 +1,38 @@
+"""The persistent kernels hand their work items out either statically or from a device-wide counter
+(first come, first served).  Which CTA computes an item must not change a single bit of the result, the
+counters must be left clean for the next launch, and the default choice must agree with both."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+
+# (B, T, Hq, Hkv, D, repetitions): few items per CTA (static by default) and many (counter by default);
+# 70 repetitions use each of the library's 64 counter pairs at least once more
+CASES = [(4, 512, 6, 2, 64, 3), (8, 2048, 16, 4, 64, 70), (2, 1024, 8, 2, 128, 3), (3, 1100, 8, 4, 64, 3)]
+
+
+def _run(case, mode):
+    env = dict(os.environ)
+    env.pop("B200ATTN_ITEMS", None)
+    if mode:
+        env["B200ATTN_ITEMS"] = mode
+    env["PYTHONPATH"] = ROOT + os.pathsep + env.get("PYTHONPATH", "")
+    out = subprocess.run([sys.executable, os.path.join(HERE, "gpu_item_worker.py"), *map(str, case)], env=env,
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    return out.stdout.strip().splitlines()[-1].split()
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_results_do_not_depend_on_who_computes_an_item(case):
+    static, dynamic, default = _run(case, "static"), _run(case, "dynamic"), _run(case, None)
+    assert len(static) == 5
+    for name, a, b, c in zip(["O", "LSE", "dQ", "dK", "dV"], static, dynamic, default):
+        assert a == b, f"{name}: static and counter-based item lists give different bits"
+        assert a == c, f"{name}: the default item list gives different bits"

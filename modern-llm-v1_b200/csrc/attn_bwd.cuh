@@ -412,8 +412,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             const int q0 = qt * 128;
             // preprocess of this row from the tiles in shared memory: D = rowsum(O * dO); L * log2(e)
             const bool in_range = q0 + row < p.T;
-            const float lse2 = in_range ? p.lse[(size_t(b) * p.Hq + h) * p.T + q0 + row] * 1.4426950408889634f
-                                        : INFINITY;  // exp2(x - inf) = 0: padding query rows contribute nothing
+            // (the load is issued here and first used after the preprocess below, so that its latency
+            // overlaps the wait for the item's tiles)
+            const float lse_raw = in_range ? p.lse[(size_t(b) * p.Hq + h) * p.T + q0 + row] : 0.f;
             B200ATTN_STAMP(tid == 0, 400 + 4 * n + 0);
             ok = mbar_wait_warp(bar_q, n & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
             if (!ok) break;
@@ -433,6 +434,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 }
             }
             mbar_arrive(bar_o_free);  // the O tile may be overwritten by the next item's load
+            // exp2(x - inf) = 0: padding query rows contribute nothing
+            const float lse2 = in_range ? lse_raw * 1.4426950408889634f : INFINITY;
             if (part == 0) {
                 const size_t vrow = (size_t(b) * p.Hq + h) * p.Tpad + q0 + row;
                 p.lse2_w[vrow] = lse2;
@@ -1118,6 +1121,93 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         const uint32_t lane_base = uint32_t(w4 * 32) << 16;
         const int c0 = part * Cfg::kPartCols;  // first query column of this thread's part
         bool ok = true;
+        // Epilogue of an item.  It is deferred until the first unit of the next item has been handed to the MMA
+        // warp, so that the wait for the item's last products overlaps that unit's arithmetic.
+        auto epilogue = [&](int n_item, int id_item) -> bool {
+            // epilogue of the item: parts 0,1 write dV, parts 2,3 write dK (times scale); each part takes D / 2
+            // of the accumulator's columns of its key row, which is contiguous in global memory
+            B200ATTN_STAMP(tid == 0, 460 + 4 * n_item + 0);
+            ok = mbar_wait_warp(bar_acc, uint32_t(n_item) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+            if (!ok) return false;
+            B200ATTN_STAMP(tid == 0, 460 + 4 * n_item + 1);
+            tc_fence_after_sync();
+            // (the values below are derived from copies the compiler cannot see through, so that it does not
+            // compute them ahead of the unit loop and keep them in registers there)
+            int part_e = part, id_e = id_item;
+            asm volatile("" : "+r"(part_e), "+r"(id_e));
+            constexpr int kHalfParts = Cfg::kParts / 2;
+            constexpr int kColsPerPart = D / kHalfParts;
+            const bool is_dk = part_e >= kHalfParts;
+            const uint32_t acc = is_dk ? Cfg::kColAcc1 : Cfg::kColAcc0;
+            const float mul = is_dk ? p.scale : 1.f;
+            const int col0 = (part_e % kHalfParts) * kColsPerPart;
+            const int k0 = item_kt(id_e) * 128;
+            if constexpr (Cfg::kOutTiles > 0) {
+                // through shared memory and a TMA store, so that no compute thread waits on the memory system:
+                // the previous item's store must have read the staging tiles before they are rewritten
+                // (mbarriers with bounded waits rather than bar.sync: a warp that has given up never arrives)
+                if (tid == 0) {
+                    tma_store_wait_read0();
+                    mbar_arrive(bar_out_free);
+                }
+                ok = mbar_wait_warp(bar_out_free, uint32_t(n_item) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
+                if (!ok) return false;
+#pragma unroll
+                for (int c = 0; c < kColsPerPart / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_x32(tmem + lane_base + acc + col0 + c * 32, v);
+                    tmem_wait_ld();
+                    if (c + 1 == kColsPerPart / 32) {
+                        tc_fence_before_sync();
+                        mbar_arrive(bar_acc_free);  // the MMA warp may start the next item's accumulation
+                    }
+                    stage_row_chunk<D>(sOut + (is_dk ? Cfg::kTileBytes : 0), row, col0 + c * 32, v, mul);
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(bar_out_full);
+                if (warp == 0) {
+                    ok = mbar_wait_warp(bar_out_full, uint32_t(n_item) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
+                    if (!ok) return false;
+                }
+                if (tid == 0) {
+#pragma unroll
+                    for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
+                        tma_store_4d(&tmdV, sOut + bx * Cfg::kBoxBytes, bx * 64, k0, item_hk(id_e), item_b(id_e));
+                        tma_store_4d(&tmdK, sOut + Cfg::kTileBytes + bx * Cfg::kBoxBytes, bx * 64, k0, item_hk(id_e), item_b(id_e));
+                    }
+                    tma_store_commit();
+                }
+            } else {
+                const bool in_range = k0 + row < p.T;
+                uint16_t* out = (is_dk ? p.dk : p.dv) + size_t(item_b(id_e)) * p.k_sb + size_t(item_hk(id_e)) * p.k_sh +
+                                size_t(k0 + row) * p.k_st + col0;
+#pragma unroll
+                for (int c = 0; c < kColsPerPart / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_x32(tmem + lane_base + acc + col0 + c * 32, v);
+                    tmem_wait_ld();
+                    if (c + 1 == kColsPerPart / 32) {
+                        tc_fence_before_sync();
+                        mbar_arrive(bar_acc_free);  // the MMA warp may start the next item's accumulation
+                    }
+                    if (in_range) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            uint4 w;
+                            w.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]) * mul, __uint_as_float(v[g * 8 + 1]) * mul);
+                            w.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * mul, __uint_as_float(v[g * 8 + 3]) * mul);
+                            w.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * mul, __uint_as_float(v[g * 8 + 5]) * mul);
+                            w.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * mul, __uint_as_float(v[g * 8 + 7]) * mul);
+                            *reinterpret_cast<uint4*>(out + c * 32 + g * 8) = w;
+                        }
+                    }
+                }
+            }
+            B200ATTN_STAMP(tid == 0, 460 + 4 * n_item + 2);
+            return true;
+        };
+        bool pending = false;
+        int pend_id = 0;
         int u = 0, n = 0;
         for (int id; ok && (id = get_item(n)) >= 0; ++n) {
             const int n_i = p.n_tiles - item_kt(id);
@@ -1188,89 +1278,17 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                 tc_fence_before_sync();
                 mbar_arrive(&bar_pds_full[u & 1]);
                 B200ATTN_STAMP(tid == 0, 16 + 8 * u + 3);
-            }
-            if (!ok) break;
-            // epilogue of the item: parts 0,1 write dV, parts 2,3 write dK (times scale); each part takes D / 2
-            // of the accumulator's columns of its key row, which is contiguous in global memory
-            B200ATTN_STAMP(tid == 0, 460 + 4 * n + 0);
-            ok = mbar_wait_warp(bar_acc, uint32_t(n) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
-            if (!ok) break;
-            B200ATTN_STAMP(tid == 0, 460 + 4 * n + 1);
-            tc_fence_after_sync();
-            // (the values below are derived from copies the compiler cannot see through, so that it does not
-            // compute them ahead of the unit loop and keep them in registers there)
-            int part_e = part, id_e = id;
-            asm volatile("" : "+r"(part_e), "+r"(id_e));
-            constexpr int kHalfParts = Cfg::kParts / 2;
-            constexpr int kColsPerPart = D / kHalfParts;
-            const bool is_dk = part_e >= kHalfParts;
-            const uint32_t acc = is_dk ? Cfg::kColAcc1 : Cfg::kColAcc0;
-            const float mul = is_dk ? p.scale : 1.f;
-            const int col0 = (part_e % kHalfParts) * kColsPerPart;
-            const int k0 = item_kt(id_e) * 128;
-            if constexpr (Cfg::kOutTiles > 0) {
-                // through shared memory and a TMA store, so that no compute thread waits on the memory system:
-                // the previous item's store must have read the staging tiles before they are rewritten
-                // (mbarriers with bounded waits rather than bar.sync: a warp that has given up never arrives)
-                if (tid == 0) {
-                    tma_store_wait_read0();
-                    mbar_arrive(bar_out_free);
-                }
-                ok = mbar_wait_warp(bar_out_free, uint32_t(n) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
-                if (!ok) break;
-#pragma unroll
-                for (int c = 0; c < kColsPerPart / 32; ++c) {
-                    uint32_t v[32];
-                    tmem_ld_x32(tmem + lane_base + acc + col0 + c * 32, v);
-                    tmem_wait_ld();
-                    if (c + 1 == kColsPerPart / 32) {
-                        tc_fence_before_sync();
-                        mbar_arrive(bar_acc_free);  // the MMA warp may start the next item's accumulation
-                    }
-                    stage_row_chunk<D>(sOut + (is_dk ? Cfg::kTileBytes : 0), row, col0 + c * 32, v, mul);
-                }
-                fence_proxy_async_smem();
-                mbar_arrive(bar_out_full);
-                if (warp == 0) {
-                    ok = mbar_wait_warp(bar_out_full, uint32_t(n) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
+                if (pending) {  // first unit of this item: now the previous item's epilogue
+                    pending = false;
+                    ok = epilogue(n - 1, pend_id);
                     if (!ok) break;
                 }
-                if (tid == 0) {
-#pragma unroll
-                    for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
-                        tma_store_4d(&tmdV, sOut + bx * Cfg::kBoxBytes, bx * 64, k0, item_hk(id_e), item_b(id_e));
-                        tma_store_4d(&tmdK, sOut + Cfg::kTileBytes + bx * Cfg::kBoxBytes, bx * 64, k0, item_hk(id_e), item_b(id_e));
-                    }
-                    tma_store_commit();
-                }
-            } else {
-                const bool in_range = k0 + row < p.T;
-                uint16_t* out = (is_dk ? p.dk : p.dv) + size_t(item_b(id_e)) * p.k_sb + size_t(item_hk(id_e)) * p.k_sh +
-                                size_t(k0 + row) * p.k_st + col0;
-#pragma unroll
-                for (int c = 0; c < kColsPerPart / 32; ++c) {
-                    uint32_t v[32];
-                    tmem_ld_x32(tmem + lane_base + acc + col0 + c * 32, v);
-                    tmem_wait_ld();
-                    if (c + 1 == kColsPerPart / 32) {
-                        tc_fence_before_sync();
-                        mbar_arrive(bar_acc_free);  // the MMA warp may start the next item's accumulation
-                    }
-                    if (in_range) {
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            uint4 w;
-                            w.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]) * mul, __uint_as_float(v[g * 8 + 1]) * mul);
-                            w.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * mul, __uint_as_float(v[g * 8 + 3]) * mul);
-                            w.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * mul, __uint_as_float(v[g * 8 + 5]) * mul);
-                            w.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * mul, __uint_as_float(v[g * 8 + 7]) * mul);
-                            *reinterpret_cast<uint4*>(out + c * 32 + g * 8) = w;
-                        }
-                    }
-                }
             }
-            B200ATTN_STAMP(tid == 0, 460 + 4 * n + 2);
+            if (!ok) break;
+            pending = true;
+            pend_id = id;
         }
+        if (ok && pending) epilogue(n - 1, pend_id);
         // the staging tiles must outlive the last store's reads
         if (Cfg::kOutTiles > 0 && tid == 0) tma_store_wait_read0();
     }

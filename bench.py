@@ -480,6 +480,15 @@ def main():
         "whole_step": {"achieved": value / world, "frac": value / world / peak,
                        "frac_of_burst": value / world / float(peaks["bf16_tflops"])},
     }
+    # the HBM roof beside the tensor roof: with L2-cold inputs a step cannot move fewer bytes than
+    # forward q,k,v,o,lse and backward q,k,v,o,lse,dO,dq,dk,dv (BF16, FP32 lse)
+    qb, kb = cfg.B * cfg.Hq * cfg.T * cfg.D * 2, cfg.B * cfg.Hkv * cfg.T * cfg.D * 2
+    lb = cfg.B * cfg.Hq * cfg.T * 4
+    min_bytes = (2 * qb + 2 * kb + lb) + (4 * qb + 4 * kb + lb)
+    hbm_ms = min_bytes / (float(peaks["hbm_gbs"]) * 1e9) * 1e3
+    roofline["hbm_roof"] = {"min_bytes_per_step": min_bytes, "ms_per_step_at_hbm_peak": hbm_ms,
+                            "tflops_ceiling": cfg.fwd_bwd_flops() / (hbm_ms * 1e-3) / 1e12,
+                            "frac_of_ceiling": (value / world) / (cfg.fwd_bwd_flops() / (hbm_ms * 1e-3) / 1e12)}
 
     # end to end with host buffers
     e2e_steps = max(20, min(steps, 200))

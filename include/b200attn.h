@@ -121,6 +121,35 @@ size_t b200attn_decode_workspace_bytes(int B, int L, int Hq, int Hkv, int D, int
 /* The split count b200attn_decode uses for n_splits <= 0. */
 int b200attn_decode_default_splits(int B, int L, int Hq, int Hkv, int D);
 
+enum { B200ATTN_DTYPE_BF16 = 0, B200ATTN_DTYPE_F32 = 1 };
+
+/*
+ * Fused RoPE + per-head RMSNorm ("QK-Norm") that prepares q or k for b200attn_fwd, and its backward.
+ * Replaces, per tensor, split_heads -> rope_apply_inplace -> rmsnorm_forward of the reference
+ * (llm/src/model/modern_gpt.cu:351-370; llm/src/model/attention.cu:344-364, llm/src/model/rope.cu:146-163,
+ * llm/src/model/rmsnorm.cu:24-53) and rmsnorm_backward -> rope_apply_backward_inplace -> merge_heads
+ * (llm/src/model/modern_gpt.cu:527-552; llm/src/model/rmsnorm.cu:55-101, llm/src/model/rope.cu:46-65).
+ *
+ *   r = RoPE(x, t)  (interleaved pairs: r[2i] = x[2i] cos - x[2i+1] sin, r[2i+1] = x[2i] sin + x[2i+1] cos)
+ *   rstd = 1 / sqrt(mean_d r[d]^2 + eps);   y[d] = r[d] * rstd * gamma[d]
+ *
+ * x: B*T*H rows of D elements, BF16 or FP32 (x_dtype), in either layout (x_layout; BTHD is the projection
+ * output read in place).  y: BF16 in y_layout (what b200attn_fwd takes).  rstd: FP32 [B, H, T], the row order of
+ * the reference's rstd vector.  gamma: FP32 [D].  cos_t, sin_t: FP32 [T, D/2] device tables with the values of
+ * make_rope_cache (llm/src/model/rope.cu:112-128); b200attn_rope_table fills host copies of them.
+ * Backward: dy BF16 in y_layout; dx in x's type and layout (overwritten); d_gamma FP32 [D] is ACCUMULATED into,
+ * as in the reference (llm/src/model/rmsnorm.h:17), but in a fixed order (no atomics: bit-reproducible).
+ * workspace: at least b200attn_rope_norm_bwd_workspace_bytes(D) bytes, 256-byte aligned.
+ */
+int b200attn_rope_table(int T, int D, float base, float* cos_host, float* sin_host);
+int b200attn_rope_norm_fwd(const void* x, int x_dtype, int x_layout, void* y, int y_layout, float* rstd,
+                           const float* gamma, const float* cos_t, const float* sin_t, int B, int T, int H, int D,
+                           float eps, void* stream);
+int b200attn_rope_norm_bwd(const void* dy, int y_layout, const void* x, int x_dtype, int x_layout, const float* rstd,
+                           const float* gamma, const float* cos_t, const float* sin_t, void* dx, float* d_gamma, int B,
+                           int T, int H, int D, void* workspace, size_t workspace_bytes, void* stream);
+size_t b200attn_rope_norm_bwd_workspace_bytes(int D);
+
 /*
  * Diagnostics for benchmarks (no counterpart in the reference): when three CUDA events are
  * set, every following b200attn_bwd records them on its stream before the dQ pass (which also

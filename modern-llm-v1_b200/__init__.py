@@ -16,6 +16,7 @@ from .flash_attn import (  # noqa: F401
     flash_attn_forward,
     flash_attn_forward_gqa,
 )
+from .rope_norm import make_rope_cache, rope_qknorm_backward, rope_qknorm_forward  # noqa: F401
 
 __all__ = [
     "flash_attn_forward",
@@ -24,4 +25,7 @@ __all__ = [
     "flash_attn_backward_gqa",
     "flash_attn_decode",
     "device_status",
+    "make_rope_cache",
+    "rope_qknorm_forward",
+    "rope_qknorm_backward",
 ]

@@ -28,6 +28,8 @@ BWD_STATIC_MAX_ROWS = 524288
 LAYOUT_BHTD = 0
 LAYOUT_BTHD = 1
 LAYOUTS = {"BHTD": LAYOUT_BHTD, "BTHD": LAYOUT_BTHD}
+DTYPE_BF16 = 0
+DTYPE_F32 = 1
 
 # every symbol include/b200attn.h declares
 SYMBOLS = (
@@ -39,6 +41,10 @@ SYMBOLS = (
     "b200attn_decode",
     "b200attn_decode_workspace_bytes",
     "b200attn_decode_default_splits",
+    "b200attn_rope_table",
+    "b200attn_rope_norm_fwd",
+    "b200attn_rope_norm_bwd",
+    "b200attn_rope_norm_bwd_workspace_bytes",
     "b200attn_last_device_status",
     "b200attn_strerror",
     "b200attn_version",
@@ -74,6 +80,14 @@ def load() -> ctypes.CDLL:
     L.b200attn_decode_workspace_bytes.restype = sz
     L.b200attn_decode_default_splits.argtypes = [i, i, i, i, i]
     L.b200attn_decode_default_splits.restype = i
+    L.b200attn_rope_table.argtypes = [i, i, f, vp, vp]
+    L.b200attn_rope_table.restype = i
+    L.b200attn_rope_norm_fwd.argtypes = [vp, i, i, vp, i, vp, vp, vp, vp, i, i, i, i, f, vp]
+    L.b200attn_rope_norm_fwd.restype = i
+    L.b200attn_rope_norm_bwd.argtypes = [vp, i, vp, i, i, vp, vp, vp, vp, vp, vp, i, i, i, i, vp, sz, vp]
+    L.b200attn_rope_norm_bwd.restype = i
+    L.b200attn_rope_norm_bwd_workspace_bytes.argtypes = [i]
+    L.b200attn_rope_norm_bwd_workspace_bytes.restype = sz
     L.b200attn_last_device_status.argtypes = [vp]
     L.b200attn_last_device_status.restype = i
     L.b200attn_strerror.argtypes = [i]

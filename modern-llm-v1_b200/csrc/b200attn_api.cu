@@ -13,6 +13,7 @@
 #include "attn_bwd.cuh"
 #include "attn_decode.cuh"
 #include "attn_fwd.cuh"
+#include "rope_norm.cuh"
 #include "tmap.h"
 
 using namespace b200attn;
@@ -278,6 +279,125 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk64, const CUtensorMap
 }
 
 }  // namespace
+
+// ---------------------------------------------------------------------------------------
+// Fused RoPE + QK-Norm (rope_norm.cuh)
+// ---------------------------------------------------------------------------------------
+namespace {
+
+int rope_norm_check(int B, int T, int H, int D, int x_dtype, int x_layout, int y_layout) {
+    if (B <= 0 || T <= 0 || H <= 0 || D <= 0) return B200ATTN_ERR_INVALID_ARG;
+    if (x_dtype != B200ATTN_DTYPE_BF16 && x_dtype != B200ATTN_DTYPE_F32) return B200ATTN_ERR_INVALID_ARG;
+    for (int l : {x_layout, y_layout})
+        if (l != B200ATTN_LAYOUT_BHTD && l != B200ATTN_LAYOUT_BTHD) return B200ATTN_ERR_INVALID_ARG;
+    if (D != 64 && D != 128) return B200ATTN_ERR_UNSUPPORTED;
+    return B200ATTN_OK;
+}
+
+// grid: enough warps to keep the memory system busy, a multiple of the SM count, never more than the rows need
+unsigned rope_norm_grid(long long rows, int ctas_per_sm) {
+    const long long need = (rows + (kRopeNormThreads / 32) * kRowsPerIter - 1) / ((kRopeNormThreads / 32) * kRowsPerIter);
+    const long long cap = (long long)ctas_per_sm * sm_count();
+    return (unsigned)std::max<long long>(1, std::min(need, cap));
+}
+
+void rope_norm_fill(RopeNormParams& p, int B, int T, int H, int D, int x_layout, int y_layout) {
+    const Strides sx = strides_for(x_layout, H, T, D), sy = strides_for(y_layout, H, T, D);
+    p.B = B;
+    p.T = T;
+    p.H = H;
+    p.x_bthd = x_layout == B200ATTN_LAYOUT_BTHD;
+    p.x_st = sx.t, p.x_sh = sx.h, p.x_sb = sx.b;
+    p.y_st = sy.t, p.y_sh = sy.h, p.y_sb = sy.b;
+}
+
+}  // namespace
+
+extern "C" int b200attn_rope_table(int T, int D, float base, float* cos_host, float* sin_host) {
+    if (T <= 0 || D <= 0 || (D & 1) || !cos_host || !sin_host || !(base > 0.f)) return B200ATTN_ERR_INVALID_ARG;
+    const int half = D / 2;
+    // the same single-precision arithmetic as make_rope_cache (llm/src/model/rope.cu:112-128)
+    for (int t = 0; t < T; ++t)
+        for (int i = 0; i < half; ++i) {
+            const float theta = powf(base, -static_cast<float>(2 * i) / static_cast<float>(D));
+            const float angle = static_cast<float>(t) * theta;
+            cos_host[(size_t)t * half + i] = cosf(angle);
+            sin_host[(size_t)t * half + i] = sinf(angle);
+        }
+    return B200ATTN_OK;
+}
+
+extern "C" int b200attn_rope_norm_fwd(const void* x, int x_dtype, int x_layout, void* y, int y_layout, float* rstd,
+                                      const float* gamma, const float* cos_t, const float* sin_t, int B, int T, int H,
+                                      int D, float eps, void* stream) {
+    int rc = rope_norm_check(B, T, H, D, x_dtype, x_layout, y_layout);
+    if (rc) return rc;
+    if (!x || !y || !rstd || !gamma || !cos_t || !sin_t) return B200ATTN_ERR_INVALID_ARG;
+    if (!aligned16(x) || !aligned16(y)) return B200ATTN_ERR_ALIGNMENT;
+    RopeNormParams p = {};
+    rope_norm_fill(p, B, T, H, D, x_layout, y_layout);
+    p.x = x;
+    p.y = y;
+    p.rstd = rstd;
+    p.gamma = gamma;
+    p.cos_t = cos_t;
+    p.sin_t = sin_t;
+    p.eps = eps;
+    const unsigned grid = rope_norm_grid((long long)B * T * H, 8);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool f32 = x_dtype == B200ATTN_DTYPE_F32;
+    if (D == 64) {
+        if (f32) rope_norm_fwd_kernel<64, true><<<grid, kRopeNormThreads, 0, st>>>(p);
+        else rope_norm_fwd_kernel<64, false><<<grid, kRopeNormThreads, 0, st>>>(p);
+    } else {
+        if (f32) rope_norm_fwd_kernel<128, true><<<grid, kRopeNormThreads, 0, st>>>(p);
+        else rope_norm_fwd_kernel<128, false><<<grid, kRopeNormThreads, 0, st>>>(p);
+    }
+    if (cudaGetLastError() != cudaSuccess) return B200ATTN_ERR_CUDA;
+    return B200ATTN_OK;
+}
+
+extern "C" size_t b200attn_rope_norm_bwd_workspace_bytes(int D) {
+    if (D <= 0) return 0;
+    return (size_t)2 * sm_count() * D * sizeof(float);
+}
+
+extern "C" int b200attn_rope_norm_bwd(const void* dy, int y_layout, const void* x, int x_dtype, int x_layout,
+                                      const float* rstd, const float* gamma, const float* cos_t, const float* sin_t,
+                                      void* dx, float* d_gamma, int B, int T, int H, int D, void* workspace,
+                                      size_t workspace_bytes, void* stream) {
+    int rc = rope_norm_check(B, T, H, D, x_dtype, x_layout, y_layout);
+    if (rc) return rc;
+    if (!dy || !x || !rstd || !gamma || !cos_t || !sin_t || !dx || !d_gamma) return B200ATTN_ERR_INVALID_ARG;
+    if (!aligned16(x) || !aligned16(dy) || !aligned16(dx)) return B200ATTN_ERR_ALIGNMENT;
+    if (!workspace || workspace_bytes < b200attn_rope_norm_bwd_workspace_bytes(D) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+        return B200ATTN_ERR_WORKSPACE;
+    RopeNormParams p = {};
+    rope_norm_fill(p, B, T, H, D, x_layout, y_layout);
+    p.x = x;
+    p.y = dx;
+    p.dy = static_cast<const uint16_t*>(dy);
+    p.rstd = const_cast<float*>(rstd);
+    p.gamma = gamma;
+    p.cos_t = cos_t;
+    p.sin_t = sin_t;
+    p.partial = static_cast<float*>(workspace);
+    const unsigned grid = rope_norm_grid((long long)B * T * H, 2);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool f32 = x_dtype == B200ATTN_DTYPE_F32;
+    if (D == 64) {
+        if (f32) rope_norm_bwd_kernel<64, true><<<grid, kRopeNormThreads, 0, st>>>(p);
+        else rope_norm_bwd_kernel<64, false><<<grid, kRopeNormThreads, 0, st>>>(p);
+        rope_norm_dgamma_kernel<64><<<1, 64, 0, st>>>(p.partial, (int)grid, d_gamma);
+    } else {
+        if (f32) rope_norm_bwd_kernel<128, true><<<grid, kRopeNormThreads, 0, st>>>(p);
+        else rope_norm_bwd_kernel<128, false><<<grid, kRopeNormThreads, 0, st>>>(p);
+        rope_norm_dgamma_kernel<128><<<1, 128, 0, st>>>(p.partial, (int)grid, d_gamma);
+    }
+    if (cudaGetLastError() != cudaSuccess) return B200ATTN_ERR_CUDA;
+    return B200ATTN_OK;
+}
 
 extern "C" int b200attn_set_bwd_profile_events(void* e0, void* e1, void* e2) {
     void* ev[3] = {e0, e1, e2};

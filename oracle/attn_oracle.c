@@ -121,6 +121,75 @@ void oracle_rmsnorm_rows(float* x, long long rows, int D, float eps) {
     }
 }
 
+/* Fused RoPE + RMSNorm with gamma over x [n_outer, T, D] (row (n, t) is token t): the chain
+ * rope_apply_inplace -> rmsnorm_forward of llm/src/model/modern_gpt.cu:358-370.
+ * Rotation and table: llm/src/model/rope.cu:25-44,112-128; norm: llm/src/model/rmsnorm.cu:24-53
+ * (rstd = rsqrt(mean r^2 + eps), y = r rstd gamma).  Sums in double. */
+void oracle_rope_norm_fwd(const float* x, const float* gamma, float* y, float* rstd, long long n_outer, int T, int D,
+                          float base, float eps) {
+    int half = D / 2;
+#pragma omp parallel for schedule(static)
+    for (long long n = 0; n < n_outer; ++n) {
+        for (int t = 0; t < T; ++t) {
+            const float* xr = x + (n * T + t) * (long long)D;
+            float* yr = y + (n * T + t) * (long long)D;
+            float r[512];
+            double sq = 0.0;
+            for (int i = 0; i < half; ++i) {
+                float theta = powf(base, -(float)(2 * i) / (float)D);
+                float angle = (float)t * theta;
+                float c = cosf(angle), s = sinf(angle);
+                r[2 * i] = xr[2 * i] * c - xr[2 * i + 1] * s;
+                r[2 * i + 1] = xr[2 * i] * s + xr[2 * i + 1] * c;
+                sq += (double)r[2 * i] * r[2 * i] + (double)r[2 * i + 1] * r[2 * i + 1];
+            }
+            float rs = (float)(1.0 / sqrt(sq / D + (double)eps));
+            rstd[n * T + t] = rs;
+            for (int d = 0; d < D; ++d) yr[d] = r[d] * rs * gamma[d];
+        }
+    }
+}
+
+/* Backward of the chain above: rmsnorm_backward (llm/src/model/rmsnorm.cu:55-101:
+ * g = dy gamma, s = sum g r, dr = rstd g - rstd^3 / D s r, d_gamma += dy r rstd) followed by
+ * rope_apply_backward_inplace (llm/src/model/rope.cu:46-65: the inverse rotation).
+ * d_gamma [D] is accumulated into (llm/src/model/rmsnorm.h:17).  Sums in double; single thread
+ * over rows for d_gamma so that the result does not depend on the thread count. */
+void oracle_rope_norm_bwd(const float* dy, const float* x, const float* gamma, const float* rstd, float* dx,
+                          float* d_gamma, long long n_outer, int T, int D, float base) {
+    int half = D / 2;
+    double dg[512];
+    for (int d = 0; d < D; ++d) dg[d] = 0.0;
+    for (long long n = 0; n < n_outer; ++n) {
+        for (int t = 0; t < T; ++t) {
+            const float* xr = x + (n * T + t) * (long long)D;
+            const float* dyr = dy + (n * T + t) * (long long)D;
+            float* dxr = dx + (n * T + t) * (long long)D;
+            double rs = rstd[n * T + t];
+            double r[512], c[256], s[256], dr[512];
+            double sum = 0.0;
+            for (int i = 0; i < half; ++i) {
+                float theta = powf(base, -(float)(2 * i) / (float)D);
+                float angle = (float)t * theta;
+                c[i] = cosf(angle), s[i] = sinf(angle);
+                r[2 * i] = xr[2 * i] * c[i] - xr[2 * i + 1] * s[i];
+                r[2 * i + 1] = xr[2 * i] * s[i] + xr[2 * i + 1] * c[i];
+            }
+            for (int d = 0; d < D; ++d) {
+                sum += (double)dyr[d] * gamma[d] * r[d];
+                dg[d] += (double)dyr[d] * r[d] * rs;
+            }
+            double coeff = rs * rs * rs / D * sum;
+            for (int d = 0; d < D; ++d) dr[d] = rs * dyr[d] * gamma[d] - coeff * r[d];
+            for (int i = 0; i < half; ++i) {
+                dxr[2 * i] = (float)(dr[2 * i] * c[i] + dr[2 * i + 1] * s[i]);
+                dxr[2 * i + 1] = (float)(-dr[2 * i] * s[i] + dr[2 * i + 1] * c[i]);
+            }
+        }
+    }
+    for (int d = 0; d < D; ++d) d_gamma[d] += (float)dg[d];
+}
+
 /* One query head (b, hq): forward and, when dout != NULL, backward.
  * dk_acc/dv_acc are [T, D] double accumulators private to this query head
  * (the per-query-head dK/dV that the reference produces before

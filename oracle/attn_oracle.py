@@ -60,6 +60,8 @@ def lib():
         L.oracle_bf16_to_f32.argtypes = [ctypes.POINTER(ctypes.c_uint16), fp, ctypes.c_longlong]
         L.oracle_rope_inplace.argtypes = [fp, ctypes.c_longlong, i, i, ctypes.c_float, i]
         L.oracle_rmsnorm_rows.argtypes = [fp, ctypes.c_longlong, i, ctypes.c_float]
+        L.oracle_rope_norm_fwd.argtypes = [fp, fp, fp, fp, ctypes.c_longlong, i, i, ctypes.c_float, ctypes.c_float]
+        L.oracle_rope_norm_bwd.argtypes = [fp, fp, fp, fp, fp, fp, ctypes.c_longlong, i, i, ctypes.c_float]
         L.oracle_attn_fwd.argtypes = [fp, fp, fp, fp, fp, i, i, i, i, i, ctypes.c_float, sp, sp, sp]
         L.oracle_attn_fwd_bwd.argtypes = [fp] * 9 + [i, i, i, i, i, ctypes.c_float, sp, sp, sp]
         L.oracle_decode.argtypes = [fp, fp, fp, fp, fp, i, i, i, i, i, ctypes.c_float, sp]
@@ -130,6 +132,29 @@ def rmsnorm(x: np.ndarray, eps: float = 1e-5) -> np.ndarray:
     D = y.shape[-1]
     lib().oracle_rmsnorm_rows(_fp(y), y.size // D, D, eps)
     return y
+
+
+def rope_norm_fwd(x: np.ndarray, gamma: np.ndarray, base: float = 10000.0, eps: float = 1e-5):
+    """Fused RoPE + RMSNorm over x[..., T, D]: returns (y, rstd[..., T]).  The chain rope_apply_inplace ->
+    rmsnorm_forward of llm/src/model/modern_gpt.cu:358-370."""
+    x = _c32(x)
+    g = _c32(gamma)
+    T, D = x.shape[-2], x.shape[-1]
+    y = np.empty_like(x)
+    rstd = np.empty(x.shape[:-1], dtype=np.float32)
+    lib().oracle_rope_norm_fwd(_fp(x), _fp(g), _fp(y), _fp(rstd), x.size // (T * D), T, D, base, eps)
+    return y, rstd
+
+
+def rope_norm_bwd(dy: np.ndarray, x: np.ndarray, gamma: np.ndarray, rstd: np.ndarray, base: float = 10000.0):
+    """Backward of rope_norm_fwd: returns (dx, d_gamma) with d_gamma summed over all rows
+    (rmsnorm_backward -> rope_apply_backward_inplace, llm/src/model/modern_gpt.cu:527-544)."""
+    dy, x, g, rstd = _c32(dy), _c32(x), _c32(gamma), _c32(rstd)
+    T, D = x.shape[-2], x.shape[-1]
+    dx = np.empty_like(x)
+    dg = np.zeros(D, dtype=np.float32)
+    lib().oracle_rope_norm_bwd(_fp(dy), _fp(x), _fp(g), _fp(rstd), _fp(dx), _fp(dg), x.size // (T * D), T, D, base)
+    return dx, dg
 
 
 # --------------------------------------------------------------------------

@@ -77,6 +77,16 @@ def main():
     z = np.zeros(x.shape, np.float32)
     L.ref_bf16_to_f32(y.ctypes.data_as(ctypes.POINTER(ctypes.c_uint16)), fp(z), x.size)
     out.update({"bf16_x": x, "bf16_bits": y, "bf16_back": z})
+    # rope_host followed by rmsnorm_host with a non-trivial gamma: the chain the model runs on q and k
+    # (llm/src/model/modern_gpt.cu:358-370), for the fused RoPE + QK-Norm kernel
+    for tag, (N, T, d) in {"ropenorm64": (3, 33, 64), "ropenorm128": (2, 9, 128)}.items():
+        x = u(N, T, d)
+        r = np.zeros_like(x)
+        L.ref_rope_host(fp(x), fp(r), N, T, d, ctypes.c_float(10000.0))
+        g = (1.0 + 0.2 * u(d)).astype(np.float32)
+        y = np.zeros_like(x)
+        L.ref_rmsnorm_host(fp(r), fp(g), fp(y), N * T, d, ctypes.c_float(1e-5))
+        out.update({f"{tag}_x": x, f"{tag}_g": g, f"{tag}_y": y})
     np.savez_compressed(os.path.join(HERE, "reference_host.npz"), **out)
     print("wrote", os.path.join(HERE, "reference_host.npz"), sum(a.nbytes for a in out.values()), "bytes raw")
 

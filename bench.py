@@ -60,6 +60,8 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c2_50m_train")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--op", default="attention", choices=["attention", "qkprep"],
+                    help="qkprep: the fused RoPE + QK-Norm operator on the config's q and k (HBM GB/s)")
     return ap.parse_args()
 
 
@@ -379,6 +381,106 @@ def run_decode(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier)
         }), flush=True)
 
 
+def run_qkprep(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier):
+    """Fused RoPE + QK-Norm, forward and backward, on q ([B,T,Hq,D]) and k ([B,T,Hkv,D]) of the config, BF16 in
+    the projection-output layout, BF16 out in the attention layout: HBM GB/s.  Algorithmic bytes per step =
+    forward (x read, y written, rstd written) + backward (x, dy, rstd read, dx written); the step rotates over
+    buffer sets larger than L2."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    B, T, D = cfg.B, cfg.T, cfg.D
+    heads = (cfg.Hq, cfg.Hkv)
+    g = torch.Generator().manual_seed(20260006 + 1000 * rank)
+    n_sets = 4
+    cos, sin = m.make_rope_cache(T, D, 10000.0, device)
+    gamma = [(1.0 + 0.1 * torch.randn(D, generator=g)).to(device) for _ in heads]
+    sets = []
+    for _ in range(n_sets):
+        s = []
+        for H in heads:
+            x = torch.randn(B, T, H, D, generator=g).bfloat16().to(device)
+            dy = torch.randn(B, H, T, D, generator=g).bfloat16().to(device)
+            s.append(dict(x=x, dy=dy, y=torch.empty(B, H, T, D, dtype=torch.bfloat16, device=device),
+                          rstd=torch.empty(B, H, T, device=device), dx=torch.empty_like(x),
+                          dg=torch.zeros(D, device=device)))
+        sets.append(s)
+
+    def step(i):
+        for (H, gm, t) in zip(heads, gamma, sets[i % n_sets]):
+            m.rope_qknorm_forward(t["x"], cos, sin, gm, 1e-5, t["y"], t["rstd"], B, T, H, D)
+        for (H, gm, t) in zip(heads, gamma, sets[i % n_sets]):
+            m.rope_qknorm_backward(t["dy"], t["x"], cos, sin, gm, t["rstd"], t["dx"], t["dg"], B, T, H, D)
+
+    for i in range(warmup):
+        step(i)
+    m.device_status()
+    # Six short launches per step: issued one by one from Python the host, not the GPU, sets the pace
+    # (about 20 us per call), so one round over the buffer sets is captured in a CUDA graph and replayed.
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(n_sets):
+                step(i)
+    torch.cuda.current_stream().wait_stream(side)
+    steps = max(n_sets, steps // n_sets * n_sets)
+    for _ in range(3):
+        graph.replay()
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(steps // n_sets):
+        graph.replay()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        t_ = torch.tensor([ms], device=device)
+        dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+        ms = float(t_.item())
+    m.device_status()
+    rows = B * T * sum(heads)
+    nbytes = rows * D * 2 * 2 + rows * 4 + rows * D * 2 * 3 + rows * 4  # fwd: x, y, rstd; bwd: x, dy, dx, rstd
+    gbs = world * nbytes / (ms * 1e-3) / 1e9
+    peak = float(peaks["hbm_gbs"])
+    out = {
+        "metric": "rope_qknorm_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": cfg.name + "_qkprep", "B_per_gpu": B, "T": T, "Hq": cfg.Hq, "Hkv": cfg.Hkv, "D": D,
+                   "io": "x, dy, dx BF16 [B,T,H,D] / [B,H,T,D]; y BF16 [B,H,T,D]; rstd FP32",
+                   "l2": f"rotating over {n_sets} buffer sets, {n_sets * rows * D * 2 * 4 / 1e6:.0f} MB > 126 MB L2",
+                   "launch": "one round over the buffer sets captured in a CUDA graph and replayed"},
+        "clocks": clocks, "gpu_launches": 6 * steps,
+        "roofline": {"bound": "hbm", "kernel": "rope_norm_fwd_kernel + rope_norm_bwd_kernel", "achieved": gbs / world,
+                     "peak": peak, "unit": "GB/s", "frac": gbs / world / peak, "traffic": None,
+                     "peak_source": f"hbm_gbs of {peaks['_source']}", "bytes_per_step": nbytes,
+                     "note": "6 launches per step: forward and backward on q and on k, and the two d_gamma sums"},
+    }
+    if rank == 0 and not args.no_cpu_baseline:
+        from oracle import attn_oracle as ao
+        use_all_host_cores()
+        xs = np.random.default_rng(1).standard_normal((8, heads[0], T, D)).astype(np.float32)
+        gs = np.ones(D, np.float32)
+        t0 = time.perf_counter()
+        yo, rs = ao.rope_norm_fwd(xs, gs)
+        ao.rope_norm_bwd(yo, xs, gs, rs)
+        dt = time.perf_counter() - t0
+        srows = xs.shape[0] * heads[0] * T
+        sbytes = srows * D * 2 * 5 + srows * 8
+        out["cpu_baseline"] = {"value": sbytes / dt / 1e9, "unit": "GB/s (same byte convention)", "cores": ao.num_threads(),
+                               "kind": "port", "sample": f"{srows} of {rows} rows, forward + backward once, {dt:.2f} s wall "
+                               "(the backward's d_gamma sum is single-threaded by design)"}
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+
+
 def main():
     args = parse_args()
     import modern_llm_v1_b200 as m
@@ -412,6 +514,12 @@ def main():
     peaks = load_peaks()
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
+    if args.op == "qkprep":
+        run_qkprep(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     if cfg.kind == "decode":
         run_decode(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier)
         if world > 1:

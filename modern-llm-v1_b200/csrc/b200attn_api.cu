@@ -285,20 +285,51 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk64, const CUtensorMap
 // ---------------------------------------------------------------------------------------
 namespace {
 
+constexpr int kRopeNormMaxCtasPerSm = 8;  // 2048 threads per SM / 256
+
 int rope_norm_check(int B, int T, int H, int D, int x_dtype, int x_layout, int y_layout) {
     if (B <= 0 || T <= 0 || H <= 0 || D <= 0) return B200ATTN_ERR_INVALID_ARG;
     if (x_dtype != B200ATTN_DTYPE_BF16 && x_dtype != B200ATTN_DTYPE_F32) return B200ATTN_ERR_INVALID_ARG;
     for (int l : {x_layout, y_layout})
         if (l != B200ATTN_LAYOUT_BHTD && l != B200ATTN_LAYOUT_BTHD) return B200ATTN_ERR_INVALID_ARG;
     if (D != 64 && D != 128) return B200ATTN_ERR_UNSUPPORTED;
+    if ((long long)B * T * H >= (1LL << 31)) return B200ATTN_ERR_TOO_LARGE;  // rows are counted in 32 bits
     return B200ATTN_OK;
 }
 
-// grid: enough warps to keep the memory system busy, a multiple of the SM count, never more than the rows need
-unsigned rope_norm_grid(long long rows, int ctas_per_sm) {
-    const long long need = (rows + (kRopeNormThreads / 32) * kRowsPerIter - 1) / ((kRopeNormThreads / 32) * kRowsPerIter);
-    const long long cap = (long long)ctas_per_sm * sm_count();
+// grid: as many CTAs as the device keeps resident at once (asked of the runtime once per kernel and device), never
+// more than the rows need
+template <typename K>
+unsigned rope_norm_grid(K kernel, long long rows, int rows_per_cta_iter, int* cached_occ) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= kMaxDevices) dev = 0;
+    if (cached_occ[dev] == 0) {
+        int occ = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, kRopeNormThreads, 0) != cudaSuccess || occ <= 0) {
+            cudaGetLastError();
+            occ = 1;
+        }
+        cached_occ[dev] = occ;
+    }
+    const long long need = (rows + rows_per_cta_iter - 1) / rows_per_cta_iter;
+    const long long cap = (long long)cached_occ[dev] * sm_count();
     return (unsigned)std::max<long long>(1, std::min(need, cap));
+}
+
+template <int D, bool F32>
+void rope_norm_launch_fwd(const RopeNormParams& p, long long rows, cudaStream_t st) {
+    static int occ[kMaxDevices] = {0};
+    const unsigned grid = rope_norm_grid(rope_norm_fwd_kernel<D, F32>, rows, (kRopeNormThreads / 32) * kFwdSteps * (256 / D), occ);
+    rope_norm_fwd_kernel<D, F32><<<grid, kRopeNormThreads, 0, st>>>(p);
+}
+template <int D, bool F32>
+unsigned rope_norm_launch_bwd(const RopeNormParams& p, long long rows, cudaStream_t st) {
+    static int occ[kMaxDevices] = {0};
+    unsigned grid = rope_norm_grid(rope_norm_bwd_kernel<D, F32>, rows, (kRopeNormThreads / 32) * kBwdSteps * (256 / D), occ);
+    grid = std::min(grid, (unsigned)(kRopeNormMaxCtasPerSm * sm_count()));  // the workspace holds that many partial sums
+    rope_norm_bwd_kernel<D, F32><<<grid, kRopeNormThreads, 0, st>>>(p);
+    return grid;
 }
 
 void rope_norm_fill(RopeNormParams& p, int B, int T, int H, int D, int x_layout, int y_layout) {
@@ -306,9 +337,10 @@ void rope_norm_fill(RopeNormParams& p, int B, int T, int H, int D, int x_layout,
     p.B = B;
     p.T = T;
     p.H = H;
-    p.x_bthd = x_layout == B200ATTN_LAYOUT_BTHD;
     p.x_st = sx.t, p.x_sh = sx.h, p.x_sb = sx.b;
     p.y_st = sy.t, p.y_sh = sy.h, p.y_sb = sy.b;
+    const RnFastDiv dh = rn_fastdiv_make((unsigned)H), dt = rn_fastdiv_make((unsigned)T);
+    p.div_h_mul = dh.mul, p.div_h_shr = dh.shr, p.div_t_mul = dt.mul, p.div_t_shr = dt.shr;
 }
 
 }  // namespace
@@ -336,6 +368,7 @@ extern "C" int b200attn_rope_norm_fwd(const void* x, int x_dtype, int x_layout, 
     if (!aligned16(x) || !aligned16(y)) return B200ATTN_ERR_ALIGNMENT;
     RopeNormParams p = {};
     rope_norm_fill(p, B, T, H, D, x_layout, y_layout);
+    p.walk_bthd = y_layout == B200ATTN_LAYOUT_BTHD;  // y is written densely
     p.x = x;
     p.y = y;
     p.rstd = rstd;
@@ -343,15 +376,15 @@ extern "C" int b200attn_rope_norm_fwd(const void* x, int x_dtype, int x_layout, 
     p.cos_t = cos_t;
     p.sin_t = sin_t;
     p.eps = eps;
-    const unsigned grid = rope_norm_grid((long long)B * T * H, 8);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool f32 = x_dtype == B200ATTN_DTYPE_F32;
+    const long long rows = (long long)B * T * H;
     if (D == 64) {
-        if (f32) rope_norm_fwd_kernel<64, true><<<grid, kRopeNormThreads, 0, st>>>(p);
-        else rope_norm_fwd_kernel<64, false><<<grid, kRopeNormThreads, 0, st>>>(p);
+        if (f32) rope_norm_launch_fwd<64, true>(p, rows, st);
+        else rope_norm_launch_fwd<64, false>(p, rows, st);
     } else {
-        if (f32) rope_norm_fwd_kernel<128, true><<<grid, kRopeNormThreads, 0, st>>>(p);
-        else rope_norm_fwd_kernel<128, false><<<grid, kRopeNormThreads, 0, st>>>(p);
+        if (f32) rope_norm_launch_fwd<128, true>(p, rows, st);
+        else rope_norm_launch_fwd<128, false>(p, rows, st);
     }
     if (cudaGetLastError() != cudaSuccess) return B200ATTN_ERR_CUDA;
     return B200ATTN_OK;
@@ -359,7 +392,7 @@ extern "C" int b200attn_rope_norm_fwd(const void* x, int x_dtype, int x_layout, 
 
 extern "C" size_t b200attn_rope_norm_bwd_workspace_bytes(int D) {
     if (D <= 0) return 0;
-    return (size_t)2 * sm_count() * D * sizeof(float);
+    return (size_t)kRopeNormMaxCtasPerSm * sm_count() * D * sizeof(float);
 }
 
 extern "C" int b200attn_rope_norm_bwd(const void* dy, int y_layout, const void* x, int x_dtype, int x_layout,
@@ -375,6 +408,7 @@ extern "C" int b200attn_rope_norm_bwd(const void* dy, int y_layout, const void* 
         return B200ATTN_ERR_WORKSPACE;
     RopeNormParams p = {};
     rope_norm_fill(p, B, T, H, D, x_layout, y_layout);
+    p.walk_bthd = x_layout == B200ATTN_LAYOUT_BTHD;  // d_x is written densely
     p.x = x;
     p.y = dx;
     p.dy = static_cast<const uint16_t*>(dy);
@@ -383,17 +417,15 @@ extern "C" int b200attn_rope_norm_bwd(const void* dy, int y_layout, const void* 
     p.cos_t = cos_t;
     p.sin_t = sin_t;
     p.partial = static_cast<float*>(workspace);
-    const unsigned grid = rope_norm_grid((long long)B * T * H, 2);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool f32 = x_dtype == B200ATTN_DTYPE_F32;
+    const long long rows = (long long)B * T * H;
     if (D == 64) {
-        if (f32) rope_norm_bwd_kernel<64, true><<<grid, kRopeNormThreads, 0, st>>>(p);
-        else rope_norm_bwd_kernel<64, false><<<grid, kRopeNormThreads, 0, st>>>(p);
-        rope_norm_dgamma_kernel<64><<<1, 64, 0, st>>>(p.partial, (int)grid, d_gamma);
+        const unsigned grid = f32 ? rope_norm_launch_bwd<64, true>(p, rows, st) : rope_norm_launch_bwd<64, false>(p, rows, st);
+        rope_norm_dgamma_kernel<64><<<64, 32, 0, st>>>(p.partial, (int)grid, d_gamma);
     } else {
-        if (f32) rope_norm_bwd_kernel<128, true><<<grid, kRopeNormThreads, 0, st>>>(p);
-        else rope_norm_bwd_kernel<128, false><<<grid, kRopeNormThreads, 0, st>>>(p);
-        rope_norm_dgamma_kernel<128><<<1, 128, 0, st>>>(p.partial, (int)grid, d_gamma);
+        const unsigned grid = f32 ? rope_norm_launch_bwd<128, true>(p, rows, st) : rope_norm_launch_bwd<128, false>(p, rows, st);
+        rope_norm_dgamma_kernel<128><<<128, 32, 0, st>>>(p.partial, (int)grid, d_gamma);
     }
     if (cudaGetLastError() != cudaSuccess) return B200ATTN_ERR_CUDA;
     return B200ATTN_OK;

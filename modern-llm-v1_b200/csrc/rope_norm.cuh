@@ -16,9 +16,9 @@
 //   d_gamma[d] += sum over rows of dy[d] r[d] rstd
 //
 // The work is bound by HBM bandwidth (one read and one write of the tensor), so the kernels are built for
-// coalescing and for bytes in flight: a warp owns a row (D = 64: one rotation pair per lane, one 4- or 8-byte
-// access; D = 128: two pairs per lane), takes kRowsPerIter rows per loop iteration with all their loads issued
-// before the first use, and the grid is a multiple of the SM count.
+// coalescing and for bytes in flight: a lane owns 8 consecutive elements of a row (one 16-byte access for BF16,
+// two for FP32), so a row takes D / 8 lanes and a warp covers 32 / (D / 8) rows per access; kStepsPerIter
+// such accesses are issued before the first use, and the grid is a multiple of the SM count.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -36,14 +36,17 @@ struct RopeNormParams {
     const float* sin_t;  // [T, D/2]
     float* partial;      // backward: [gridDim.x, D] partial d_gamma sums
     int B, T, H;
-    int x_bthd;          // x is [B, T, H, D] (else [B, H, T, D]): the order in which rows are walked
+    unsigned div_h_mul, div_h_shr, div_t_mul, div_t_shr;  // division by H and by T as multiply + shift (rn_fastdiv)
+    int walk_bthd;       // rows are walked in [B, T, H] order (else [B, H, T]): the order of the tensor that is WRITTEN
+                         // (y in the forward, d_x in the backward), so that all stores are dense
     long long x_st, x_sh, x_sb;  // element strides of x (and of d_x): token, head, batch
     long long y_st, y_sh, y_sb;  // element strides of y (and of dy)
     float eps;
 };
 
 constexpr int kRopeNormThreads = 256;  // 8 warps
-constexpr int kRowsPerIter = 4;
+constexpr int kFwdSteps = 2;           // row groups per loop iteration (all their loads are issued first)
+constexpr int kBwdSteps = 2;
 
 __device__ __forceinline__ float rn_bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float rn_bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
@@ -57,175 +60,215 @@ __device__ __forceinline__ float rn_warp_sum(float v) {
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
+// sum over the LPR lanes that share a row (LPR a power of two, lanes of a row are adjacent)
+template <int LPR>
+__device__ __forceinline__ float rn_row_sum(float v) {
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Division of n < 2^31 by a fixed d through one multiply-high and one shift (the round-up method of Granlund and
+// Montgomery: mul = ceil(2^(31 + ceil(log2 d)) / d), shr = ceil(log2 d) - 1).  A hardware division costs about
+// as many instructions as the rest of a row's work.
+struct RnFastDiv {
+    unsigned mul, shr;
+};
+inline RnFastDiv rn_fastdiv_make(unsigned d) {
+    RnFastDiv f = {0u, 0u};
+    if (d <= 1) return f;
+    unsigned lg = 0;
+    while ((1u << lg) < d) ++lg;
+    const unsigned p = 31 + lg;
+    f.mul = static_cast<unsigned>(((1ull << p) + d - 1) / d);
+    f.shr = p - 32;
+    return f;
+}
+__device__ __forceinline__ unsigned rn_fastdiv(unsigned n, unsigned d, unsigned mul, unsigned shr) {
+    return d == 1 ? n : (__umulhi(n, mul) >> shr);
+}
 
 // Row r of the walk -> (batch, token, head)
-__device__ __forceinline__ void rn_decode_row(const RopeNormParams& p, long long r, int& b, int& t, int& h) {
-    if (p.x_bthd) {
-        h = int(r % p.H);
-        t = int((r / p.H) % p.T);
-        b = int(r / (static_cast<long long>(p.H) * p.T));
+__device__ __forceinline__ void rn_decode_row(const RopeNormParams& p, unsigned r, int& b, int& t, int& h) {
+    if (p.walk_bthd) {
+        const unsigned bt = rn_fastdiv(r, unsigned(p.H), p.div_h_mul, p.div_h_shr);
+        h = int(r - bt * unsigned(p.H));
+        b = int(rn_fastdiv(bt, unsigned(p.T), p.div_t_mul, p.div_t_shr));
+        t = int(bt - unsigned(b) * unsigned(p.T));
     } else {
-        t = int(r % p.T);
-        h = int((r / p.T) % p.H);
-        b = int(r / (static_cast<long long>(p.H) * p.T));
+        const unsigned bh = rn_fastdiv(r, unsigned(p.T), p.div_t_mul, p.div_t_shr);
+        t = int(r - bh * unsigned(p.T));
+        b = int(rn_fastdiv(bh, unsigned(p.H), p.div_h_mul, p.div_h_shr));
+        h = int(bh - unsigned(b) * unsigned(p.H));
     }
 }
 
-// PPL = rotation pairs per lane (D / 64); the lane owns elements [lane * 2 PPL, lane * 2 PPL + 2 PPL)
-template <int PPL, bool F32>
-__device__ __forceinline__ void rn_load_row(const void* base, long long off, int lane, float (&v)[2 * PPL]) {
+// 8 consecutive elements starting at element offset `off`
+template <bool F32>
+__device__ __forceinline__ void rn_load8(const void* base, long long off, float (&v)[8]) {
     if (F32) {
-        const float* ptr = static_cast<const float*>(base) + off + lane * 2 * PPL;
-        if (PPL == 1) {
-            const float2 a = *reinterpret_cast<const float2*>(ptr);
-            v[0] = a.x, v[1] = a.y;
-        } else {
-            const float4 a = *reinterpret_cast<const float4*>(ptr);
-            v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w;
-        }
+        const float4* ptr = reinterpret_cast<const float4*>(static_cast<const float*>(base) + off);
+        const float4 a = ptr[0], c = ptr[1];
+        v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = c.x, v[5] = c.y, v[6] = c.z, v[7] = c.w;
     } else {
-        const uint16_t* ptr = static_cast<const uint16_t*>(base) + off + lane * 2 * PPL;
-        if (PPL == 1) {
-            const uint32_t a = *reinterpret_cast<const uint32_t*>(ptr);
-            v[0] = rn_bf16_lo(a), v[1] = rn_bf16_hi(a);
-        } else {
-            const uint2 a = *reinterpret_cast<const uint2*>(ptr);
-            v[0] = rn_bf16_lo(a.x), v[1] = rn_bf16_hi(a.x), v[2] = rn_bf16_lo(a.y), v[3] = rn_bf16_hi(a.y);
-        }
+        const uint4 a = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + off);
+        v[0] = rn_bf16_lo(a.x), v[1] = rn_bf16_hi(a.x), v[2] = rn_bf16_lo(a.y), v[3] = rn_bf16_hi(a.y);
+        v[4] = rn_bf16_lo(a.z), v[5] = rn_bf16_hi(a.z), v[6] = rn_bf16_lo(a.w), v[7] = rn_bf16_hi(a.w);
     }
 }
-template <int PPL, bool F32>
-__device__ __forceinline__ void rn_store_row(void* base, long long off, int lane, const float (&v)[2 * PPL]) {
+template <bool F32>
+__device__ __forceinline__ void rn_store8(void* base, long long off, const float (&v)[8]) {
     if (F32) {
-        float* ptr = static_cast<float*>(base) + off + lane * 2 * PPL;
-        if (PPL == 1) *reinterpret_cast<float2*>(ptr) = make_float2(v[0], v[1]);
-        else *reinterpret_cast<float4*>(ptr) = make_float4(v[0], v[1], v[2], v[3]);
+        float4* ptr = reinterpret_cast<float4*>(static_cast<float*>(base) + off);
+        ptr[0] = make_float4(v[0], v[1], v[2], v[3]);
+        ptr[1] = make_float4(v[4], v[5], v[6], v[7]);
     } else {
-        uint16_t* ptr = static_cast<uint16_t*>(base) + off + lane * 2 * PPL;
-        if (PPL == 1) *reinterpret_cast<uint32_t*>(ptr) = rn_pack_bf16x2(v[0], v[1]);
-        else *reinterpret_cast<uint2*>(ptr) = make_uint2(rn_pack_bf16x2(v[0], v[1]), rn_pack_bf16x2(v[2], v[3]));
+        *reinterpret_cast<uint4*>(static_cast<uint16_t*>(base) + off) =
+            make_uint4(rn_pack_bf16x2(v[0], v[1]), rn_pack_bf16x2(v[2], v[3]), rn_pack_bf16x2(v[4], v[5]),
+                       rn_pack_bf16x2(v[6], v[7]));
     }
 }
 
 template <int D, bool F32>
-__global__ void __launch_bounds__(kRopeNormThreads) rope_norm_fwd_kernel(const RopeNormParams p) {
-    constexpr int PPL = D / 64;
+__global__ void __launch_bounds__(kRopeNormThreads, 3) rope_norm_fwd_kernel(const RopeNormParams p) {
+    constexpr int LPR = D / 8;      // lanes per row
+    constexpr int RPS = 32 / LPR;   // rows per warp and step
     const int lane = threadIdx.x & 31;
-    const long long n_rows = static_cast<long long>(p.B) * p.T * p.H;
-    const long long warp0 = (static_cast<long long>(blockIdx.x) * kRopeNormThreads + threadIdx.x) >> 5;
-    const long long n_warps = (static_cast<long long>(gridDim.x) * kRopeNormThreads) >> 5;
-    float gm[2 * PPL];
+    const int sub = lane / LPR, li = lane % LPR;  // row within the step, position within the row
+    const unsigned n_rows = unsigned(p.B) * unsigned(p.T) * unsigned(p.H);
+    const unsigned warp0 = (blockIdx.x * kRopeNormThreads + threadIdx.x) >> 5;
+    const unsigned n_warps = (gridDim.x * kRopeNormThreads) >> 5;
+    float gm[8];
 #pragma unroll
-    for (int e = 0; e < 2 * PPL; ++e) gm[e] = p.gamma[lane * 2 * PPL + e];
+    for (int e = 0; e < 8; ++e) gm[e] = p.gamma[li * 8 + e];
 
-    for (long long r0 = warp0 * kRowsPerIter; r0 < n_rows; r0 += n_warps * kRowsPerIter) {
-        float v[kRowsPerIter][2 * PPL], cs[kRowsPerIter][PPL], sn[kRowsPerIter][PPL];
-        int bb[kRowsPerIter], tt[kRowsPerIter], hh[kRowsPerIter];
+    for (unsigned long long r0 = static_cast<unsigned long long>(warp0) * (kFwdSteps * RPS); r0 < n_rows;
+         r0 += static_cast<unsigned long long>(n_warps) * (kFwdSteps * RPS)) {
+        float v[kFwdSteps][8];
+        float4 cs[kFwdSteps], sn[kFwdSteps];
+        int bb[kFwdSteps], tt[kFwdSteps], hh[kFwdSteps];
+        bool live[kFwdSteps];
         // all loads of the iteration first
 #pragma unroll
-        for (int k = 0; k < kRowsPerIter; ++k) {
-            const long long r = r0 + k;
-            if (r < n_rows) {
-                rn_decode_row(p, r, bb[k], tt[k], hh[k]);
-                rn_load_row<PPL, F32>(p.x, bb[k] * p.x_sb + tt[k] * p.x_st + hh[k] * p.x_sh, lane, v[k]);
-#pragma unroll
-                for (int i = 0; i < PPL; ++i) {
-                    cs[k][i] = p.cos_t[static_cast<long long>(tt[k]) * (D / 2) + lane * PPL + i];
-                    sn[k][i] = p.sin_t[static_cast<long long>(tt[k]) * (D / 2) + lane * PPL + i];
-                }
+        for (int k = 0; k < kFwdSteps; ++k) {
+            const unsigned long long r = r0 + k * RPS + sub;
+            live[k] = r < n_rows;
+            if (live[k]) {
+                rn_decode_row(p, unsigned(r), bb[k], tt[k], hh[k]);
+                rn_load8<F32>(p.x, bb[k] * p.x_sb + tt[k] * p.x_st + hh[k] * p.x_sh + li * 8, v[k]);
+                cs[k] = *reinterpret_cast<const float4*>(p.cos_t + static_cast<long long>(tt[k]) * (D / 2) + li * 4);
+                sn[k] = *reinterpret_cast<const float4*>(p.sin_t + static_cast<long long>(tt[k]) * (D / 2) + li * 4);
             }
         }
 #pragma unroll
-        for (int k = 0; k < kRowsPerIter; ++k) {
-            const long long r = r0 + k;
-            if (r >= n_rows) break;  // warp-uniform
-            float rot[2 * PPL];
+        for (int k = 0; k < kFwdSteps; ++k) {
+            float rot[8];
             float ss = 0.f;
+            if (live[k]) {
+                const float c[4] = {cs[k].x, cs[k].y, cs[k].z, cs[k].w}, s[4] = {sn[k].x, sn[k].y, sn[k].z, sn[k].w};
 #pragma unroll
-            for (int i = 0; i < PPL; ++i) {
-                const float x0 = v[k][2 * i], x1 = v[k][2 * i + 1];
-                rot[2 * i] = x0 * cs[k][i] - x1 * sn[k][i];
-                rot[2 * i + 1] = x0 * sn[k][i] + x1 * cs[k][i];
-                ss += rot[2 * i] * rot[2 * i] + rot[2 * i + 1] * rot[2 * i + 1];
+                for (int i = 0; i < 4; ++i) {
+                    const float x0 = v[k][2 * i], x1 = v[k][2 * i + 1];
+                    rot[2 * i] = x0 * c[i] - x1 * s[i];
+                    rot[2 * i + 1] = x0 * s[i] + x1 * c[i];
+                    ss += rot[2 * i] * rot[2 * i] + rot[2 * i + 1] * rot[2 * i + 1];
+                }
             }
-            ss = rn_warp_sum(ss);
-            const float rstd = rsqrtf(ss / float(D) + p.eps);
-            float out[2 * PPL];
+            ss = rn_row_sum<LPR>(ss);  // every lane takes part in the shuffles
+            if (live[k]) {
+                const float rstd = rsqrtf(ss / float(D) + p.eps);
+                float out[8];
 #pragma unroll
-            for (int e = 0; e < 2 * PPL; ++e) out[e] = rot[e] * rstd * gm[e];
-            rn_store_row<PPL, false>(p.y, bb[k] * p.y_sb + tt[k] * p.y_st + hh[k] * p.y_sh, lane, out);
-            if (lane == 0) p.rstd[(static_cast<long long>(bb[k]) * p.H + hh[k]) * p.T + tt[k]] = rstd;
+                for (int e = 0; e < 8; ++e) out[e] = rot[e] * rstd * gm[e];
+                rn_store8<false>(p.y, (static_cast<long long>(r0) + k * RPS + sub) * D + li * 8, out);  // y is dense in walk order
+                if (li == 0) p.rstd[(static_cast<long long>(bb[k]) * p.H + hh[k]) * p.T + tt[k]] = rstd;
+            }
         }
     }
 }
 
 template <int D, bool F32>
-__global__ void __launch_bounds__(kRopeNormThreads) rope_norm_bwd_kernel(const RopeNormParams p) {
-    constexpr int PPL = D / 64;
+__global__ void __launch_bounds__(kRopeNormThreads, 2) rope_norm_bwd_kernel(const RopeNormParams p) {
+    constexpr int LPR = D / 8;
+    constexpr int RPS = 32 / LPR;
     __shared__ float s_part[kRopeNormThreads / 32][D];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const long long n_rows = static_cast<long long>(p.B) * p.T * p.H;
-    const long long warp0 = (static_cast<long long>(blockIdx.x) * kRopeNormThreads + threadIdx.x) >> 5;
-    const long long n_warps = (static_cast<long long>(gridDim.x) * kRopeNormThreads) >> 5;
-    float gm[2 * PPL], dg[2 * PPL];
+    const int sub = lane / LPR, li = lane % LPR;
+    const unsigned n_rows = unsigned(p.B) * unsigned(p.T) * unsigned(p.H);
+    const unsigned warp0 = (blockIdx.x * kRopeNormThreads + threadIdx.x) >> 5;
+    const unsigned n_warps = (gridDim.x * kRopeNormThreads) >> 5;
+    float gm[8], dg[8];
 #pragma unroll
-    for (int e = 0; e < 2 * PPL; ++e) {
-        gm[e] = p.gamma[lane * 2 * PPL + e];
+    for (int e = 0; e < 8; ++e) {
+        gm[e] = p.gamma[li * 8 + e];
         dg[e] = 0.f;
     }
-    for (long long r0 = warp0 * kRowsPerIter; r0 < n_rows; r0 += n_warps * kRowsPerIter) {
-        float v[kRowsPerIter][2 * PPL], dyv[kRowsPerIter][2 * PPL], cs[kRowsPerIter][PPL], sn[kRowsPerIter][PPL];
-        float rs[kRowsPerIter];
-        int bb[kRowsPerIter], tt[kRowsPerIter], hh[kRowsPerIter];
+    for (unsigned long long r0 = static_cast<unsigned long long>(warp0) * (kBwdSteps * RPS); r0 < n_rows;
+         r0 += static_cast<unsigned long long>(n_warps) * (kBwdSteps * RPS)) {
+        float v[kBwdSteps][8], dyv[kBwdSteps][8], rs[kBwdSteps];
+        float4 cs[kBwdSteps], sn[kBwdSteps];
+        int bb[kBwdSteps], tt[kBwdSteps], hh[kBwdSteps];
+        bool live[kBwdSteps];
 #pragma unroll
-        for (int k = 0; k < kRowsPerIter; ++k) {
-            const long long r = r0 + k;
-            if (r < n_rows) {
-                rn_decode_row(p, r, bb[k], tt[k], hh[k]);
-                rn_load_row<PPL, F32>(p.x, bb[k] * p.x_sb + tt[k] * p.x_st + hh[k] * p.x_sh, lane, v[k]);
-                rn_load_row<PPL, false>(p.dy, bb[k] * p.y_sb + tt[k] * p.y_st + hh[k] * p.y_sh, lane, dyv[k]);
+        for (int k = 0; k < kBwdSteps; ++k) {
+            const unsigned long long r = r0 + k * RPS + sub;
+            live[k] = r < n_rows;
+            if (live[k]) {
+                rn_decode_row(p, unsigned(r), bb[k], tt[k], hh[k]);
+                rn_load8<F32>(p.x, static_cast<long long>(r) * D + li * 8, v[k]);  // x is dense in walk order
+                rn_load8<false>(p.dy, bb[k] * p.y_sb + tt[k] * p.y_st + hh[k] * p.y_sh + li * 8, dyv[k]);
                 rs[k] = p.rstd[(static_cast<long long>(bb[k]) * p.H + hh[k]) * p.T + tt[k]];
+                cs[k] = *reinterpret_cast<const float4*>(p.cos_t + static_cast<long long>(tt[k]) * (D / 2) + li * 4);
+                sn[k] = *reinterpret_cast<const float4*>(p.sin_t + static_cast<long long>(tt[k]) * (D / 2) + li * 4);
+            }
+        }
 #pragma unroll
-                for (int i = 0; i < PPL; ++i) {
-                    cs[k][i] = p.cos_t[static_cast<long long>(tt[k]) * (D / 2) + lane * PPL + i];
-                    sn[k][i] = p.sin_t[static_cast<long long>(tt[k]) * (D / 2) + lane * PPL + i];
+        for (int k = 0; k < kBwdSteps; ++k) {
+            float rot[8], g[8];
+            float s = 0.f;
+            float c[4] = {0.f, 0.f, 0.f, 0.f}, sv[4] = {0.f, 0.f, 0.f, 0.f};
+            if (live[k]) {
+                c[0] = cs[k].x, c[1] = cs[k].y, c[2] = cs[k].z, c[3] = cs[k].w;
+                sv[0] = sn[k].x, sv[1] = sn[k].y, sv[2] = sn[k].z, sv[3] = sn[k].w;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float x0 = v[k][2 * i], x1 = v[k][2 * i + 1];
+                    rot[2 * i] = x0 * c[i] - x1 * sv[i];
+                    rot[2 * i + 1] = x0 * sv[i] + x1 * c[i];
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    g[e] = dyv[k][e] * gm[e];
+                    s += g[e] * rot[e];
+                    dg[e] += dyv[k][e] * rot[e] * rs[k];
                 }
             }
-        }
+            s = rn_row_sum<LPR>(s);
+            if (live[k]) {
+                const float coeff = rs[k] * rs[k] * rs[k] * (1.f / float(D)) * s;
+                float dx[8];
 #pragma unroll
-        for (int k = 0; k < kRowsPerIter; ++k) {
-            const long long r = r0 + k;
-            if (r >= n_rows) break;  // warp-uniform
-            float rot[2 * PPL], g[2 * PPL];
-            float s = 0.f;
-#pragma unroll
-            for (int i = 0; i < PPL; ++i) {
-                const float x0 = v[k][2 * i], x1 = v[k][2 * i + 1];
-                rot[2 * i] = x0 * cs[k][i] - x1 * sn[k][i];
-                rot[2 * i + 1] = x0 * sn[k][i] + x1 * cs[k][i];
+                for (int i = 0; i < 4; ++i) {
+                    const float d0 = rs[k] * g[2 * i] - coeff * rot[2 * i];
+                    const float d1 = rs[k] * g[2 * i + 1] - coeff * rot[2 * i + 1];
+                    dx[2 * i] = d0 * c[i] + d1 * sv[i];
+                    dx[2 * i + 1] = -d0 * sv[i] + d1 * c[i];
+                }
+                rn_store8<F32>(p.y, (static_cast<long long>(r0) + k * RPS + sub) * D + li * 8, dx);
             }
-#pragma unroll
-            for (int e = 0; e < 2 * PPL; ++e) {
-                g[e] = dyv[k][e] * gm[e];
-                s += g[e] * rot[e];
-                dg[e] += dyv[k][e] * rot[e] * rs[k];
-            }
-            s = rn_warp_sum(s);
-            const float coeff = rs[k] * rs[k] * rs[k] * (1.f / float(D)) * s;
-            float dx[2 * PPL];
-#pragma unroll
-            for (int i = 0; i < PPL; ++i) {
-                const float d0 = rs[k] * g[2 * i] - coeff * rot[2 * i];
-                const float d1 = rs[k] * g[2 * i + 1] - coeff * rot[2 * i + 1];
-                dx[2 * i] = d0 * cs[k][i] + d1 * sn[k][i];
-                dx[2 * i + 1] = -d0 * sn[k][i] + d1 * cs[k][i];
-            }
-            rn_store_row<PPL, F32>(p.y, bb[k] * p.x_sb + tt[k] * p.x_st + hh[k] * p.x_sh, lane, dx);
         }
     }
-    // d_gamma: lanes hold per-column sums of their warp's rows; add the warps of the CTA in a fixed order
+    // d_gamma: a lane holds sums for its 8 columns over its rows.  Add the lanes that own the same columns
+    // (they differ in `sub`), then the warps of the CTA, both in a fixed order.
 #pragma unroll
-    for (int e = 0; e < 2 * PPL; ++e) s_part[warp][lane * 2 * PPL + e] = dg[e];
+    for (int e = 0; e < 8; ++e) {
+#pragma unroll
+        for (int o = LPR; o < 32; o <<= 1) dg[e] += __shfl_xor_sync(0xffffffffu, dg[e], o);
+    }
+    if (sub == 0) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s_part[warp][li * 8 + e] = dg[e];
+    }
     __syncthreads();
     for (int d = threadIdx.x; d < D; d += kRopeNormThreads) {
         float acc = 0.f;
@@ -235,14 +278,17 @@ __global__ void __launch_bounds__(kRopeNormThreads) rope_norm_bwd_kernel(const R
     }
 }
 
-// d_gamma[d] += sum over the CTAs' partial sums, in CTA order (one thread per column: bit-reproducible)
+// d_gamma[d] += sum of the CTAs' partial sums.  One warp per column: lane l adds parts l, l + 32, ... in order,
+// then the 32 lane sums are added in a fixed tree, so the result is bit-reproducible; the loads of a lane are
+// independent, which keeps this tail kernel at a few microseconds.
 template <int D>
-__global__ void rope_norm_dgamma_kernel(const float* __restrict__ partial, int n_parts, float* __restrict__ d_gamma) {
-    const int d = blockIdx.x * blockDim.x + threadIdx.x;
-    if (d >= D) return;
+__global__ void __launch_bounds__(32) rope_norm_dgamma_kernel(const float* __restrict__ partial, int n_parts,
+                                                              float* __restrict__ d_gamma) {
+    const int d = blockIdx.x, lane = threadIdx.x;
     float acc = 0.f;
-    for (int i = 0; i < n_parts; ++i) acc += partial[static_cast<long long>(i) * D + d];
-    d_gamma[d] += acc;
+    for (int i = lane; i < n_parts; i += 32) acc += partial[static_cast<long long>(i) * D + d];
+    acc = rn_warp_sum(acc);
+    if (lane == 0) d_gamma[d] += acc;
 }
 
 }  // namespace b200attn

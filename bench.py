@@ -372,7 +372,7 @@ def run_decode(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier)
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": cfg.name, "B_per_gpu": cfg.B, "cache_len": cfg.T, "Hq": cfg.Hq, "Hkv": cfg.Hkv,
                        "D": cfg.D, "l2": f"cache of {nbytes / 1e6:.0f} MB > 126 MB L2"},
-            "clocks": clocks, "gpu_launches": 2 * steps,
+            "clocks": clocks, "gpu_launches": 3 * steps,
             "roofline": {"bound": "hbm", "kernel": "attn_decode_kernel", "achieved": gbs / world, "peak": peak,
                          "unit": "GB/s", "frac": gbs / world / peak,
                          "traffic": 273453056 if cfg.name == "c5_decode" else None,  # profiles/attn_decode_c5_decode.md
@@ -408,15 +408,16 @@ def run_qkprep(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier)
         sets.append(s)
 
     def step(i):
-        for (H, gm, t) in zip(heads, gamma, sets[i % n_sets]):
-            m.rope_qknorm_forward(t["x"], cos, sin, gm, 1e-5, t["y"], t["rstd"], B, T, H, D)
-        for (H, gm, t) in zip(heads, gamma, sets[i % n_sets]):
-            m.rope_qknorm_backward(t["dy"], t["x"], cos, sin, gm, t["rstd"], t["dx"], t["dg"], B, T, H, D)
+        tq, tk = sets[i % n_sets]
+        m.rope_qknorm_forward_qk(tq["x"], tk["x"], cos, sin, gamma[0], gamma[1], 1e-5, tq["y"], tk["y"], tq["rstd"],
+                                 tk["rstd"], B, T, cfg.Hq, cfg.Hkv, D)
+        m.rope_qknorm_backward_qk(tq["dy"], tk["dy"], tq["x"], tk["x"], cos, sin, gamma[0], gamma[1], tq["rstd"],
+                                  tk["rstd"], tq["dx"], tk["dx"], tq["dg"], tk["dg"], B, T, cfg.Hq, cfg.Hkv, D)
 
     for i in range(warmup):
         step(i)
     m.device_status()
-    # Six short launches per step: issued one by one from Python the host, not the GPU, sets the pace
+    # Three short launches per step: issued one by one from Python the host, not the GPU, sets the pace
     # (about 20 us per call), so one round over the buffer sets is captured in a CUDA graph and replayed.
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
@@ -457,11 +458,11 @@ def run_qkprep(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier)
                    "io": "x, dy, dx BF16 [B,T,H,D] / [B,H,T,D]; y BF16 [B,H,T,D]; rstd FP32",
                    "l2": f"rotating over {n_sets} buffer sets, {n_sets * rows * D * 2 * 4 / 1e6:.0f} MB > 126 MB L2",
                    "launch": "one round over the buffer sets captured in a CUDA graph and replayed"},
-        "clocks": clocks, "gpu_launches": 6 * steps,
+        "clocks": clocks, "gpu_launches": 3 * steps,
         "roofline": {"bound": "hbm", "kernel": "rope_norm_fwd_kernel + rope_norm_bwd_kernel", "achieved": gbs / world,
                      "peak": peak, "unit": "GB/s", "frac": gbs / world / peak, "traffic": None,
                      "peak_source": f"hbm_gbs of {peaks['_source']}", "bytes_per_step": nbytes,
-                     "note": "6 launches per step: forward and backward on q and on k, and the two d_gamma sums"},
+                     "note": "3 launches per step: q and k together, forward, backward, d_gamma sums"},
     }
     if rank == 0 and not args.no_cpu_baseline:
         from oracle import attn_oracle as ao

@@ -149,6 +149,20 @@ int b200attn_rope_norm_bwd(const void* dy, int y_layout, const void* x, int x_dt
                            const float* gamma, const float* cos_t, const float* sin_t, void* dx, float* d_gamma, int B,
                            int T, int H, int D, void* workspace, size_t workspace_bytes, void* stream);
 size_t b200attn_rope_norm_bwd_workspace_bytes(int D);
+/*
+ * The same for q and k in one launch each way (what the model does back to back, llm/src/model/modern_gpt.cu:358-370
+ * and :527-544): q has Hq heads and its own gamma, k has Hkv heads and its own; type, layouts, tables, B, T, D and
+ * eps are shared.  Results are bit-identical to two single calls; the workspace size is the same.
+ */
+int b200attn_rope_norm_fwd_qk(const void* xq, const void* xk, int x_dtype, int x_layout, void* yq, void* yk, int y_layout,
+                              float* rstd_q, float* rstd_k, const float* gamma_q, const float* gamma_k,
+                              const float* cos_t, const float* sin_t, int B, int T, int Hq, int Hkv, int D, float eps,
+                              void* stream);
+int b200attn_rope_norm_bwd_qk(const void* dyq, const void* dyk, int y_layout, const void* xq, const void* xk, int x_dtype,
+                              int x_layout, const float* rstd_q, const float* rstd_k, const float* gamma_q,
+                              const float* gamma_k, const float* cos_t, const float* sin_t, void* dxq, void* dxk,
+                              float* d_gamma_q, float* d_gamma_k, int B, int T, int Hq, int Hkv, int D, void* workspace,
+                              size_t workspace_bytes, void* stream);
 
 /*
  * Diagnostics for benchmarks (no counterpart in the reference): when three CUDA events are

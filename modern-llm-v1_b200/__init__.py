@@ -16,7 +16,13 @@ from .flash_attn import (  # noqa: F401
     flash_attn_forward,
     flash_attn_forward_gqa,
 )
-from .rope_norm import make_rope_cache, rope_qknorm_backward, rope_qknorm_forward  # noqa: F401
+from .rope_norm import (  # noqa: F401
+    make_rope_cache,
+    rope_qknorm_backward,
+    rope_qknorm_backward_qk,
+    rope_qknorm_forward,
+    rope_qknorm_forward_qk,
+)
 
 __all__ = [
     "flash_attn_forward",
@@ -28,4 +34,6 @@ __all__ = [
     "make_rope_cache",
     "rope_qknorm_forward",
     "rope_qknorm_backward",
+    "rope_qknorm_forward_qk",
+    "rope_qknorm_backward_qk",
 ]

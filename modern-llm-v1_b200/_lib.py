@@ -45,6 +45,8 @@ SYMBOLS = (
     "b200attn_rope_norm_fwd",
     "b200attn_rope_norm_bwd",
     "b200attn_rope_norm_bwd_workspace_bytes",
+    "b200attn_rope_norm_fwd_qk",
+    "b200attn_rope_norm_bwd_qk",
     "b200attn_last_device_status",
     "b200attn_strerror",
     "b200attn_version",
@@ -86,6 +88,11 @@ def load() -> ctypes.CDLL:
     L.b200attn_rope_norm_fwd.restype = i
     L.b200attn_rope_norm_bwd.argtypes = [vp, i, vp, i, i, vp, vp, vp, vp, vp, vp, i, i, i, i, vp, sz, vp]
     L.b200attn_rope_norm_bwd.restype = i
+    L.b200attn_rope_norm_fwd_qk.argtypes = [vp, vp, i, i, vp, vp, i, vp, vp, vp, vp, vp, vp, i, i, i, i, i, f, vp]
+    L.b200attn_rope_norm_fwd_qk.restype = i
+    L.b200attn_rope_norm_bwd_qk.argtypes = [vp, vp, i, vp, vp, i, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i,
+                                            vp, sz, vp]
+    L.b200attn_rope_norm_bwd_qk.restype = i
     L.b200attn_rope_norm_bwd_workspace_bytes.argtypes = [i]
     L.b200attn_rope_norm_bwd_workspace_bytes.restype = sz
     L.b200attn_last_device_status.argtypes = [vp]

@@ -318,18 +318,22 @@ unsigned rope_norm_grid(K kernel, long long rows, int rows_per_cta_iter, int* ca
 }
 
 template <int D, bool F32>
-void rope_norm_launch_fwd(const RopeNormParams& p, long long rows, cudaStream_t st) {
+void rope_norm_launch_fwd(const RopeNormParams& p0, const RopeNormParams& p1, int n_tensors, long long rows,
+                          cudaStream_t st) {
     static int occ[kMaxDevices] = {0};
     const unsigned grid = rope_norm_grid(rope_norm_fwd_kernel<D, F32>, rows, (kRopeNormThreads / 32) * kFwdSteps * (256 / D), occ);
-    rope_norm_fwd_kernel<D, F32><<<grid, kRopeNormThreads, 0, st>>>(p);
+    rope_norm_fwd_kernel<D, F32><<<grid, kRopeNormThreads, 0, st>>>(p0, p1, n_tensors);
 }
 template <int D, bool F32>
-unsigned rope_norm_launch_bwd(const RopeNormParams& p, long long rows, cudaStream_t st) {
+void rope_norm_launch_bwd(RopeNormParams p0, RopeNormParams p1, int n_tensors, long long rows, float* workspace,
+                          cudaStream_t st) {
     static int occ[kMaxDevices] = {0};
     unsigned grid = rope_norm_grid(rope_norm_bwd_kernel<D, F32>, rows, (kRopeNormThreads / 32) * kBwdSteps * (256 / D), occ);
     grid = std::min(grid, (unsigned)(kRopeNormMaxCtasPerSm * sm_count()));  // the workspace holds that many partial sums
-    rope_norm_bwd_kernel<D, F32><<<grid, kRopeNormThreads, 0, st>>>(p);
-    return grid;
+    p0.partial = workspace;
+    p1.partial = workspace + (size_t)kRopeNormMaxCtasPerSm * sm_count() * D;
+    rope_norm_bwd_kernel<D, F32><<<grid, kRopeNormThreads, 0, st>>>(p0, p1, n_tensors);
+    rope_norm_dgamma_kernel<D><<<n_tensors * D, 32, 0, st>>>(p0.partial, p0.d_gamma, p1.partial, p1.d_gamma, (int)grid);
 }
 
 void rope_norm_fill(RopeNormParams& p, int B, int T, int H, int D, int x_layout, int y_layout) {
@@ -341,6 +345,69 @@ void rope_norm_fill(RopeNormParams& p, int B, int T, int H, int D, int x_layout,
     p.y_st = sy.t, p.y_sh = sy.h, p.y_sb = sy.b;
     const RnFastDiv dh = rn_fastdiv_make((unsigned)H), dt = rn_fastdiv_make((unsigned)T);
     p.div_h_mul = dh.mul, p.div_h_shr = dh.shr, p.div_t_mul = dt.mul, p.div_t_shr = dt.shr;
+}
+
+struct RopeNormTensor {  // what differs between q and k
+    const void* x;
+    void* y;            // forward: y; backward: d_x
+    const void* dy;     // backward only
+    float* rstd;
+    const float* gamma;
+    float* d_gamma;     // backward only
+    int H;
+};
+
+int rope_norm_run(bool backward, const RopeNormTensor* t, int n_tensors, int x_dtype, int x_layout, int y_layout,
+                  const float* cos_t, const float* sin_t, int B, int T, int D, float eps, void* workspace,
+                  size_t workspace_bytes, void* stream) {
+    RopeNormParams p[2] = {};
+    long long rows = 0;
+    for (int i = 0; i < n_tensors; ++i) {
+        int rc = rope_norm_check(B, T, t[i].H, D, x_dtype, x_layout, y_layout);
+        if (rc) return rc;
+        if (!t[i].x || !t[i].y || !t[i].rstd || !t[i].gamma || (backward && (!t[i].dy || !t[i].d_gamma)))
+            return B200ATTN_ERR_INVALID_ARG;
+        if (!aligned16(t[i].x) || !aligned16(t[i].y) || (backward && !aligned16(t[i].dy))) return B200ATTN_ERR_ALIGNMENT;
+        rope_norm_fill(p[i], B, T, t[i].H, D, x_layout, y_layout);
+        // rows are walked in the order of the tensor that is written (y forward, d_x backward): dense stores
+        p[i].walk_bthd = (backward ? x_layout : y_layout) == B200ATTN_LAYOUT_BTHD;
+        p[i].x = t[i].x;
+        p[i].y = t[i].y;
+        p[i].dy = static_cast<const uint16_t*>(t[i].dy);
+        p[i].rstd = t[i].rstd;
+        p[i].gamma = t[i].gamma;
+        p[i].d_gamma = t[i].d_gamma;
+        p[i].cos_t = cos_t;
+        p[i].sin_t = sin_t;
+        p[i].eps = eps;
+        rows = std::max(rows, (long long)B * T * t[i].H);
+    }
+    if (!cos_t || !sin_t) return B200ATTN_ERR_INVALID_ARG;
+    if (backward && (!workspace || workspace_bytes < b200attn_rope_norm_bwd_workspace_bytes(D) ||
+                     (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0))
+        return B200ATTN_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool f32 = x_dtype == B200ATTN_DTYPE_F32;
+    float* ws = static_cast<float*>(workspace);
+    if (!backward) {
+        if (D == 64) {
+            if (f32) rope_norm_launch_fwd<64, true>(p[0], p[1], n_tensors, rows, st);
+            else rope_norm_launch_fwd<64, false>(p[0], p[1], n_tensors, rows, st);
+        } else {
+            if (f32) rope_norm_launch_fwd<128, true>(p[0], p[1], n_tensors, rows, st);
+            else rope_norm_launch_fwd<128, false>(p[0], p[1], n_tensors, rows, st);
+        }
+    } else {
+        if (D == 64) {
+            if (f32) rope_norm_launch_bwd<64, true>(p[0], p[1], n_tensors, rows, ws, st);
+            else rope_norm_launch_bwd<64, false>(p[0], p[1], n_tensors, rows, ws, st);
+        } else {
+            if (f32) rope_norm_launch_bwd<128, true>(p[0], p[1], n_tensors, rows, ws, st);
+            else rope_norm_launch_bwd<128, false>(p[0], p[1], n_tensors, rows, ws, st);
+        }
+    }
+    if (cudaGetLastError() != cudaSuccess) return B200ATTN_ERR_CUDA;
+    return B200ATTN_OK;
 }
 
 }  // namespace
@@ -359,76 +426,45 @@ extern "C" int b200attn_rope_table(int T, int D, float base, float* cos_host, fl
     return B200ATTN_OK;
 }
 
+extern "C" size_t b200attn_rope_norm_bwd_workspace_bytes(int D) {
+    if (D <= 0) return 0;
+    return (size_t)2 * kRopeNormMaxCtasPerSm * sm_count() * D * sizeof(float);  // partial sums for up to two tensors
+}
+
 extern "C" int b200attn_rope_norm_fwd(const void* x, int x_dtype, int x_layout, void* y, int y_layout, float* rstd,
                                       const float* gamma, const float* cos_t, const float* sin_t, int B, int T, int H,
                                       int D, float eps, void* stream) {
-    int rc = rope_norm_check(B, T, H, D, x_dtype, x_layout, y_layout);
-    if (rc) return rc;
-    if (!x || !y || !rstd || !gamma || !cos_t || !sin_t) return B200ATTN_ERR_INVALID_ARG;
-    if (!aligned16(x) || !aligned16(y)) return B200ATTN_ERR_ALIGNMENT;
-    RopeNormParams p = {};
-    rope_norm_fill(p, B, T, H, D, x_layout, y_layout);
-    p.walk_bthd = y_layout == B200ATTN_LAYOUT_BTHD;  // y is written densely
-    p.x = x;
-    p.y = y;
-    p.rstd = rstd;
-    p.gamma = gamma;
-    p.cos_t = cos_t;
-    p.sin_t = sin_t;
-    p.eps = eps;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const bool f32 = x_dtype == B200ATTN_DTYPE_F32;
-    const long long rows = (long long)B * T * H;
-    if (D == 64) {
-        if (f32) rope_norm_launch_fwd<64, true>(p, rows, st);
-        else rope_norm_launch_fwd<64, false>(p, rows, st);
-    } else {
-        if (f32) rope_norm_launch_fwd<128, true>(p, rows, st);
-        else rope_norm_launch_fwd<128, false>(p, rows, st);
-    }
-    if (cudaGetLastError() != cudaSuccess) return B200ATTN_ERR_CUDA;
-    return B200ATTN_OK;
-}
-
-extern "C" size_t b200attn_rope_norm_bwd_workspace_bytes(int D) {
-    if (D <= 0) return 0;
-    return (size_t)kRopeNormMaxCtasPerSm * sm_count() * D * sizeof(float);
+    const RopeNormTensor t = {x, y, nullptr, rstd, gamma, nullptr, H};
+    return rope_norm_run(false, &t, 1, x_dtype, x_layout, y_layout, cos_t, sin_t, B, T, D, eps, nullptr, 0, stream);
 }
 
 extern "C" int b200attn_rope_norm_bwd(const void* dy, int y_layout, const void* x, int x_dtype, int x_layout,
                                       const float* rstd, const float* gamma, const float* cos_t, const float* sin_t,
                                       void* dx, float* d_gamma, int B, int T, int H, int D, void* workspace,
                                       size_t workspace_bytes, void* stream) {
-    int rc = rope_norm_check(B, T, H, D, x_dtype, x_layout, y_layout);
-    if (rc) return rc;
-    if (!dy || !x || !rstd || !gamma || !cos_t || !sin_t || !dx || !d_gamma) return B200ATTN_ERR_INVALID_ARG;
-    if (!aligned16(x) || !aligned16(dy) || !aligned16(dx)) return B200ATTN_ERR_ALIGNMENT;
-    if (!workspace || workspace_bytes < b200attn_rope_norm_bwd_workspace_bytes(D) ||
-        (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
-        return B200ATTN_ERR_WORKSPACE;
-    RopeNormParams p = {};
-    rope_norm_fill(p, B, T, H, D, x_layout, y_layout);
-    p.walk_bthd = x_layout == B200ATTN_LAYOUT_BTHD;  // d_x is written densely
-    p.x = x;
-    p.y = dx;
-    p.dy = static_cast<const uint16_t*>(dy);
-    p.rstd = const_cast<float*>(rstd);
-    p.gamma = gamma;
-    p.cos_t = cos_t;
-    p.sin_t = sin_t;
-    p.partial = static_cast<float*>(workspace);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const bool f32 = x_dtype == B200ATTN_DTYPE_F32;
-    const long long rows = (long long)B * T * H;
-    if (D == 64) {
-        const unsigned grid = f32 ? rope_norm_launch_bwd<64, true>(p, rows, st) : rope_norm_launch_bwd<64, false>(p, rows, st);
-        rope_norm_dgamma_kernel<64><<<64, 32, 0, st>>>(p.partial, (int)grid, d_gamma);
-    } else {
-        const unsigned grid = f32 ? rope_norm_launch_bwd<128, true>(p, rows, st) : rope_norm_launch_bwd<128, false>(p, rows, st);
-        rope_norm_dgamma_kernel<128><<<128, 32, 0, st>>>(p.partial, (int)grid, d_gamma);
-    }
-    if (cudaGetLastError() != cudaSuccess) return B200ATTN_ERR_CUDA;
-    return B200ATTN_OK;
+    const RopeNormTensor t = {x, dx, dy, const_cast<float*>(rstd), gamma, d_gamma, H};
+    return rope_norm_run(true, &t, 1, x_dtype, x_layout, y_layout, cos_t, sin_t, B, T, D, 0.f, workspace, workspace_bytes,
+                         stream);
+}
+
+extern "C" int b200attn_rope_norm_fwd_qk(const void* xq, const void* xk, int x_dtype, int x_layout, void* yq, void* yk,
+                                         int y_layout, float* rstd_q, float* rstd_k, const float* gamma_q,
+                                         const float* gamma_k, const float* cos_t, const float* sin_t, int B, int T,
+                                         int Hq, int Hkv, int D, float eps, void* stream) {
+    const RopeNormTensor t[2] = {{xq, yq, nullptr, rstd_q, gamma_q, nullptr, Hq}, {xk, yk, nullptr, rstd_k, gamma_k, nullptr, Hkv}};
+    return rope_norm_run(false, t, 2, x_dtype, x_layout, y_layout, cos_t, sin_t, B, T, D, eps, nullptr, 0, stream);
+}
+
+extern "C" int b200attn_rope_norm_bwd_qk(const void* dyq, const void* dyk, int y_layout, const void* xq, const void* xk,
+                                         int x_dtype, int x_layout, const float* rstd_q, const float* rstd_k,
+                                         const float* gamma_q, const float* gamma_k, const float* cos_t,
+                                         const float* sin_t, void* dxq, void* dxk, float* d_gamma_q, float* d_gamma_k,
+                                         int B, int T, int Hq, int Hkv, int D, void* workspace, size_t workspace_bytes,
+                                         void* stream) {
+    const RopeNormTensor t[2] = {{xq, dxq, dyq, const_cast<float*>(rstd_q), gamma_q, d_gamma_q, Hq},
+                                 {xk, dxk, dyk, const_cast<float*>(rstd_k), gamma_k, d_gamma_k, Hkv}};
+    return rope_norm_run(true, t, 2, x_dtype, x_layout, y_layout, cos_t, sin_t, B, T, D, 0.f, workspace, workspace_bytes,
+                         stream);
 }
 
 extern "C" int b200attn_set_bwd_profile_events(void* e0, void* e1, void* e2) {

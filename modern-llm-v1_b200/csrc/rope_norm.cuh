@@ -35,6 +35,7 @@ struct RopeNormParams {
     const float* cos_t;  // [T, D/2]
     const float* sin_t;  // [T, D/2]
     float* partial;      // backward: [gridDim.x, D] partial d_gamma sums
+    float* d_gamma;      // backward: [D], accumulated into by rope_norm_dgamma_kernel
     int B, T, H;
     unsigned div_h_mul, div_h_shr, div_t_mul, div_t_shr;  // division by H and by T as multiply + shift (rn_fastdiv)
     int walk_bthd;       // rows are walked in [B, T, H] order (else [B, H, T]): the order of the tensor that is WRITTEN
@@ -129,15 +130,17 @@ __device__ __forceinline__ void rn_store8(void* base, long long off, const float
     }
 }
 
+// One tensor's forward.  (A function of its own, called once per tensor with the kernel parameter itself, so that
+// every field stays a constant-bank operand; selecting the struct at run time would move it to local memory.)
 template <int D, bool F32>
-__global__ void __launch_bounds__(kRopeNormThreads, 3) rope_norm_fwd_kernel(const RopeNormParams p) {
+__device__ __forceinline__ void rope_norm_fwd_tensor(const RopeNormParams& p) {
     constexpr int LPR = D / 8;      // lanes per row
     constexpr int RPS = 32 / LPR;   // rows per warp and step
     const int lane = threadIdx.x & 31;
     const int sub = lane / LPR, li = lane % LPR;  // row within the step, position within the row
-    const unsigned n_rows = unsigned(p.B) * unsigned(p.T) * unsigned(p.H);
     const unsigned warp0 = (blockIdx.x * kRopeNormThreads + threadIdx.x) >> 5;
     const unsigned n_warps = (gridDim.x * kRopeNormThreads) >> 5;
+    const unsigned n_rows = unsigned(p.B) * unsigned(p.T) * unsigned(p.H);
     float gm[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) gm[e] = p.gamma[li * 8 + e];
@@ -187,16 +190,24 @@ __global__ void __launch_bounds__(kRopeNormThreads, 3) rope_norm_fwd_kernel(cons
     }
 }
 
+// one launch takes q and k (n_tensors = 2), one after the other
 template <int D, bool F32>
-__global__ void __launch_bounds__(kRopeNormThreads, 2) rope_norm_bwd_kernel(const RopeNormParams p) {
+__global__ void __launch_bounds__(kRopeNormThreads, 3)
+rope_norm_fwd_kernel(const __grid_constant__ RopeNormParams p0, const __grid_constant__ RopeNormParams p1,
+                     const int n_tensors) {
+    rope_norm_fwd_tensor<D, F32>(p0);
+    if (n_tensors > 1) rope_norm_fwd_tensor<D, F32>(p1);
+}
+
+template <int D, bool F32>
+__device__ __forceinline__ void rope_norm_bwd_tensor(const RopeNormParams& p, float (*s_part)[D]) {
     constexpr int LPR = D / 8;
     constexpr int RPS = 32 / LPR;
-    __shared__ float s_part[kRopeNormThreads / 32][D];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sub = lane / LPR, li = lane % LPR;
-    const unsigned n_rows = unsigned(p.B) * unsigned(p.T) * unsigned(p.H);
     const unsigned warp0 = (blockIdx.x * kRopeNormThreads + threadIdx.x) >> 5;
     const unsigned n_warps = (gridDim.x * kRopeNormThreads) >> 5;
+    const unsigned n_rows = unsigned(p.B) * unsigned(p.T) * unsigned(p.H);
     float gm[8], dg[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
@@ -276,15 +287,30 @@ __global__ void __launch_bounds__(kRopeNormThreads, 2) rope_norm_bwd_kernel(cons
         for (int w = 0; w < kRopeNormThreads / 32; ++w) acc += s_part[w][d];
         p.partial[static_cast<long long>(blockIdx.x) * D + d] = acc;
     }
+    __syncthreads();  // s_part is rewritten for the next tensor
 }
 
-// d_gamma[d] += sum of the CTAs' partial sums.  One warp per column: lane l adds parts l, l + 32, ... in order,
-// then the 32 lane sums are added in a fixed tree, so the result is bit-reproducible; the loads of a lane are
-// independent, which keeps this tail kernel at a few microseconds.
+template <int D, bool F32>
+__global__ void __launch_bounds__(kRopeNormThreads, 2)
+rope_norm_bwd_kernel(const __grid_constant__ RopeNormParams p0, const __grid_constant__ RopeNormParams p1,
+                     const int n_tensors) {
+    __shared__ float s_part[kRopeNormThreads / 32][D];
+    rope_norm_bwd_tensor<D, F32>(p0, s_part);
+    if (n_tensors > 1) rope_norm_bwd_tensor<D, F32>(p1, s_part);
+}
+
+// d_gamma[d] += sum of the CTAs' partial sums, for one or two tensors.  One warp per column (CTA c takes column
+// c % D of tensor c / D): lane l adds parts l, l + 32, ... in order, then the 32 lane sums are added in a fixed
+// tree, so the result is bit-reproducible; the loads of a lane are independent, which keeps this tail kernel at a
+// microsecond or two.  (Done by the last CTA of the backward kernel instead, the same sums took 25 us: one CTA
+// cannot keep enough loads in flight.)
 template <int D>
-__global__ void __launch_bounds__(32) rope_norm_dgamma_kernel(const float* __restrict__ partial, int n_parts,
-                                                              float* __restrict__ d_gamma) {
-    const int d = blockIdx.x, lane = threadIdx.x;
+__global__ void __launch_bounds__(32) rope_norm_dgamma_kernel(const float* __restrict__ partial0, float* __restrict__ d_gamma0,
+                                                              const float* __restrict__ partial1, float* __restrict__ d_gamma1,
+                                                              int n_parts) {
+    const int ts = blockIdx.x / D, d = blockIdx.x % D, lane = threadIdx.x;
+    const float* partial = ts ? partial1 : partial0;
+    float* d_gamma = ts ? d_gamma1 : d_gamma0;
     float acc = 0.f;
     for (int i = lane; i < n_parts; i += 32) acc += partial[static_cast<long long>(i) * D + d];
     acc = rn_warp_sum(acc);

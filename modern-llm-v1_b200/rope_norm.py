@@ -91,3 +91,53 @@ def rope_qknorm_backward(d_y, x, cos, sin, gamma, rstd, d_x, d_gamma, B, T, H, D
                                           _lib.LAYOUTS[x_layout], rstd.data_ptr(), gamma.data_ptr(), cos.data_ptr(),
                                           sin.data_ptr(), d_x.data_ptr(), d_gamma.data_ptr(), B, T, H, D, ws.data_ptr(),
                                           ws.numel(), _stream_ptr()), fn)
+
+
+def rope_qknorm_forward_qk(xq, xk, cos, sin, gamma_q, gamma_k, eps, yq, yk, rstd_q, rstd_k, B, T, Hq, Hkv, D,
+                           x_layout="BTHD", y_layout="BHTD"):
+    """rope_qknorm_forward for q (Hq heads) and k (Hkv heads) in one launch; bit-identical to two calls."""
+    fn = "rope_qknorm_forward"
+    xd = _x_dtype(fn, xq)
+    if xk.dtype != xq.dtype:
+        raise ValueError(f"{fn}: xq and xk must have the same dtype")
+    bf = torch.bfloat16
+    _common(fn, [(xq, "xq", xq.dtype), (xk, "xk", xq.dtype), (yq, "yq", bf), (yk, "yk", bf),
+                 (gamma_k, "gamma_k", torch.float32), (rstd_k, "rstd_k", torch.float32)],
+            xq, cos, sin, gamma_q, rstd_q, B, T, Hq, D, x_layout, y_layout)
+    if xk.numel() != B * T * Hkv * D or yq.numel() != xq.numel() or yk.numel() != xk.numel():
+        raise ValueError(f"{fn}: shape mismatch (xk/yq/yk)")
+    if gamma_k.numel() != D or rstd_k.numel() != B * Hkv * T:
+        raise ValueError(f"{fn}: shape mismatch (gamma_k/rstd_k)")
+    lib = _lib.load()
+    _lib.check(lib.b200attn_rope_norm_fwd_qk(xq.data_ptr(), xk.data_ptr(), xd, _lib.LAYOUTS[x_layout], yq.data_ptr(),
+                                             yk.data_ptr(), _lib.LAYOUTS[y_layout], rstd_q.data_ptr(), rstd_k.data_ptr(),
+                                             gamma_q.data_ptr(), gamma_k.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                             B, T, Hq, Hkv, D, ctypes.c_float(eps), _stream_ptr()), fn)
+
+
+def rope_qknorm_backward_qk(d_yq, d_yk, xq, xk, cos, sin, gamma_q, gamma_k, rstd_q, rstd_k, d_xq, d_xk, d_gamma_q,
+                            d_gamma_k, B, T, Hq, Hkv, D, x_layout="BTHD", y_layout="BHTD"):
+    """rope_qknorm_backward for q and k in one launch; bit-identical to two calls."""
+    fn = "rope_qknorm_backward"
+    xd = _x_dtype(fn, xq)
+    if xk.dtype != xq.dtype:
+        raise ValueError(f"{fn}: xq and xk must have the same dtype")
+    bf, f32 = torch.bfloat16, torch.float32
+    _common(fn, [(d_yq, "d_yq", bf), (d_yk, "d_yk", bf), (xq, "xq", xq.dtype), (xk, "xk", xq.dtype),
+                 (d_xq, "d_xq", xq.dtype), (d_xk, "d_xk", xq.dtype), (d_gamma_q, "d_gamma_q", f32),
+                 (d_gamma_k, "d_gamma_k", f32), (gamma_k, "gamma_k", f32), (rstd_k, "rstd_k", f32)],
+            xq, cos, sin, gamma_q, rstd_q, B, T, Hq, D, x_layout, y_layout)
+    nq, nk = B * T * Hq * D, B * T * Hkv * D
+    if xk.numel() != nk or d_yq.numel() != nq or d_yk.numel() != nk or d_xq.numel() != nq or d_xk.numel() != nk:
+        raise ValueError(f"{fn}: shape mismatch (xk/d_y/d_x)")
+    if gamma_k.numel() != D or rstd_k.numel() != B * Hkv * T or d_gamma_q.numel() != D or d_gamma_k.numel() != D:
+        raise ValueError(f"{fn}: shape mismatch (gamma_k/rstd_k/d_gamma)")
+    lib = _lib.load()
+    nbytes = int(lib.b200attn_rope_norm_bwd_workspace_bytes(D))
+    ws = _workspace("rope_norm_bwd", nbytes, xq.device)
+    _lib.check(lib.b200attn_rope_norm_bwd_qk(d_yq.data_ptr(), d_yk.data_ptr(), _lib.LAYOUTS[y_layout], xq.data_ptr(),
+                                             xk.data_ptr(), xd, _lib.LAYOUTS[x_layout], rstd_q.data_ptr(),
+                                             rstd_k.data_ptr(), gamma_q.data_ptr(), gamma_k.data_ptr(), cos.data_ptr(),
+                                             sin.data_ptr(), d_xq.data_ptr(), d_xk.data_ptr(), d_gamma_q.data_ptr(),
+                                             d_gamma_k.data_ptr(), B, T, Hq, Hkv, D, ws.data_ptr(), ws.numel(),
+                                             _stream_ptr()), fn)

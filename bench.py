@@ -36,8 +36,8 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 # DRAM traffic of the dominant kernel per launch at the default workload, from the committed ncu
 # summary (profiles/); None until a capture exists for the current kernel.
 # (dram read + write per launch of each kernel, profiles/attn_fwd_bwd_c2_50m_train.md)
-NCU_TRAFFIC_BYTES = {"c2_50m_train": {"attn_fwd_kernel": 21031936, "attn_bwd_dq_kernel": 46682112,
-                                      "attn_bwd_dkdv_kernel": 34404864}}
+NCU_TRAFFIC_BYTES = {"c2_50m_train": {"attn_fwd_kernel": 21033472, "attn_bwd_dq_kernel": 46723584,
+                                      "attn_bwd_dkdv_kernel": 34438400}}
 
 
 def load_peaks():
@@ -460,7 +460,8 @@ def run_qkprep(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier)
                    "launch": "one round over the buffer sets captured in a CUDA graph and replayed"},
         "clocks": clocks, "gpu_launches": 3 * steps,
         "roofline": {"bound": "hbm", "kernel": "rope_norm_fwd_kernel + rope_norm_bwd_kernel", "achieved": gbs / world,
-                     "peak": peak, "unit": "GB/s", "frac": gbs / world / peak, "traffic": None,
+                     "peak": peak, "unit": "GB/s", "frac": gbs / world / peak,
+                     "traffic": 799593216 if cfg.name == "c4_long_context" else None,  # profiles/rope_norm_c4_long_context.md
                      "peak_source": f"hbm_gbs of {peaks['_source']}", "bytes_per_step": nbytes,
                      "note": "3 launches per step: q and k together, forward, backward, d_gamma sums"},
     }

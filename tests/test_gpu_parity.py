@@ -111,3 +111,22 @@ def test_long_context_config_sampled_rows():
         od, ld = ao.decode_c(np32(q[:, :, t]), np32(k[:, :, :t + 1]), np32(v[:, :, :t + 1]))
         assert_close(f"O[{t}]", o[:, :, t], od)
         assert_close(f"LSE[{t}]", lse[:, :, t], ld, max_abs=TOL_LSE, rel_l2=1.0)
+
+
+def test_head_dim_128_with_several_items_per_cta():
+    # B=4, T=2048, Hq=8, Hkv=2, D=128: 512 forward items on 296 persistent CTAs (single Q buffer, two S buffers),
+    # 128-key-tile dQ pass, persistent dK/dV pass with one K/V buffer.  Full problem on the GPU, the oracle on two
+    # (batch, KV head) units.
+    B, T, Hq, Hkv, D = 4, 2048, 8, 2, 128
+    q, k, v, do = _case(B, T, Hq, Hkv, D, seed=128)
+    got = run_fwd_bwd(q, k, v, do)
+    g = Hq // Hkv
+    for b, hk in ((0, 1), (3, 0)):
+        hs = slice(hk * g, hk * g + g)
+        want = ao.attn_fwd_bwd_c(np32(q[b:b + 1, hs]), np32(k[b:b + 1, hk:hk + 1]), np32(v[b:b + 1, hk:hk + 1]),
+                                 np32(do[b:b + 1, hs]))
+        assert_close("O", got[0][b:b + 1, hs], want[0])
+        assert_close("LSE", got[1][b:b + 1, hs], want[1], max_abs=TOL_LSE, rel_l2=1.0)
+        assert_close("dQ", got[2][b:b + 1, hs], want[2])
+        assert_close("dK", got[3][b:b + 1, hk:hk + 1], want[3])
+        assert_close("dV", got[4][b:b + 1, hk:hk + 1], want[4])

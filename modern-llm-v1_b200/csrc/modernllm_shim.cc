@@ -103,5 +103,59 @@ void flash_attn_decode(const Tensor& q, const Tensor& kcache, const Tensor& vcac
     raise(b200attn_last_device_status(nullptr), fn);
 }
 
+namespace {
+int x_dtype_of(const Tensor& x, const char* fn) {
+    if (x.dtype() == DType::BF16) return B200ATTN_DTYPE_BF16;
+    if (x.dtype() == DType::FP32) return B200ATTN_DTYPE_F32;
+    throw std::invalid_argument(std::string(fn) + ": x must be FP32 or BF16");
+}
+}  // namespace
+
+void rope_qknorm_forward(const Tensor& x, const Tensor& cos, const Tensor& sin, const Tensor& gamma, float eps, Tensor& y,
+                         Tensor& rstd, int B, int T, int H, int d_h, Layout x_layout, Layout y_layout) {
+    const char* fn = "rope_qknorm_forward";
+    const int xd = x_dtype_of(x, fn);
+    check(y, DType::BF16, fn, "y"); check(cos, DType::FP32, fn, "cos"); check(sin, DType::FP32, fn, "sin");
+    check(gamma, DType::FP32, fn, "gamma"); check(rstd, DType::FP32, fn, "rstd");
+    check_cuda(x, fn, "x"); check_cuda(y, fn, "y"); check_cuda(cos, fn, "cos"); check_cuda(sin, fn, "sin");
+    check_cuda(gamma, fn, "gamma"); check_cuda(rstd, fn, "rstd");
+    if (d_h % 2 != 0) throw std::invalid_argument("rope: d_h must be even");
+    if (x.numel() != 1LL * B * T * H * d_h || y.numel() != x.numel()) throw std::invalid_argument("rope: x numel mismatch");
+    if (gamma.numel() != d_h || rstd.numel() != 1LL * B * H * T || cos.numel() < 1LL * T * (d_h / 2) ||
+        sin.numel() < 1LL * T * (d_h / 2))
+        throw std::invalid_argument("rope_qknorm_forward: shape mismatch (gamma/rstd/cos/sin)");
+    raise(b200attn_rope_norm_fwd(x.data(), xd, static_cast<int>(x_layout), y.data(), static_cast<int>(y_layout),
+                                 static_cast<float*>(rstd.data()), static_cast<const float*>(gamma.data()),
+                                 static_cast<const float*>(cos.data()), static_cast<const float*>(sin.data()), B, T, H, d_h,
+                                 eps, nullptr),
+          fn);
+}
+
+void rope_qknorm_backward(const Tensor& d_y, const Tensor& x, const Tensor& cos, const Tensor& sin, const Tensor& gamma,
+                          const Tensor& rstd, Tensor& d_x, Tensor& d_gamma, int B, int T, int H, int d_h, Layout x_layout,
+                          Layout y_layout) {
+    const char* fn = "rope_qknorm_backward";
+    const int xd = x_dtype_of(x, fn);
+    check(d_y, DType::BF16, fn, "d_y"); check(d_x, x.dtype(), fn, "d_x"); check(cos, DType::FP32, fn, "cos");
+    check(sin, DType::FP32, fn, "sin"); check(gamma, DType::FP32, fn, "gamma"); check(rstd, DType::FP32, fn, "rstd");
+    check(d_gamma, DType::FP32, fn, "d_gamma");
+    check_cuda(d_y, fn, "d_y"); check_cuda(x, fn, "x"); check_cuda(d_x, fn, "d_x"); check_cuda(cos, fn, "cos");
+    check_cuda(sin, fn, "sin"); check_cuda(gamma, fn, "gamma"); check_cuda(rstd, fn, "rstd"); check_cuda(d_gamma, fn, "d_gamma");
+    if (d_h % 2 != 0) throw std::invalid_argument("rope: d_h must be even");
+    if (x.numel() != 1LL * B * T * H * d_h || d_y.numel() != x.numel() || d_x.numel() != x.numel())
+        throw std::invalid_argument("rope: x numel mismatch");
+    if (gamma.numel() != d_h || d_gamma.numel() != d_h || rstd.numel() != 1LL * B * H * T)
+        throw std::invalid_argument("rope_qknorm_backward: shape mismatch (gamma/d_gamma/rstd)");
+    const long long ws_bytes = static_cast<long long>(b200attn_rope_norm_bwd_workspace_bytes(d_h));
+    Tensor ws({(ws_bytes + 3) / 4}, DType::FP32, Device::Cuda);  // private temporary, like the reference's Dh
+    raise(b200attn_rope_norm_bwd(d_y.data(), static_cast<int>(y_layout), x.data(), xd, static_cast<int>(x_layout),
+                                 static_cast<const float*>(rstd.data()), static_cast<const float*>(gamma.data()),
+                                 static_cast<const float*>(cos.data()), static_cast<const float*>(sin.data()), d_x.data(),
+                                 static_cast<float*>(d_gamma.data()), B, T, H, d_h, ws.data(), static_cast<size_t>(ws_bytes),
+                                 nullptr),
+          fn);
+    raise(b200attn_last_device_status(nullptr), fn);  // the workspace is freed on return: the kernels must be done
+}
+
 }  // namespace b200
 }  // namespace modernllm

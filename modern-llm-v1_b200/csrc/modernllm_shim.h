@@ -39,5 +39,18 @@ void flash_attn_backward_gqa(const Tensor& q, const Tensor& k, const Tensor& v, 
 void flash_attn_decode(const Tensor& q, const Tensor& kcache, const Tensor& vcache, Tensor& o, int B, int Lcache,
                        int Hq, int Hkv, int D);
 
+// Fused RoPE + QK-Norm in front of attention and its backward: one call instead of split_heads ->
+// rope_apply_inplace -> rmsnorm_forward (llm/src/model/modern_gpt.cu:351-370) and of rmsnorm_backward ->
+// rope_apply_backward_inplace -> merge_heads (llm/src/model/modern_gpt.cu:527-552).  x: FP32 or BF16 rows of d_h
+// elements in x_layout (BTHD = the projection output [B, T, H*d_h] where it lies); y / d_y: BF16 in y_layout;
+// cos, sin: the tables of make_rope_cache; rstd [B*H, T] FP32; d_gamma is accumulated into (rmsnorm.h:17).
+void rope_qknorm_forward(const Tensor& x, const Tensor& cos, const Tensor& sin, const Tensor& gamma, float eps, Tensor& y,
+                         Tensor& rstd, int B, int T, int H, int d_h, Layout x_layout = Layout::BTHD,
+                         Layout y_layout = Layout::BHTD);
+
+void rope_qknorm_backward(const Tensor& d_y, const Tensor& x, const Tensor& cos, const Tensor& sin, const Tensor& gamma,
+                          const Tensor& rstd, Tensor& d_x, Tensor& d_gamma, int B, int T, int H, int d_h,
+                          Layout x_layout = Layout::BTHD, Layout y_layout = Layout::BHTD);
+
 }  // namespace b200
 }  // namespace modernllm

@@ -51,6 +51,7 @@ struct BwdParams {
     long long k_st, k_sh, k_sb;  // element strides of the k layout: token, head, batch
     int* sched;   // two words of the device-wide item counter of the persistent dQ pass (see ptx.cuh), or nullptr
     int* sched2;  // the same for the dK/dV pass
+    FastDiv div_bhq, div_hq, div_bhkv, div_hkv, div_group;  // division by B * Hq, Hq, B * Hkv, Hkv and the group size
 };
 
 template <int D>
@@ -201,9 +202,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int n_bh = p.B * p.Hq;
     const int n_items = p.n_tiles * n_bh;
     // item id -> (query tile, head, batch); ids are ordered by work, heaviest query tile first
-    auto item_qt = [&](int id) { return p.n_tiles - 1 - id / n_bh; };
-    auto item_h = [&](int id) { return (id % n_bh) % p.Hq; };
-    auto item_b = [&](int id) { return (id % n_bh) / p.Hq; };
+    auto item_rest = [&](int id) { return id - int(fastdiv(unsigned(id), p.div_bhq)) * n_bh; };  // b * Hq + h
+    auto item_qt = [&](int id) { return p.n_tiles - 1 - int(fastdiv(unsigned(id), p.div_bhq)); };
+    auto item_b = [&](int id) { return int(fastdiv(unsigned(item_rest(id)), p.div_hq)); };
+    auto item_h = [&](int id) { return item_rest(id) - item_b(id) * p.Hq; };
     auto item_nkv = [&](int id) { return (min(p.T, item_qt(id) * 128 + 128) + Cfg::kKeys - 1) / Cfg::kKeys; };
     auto get_item = [&](int n) { return item_get(bar_item, item_ring, n, abort_flag, p.status); };
 
@@ -258,7 +260,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         __syncwarp();
         for (int n = 0; ok; ++n) {
-            const int qt = item_qt(id), h = item_h(id), b = item_b(id), hk = h / p.group, n_kv = item_nkv(id);
+            const int qt = item_qt(id), h = item_h(id), b = item_b(id), hk = int(fastdiv(unsigned(h), p.div_group)), n_kv = item_nkv(id);
             // the next item is taken and announced shortly before this item's loads end, but not before the
             // ring has been filled for this item
             const int j_next = max(min(n_kv, NST) - 1, n_kv - 2);
@@ -885,9 +887,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     // item id -> (key tile, KV head, batch); ids are ordered by work: key tile 0 has the most query tiles below it
     const int n_bh = p.B * p.Hkv;
     const int n_items = p.n_tiles * n_bh;
-    auto item_kt = [&](int id) { return id / n_bh; };
-    auto item_hk = [&](int id) { return (id % n_bh) % p.Hkv; };
-    auto item_b = [&](int id) { return (id % n_bh) / p.Hkv; };
+    auto item_kt = [&](int id) { return int(fastdiv(unsigned(id), p.div_bhkv)); };
+    auto item_rest = [&](int id) { return id - item_kt(id) * n_bh; };  // b * Hkv + hk
+    auto item_b = [&](int id) { return int(fastdiv(unsigned(item_rest(id)), p.div_hkv)); };
+    auto item_hk = [&](int id) { return item_rest(id) - item_b(id) * p.Hkv; };
     auto item_units = [&](int id) { return p.group * (p.n_tiles - item_kt(id)); };
     auto get_item = [&](int n) { return item_get(bar_item, item_ring, n, abort_flag, p.status); };
 
@@ -964,10 +967,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             // ring has been filled for this item
             const int j_next = max(min(n_it, NST) - 1, n_it - 2);
             int id_new = n_items;
-            for (int it = 0; it < n_it; ++it, ++u) {
+            for (int it = 0, h = hk * p.group, i = kt; it < n_it; ++it, ++u, i = (i + 1 == p.n_tiles ? kt : i + 1), h += (i == kt)) {
                 const int s = u % NST;
-                const int h = hk * p.group + it / n_i;
-                const int i = kt + it % n_i;
                 if (u >= NST) ok = mbar_wait_warp(&bar_free[s], uint32_t(u / NST - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
                 if (!ok) break;
                 if (elect_one()) {

@@ -38,6 +38,7 @@ struct FwdParams {
     long long o_st, o_sh, o_sb;  // element strides of o: token, head, batch
     int* status;       // device status word
     int* sched;        // two words of the device-wide item counter (see ptx.cuh)
+    FastDiv div_bh, div_h, div_group;  // division by B * Hq, by Hq and by the group size
 };
 
 template <int D>
@@ -101,9 +102,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int n_bh = p.B * p.Hq;
     const int n_items = p.n_qtiles * n_bh;
     auto get_item = [&](int n) { return item_get(bar_item, item_ring, n, abort_flag, p.status); };
-    auto item_qt = [&](int id) { return p.n_qtiles - 1 - id / n_bh; };
-    auto item_h = [&](int id) { return (id % n_bh) % p.Hq; };
-    auto item_b = [&](int id) { return (id % n_bh) / p.Hq; };
+    auto item_rest = [&](int id) { return id - int(fastdiv(unsigned(id), p.div_bh)) * n_bh; };  // b * Hq + h
+    auto item_qt = [&](int id) { return p.n_qtiles - 1 - int(fastdiv(unsigned(id), p.div_bh)); };
+    auto item_b = [&](int id) { return int(fastdiv(unsigned(item_rest(id)), p.div_h)); };
+    auto item_h = [&](int id) { return item_rest(id) - item_b(id) * p.Hq; };
     auto item_nkv = [&](int id) { return (min(p.T, item_qt(id) * 128 + 128) + Cfg::kKeys - 1) / Cfg::kKeys; };
 
     B200ATTN_TRACE_BEGIN(0);
@@ -178,7 +180,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         __syncwarp();
         load_q(0, id);
         for (int n = 0; ok; ++n) {
-            const int h = item_h(id), b = item_b(id), hk = h / p.group, n_kv = item_nkv(id);
+            const int h = item_h(id), b = item_b(id), hk = int(fastdiv(unsigned(h), p.div_group)), n_kv = item_nkv(id);
             // The next item is taken, announced and its Q requested a few tiles before this item's loads end
             // (late, so that a CTA commits itself to little work ahead, but not before the ring has been
             // filled for this item); with one Q buffer, after this item's last tile (it is free only then).

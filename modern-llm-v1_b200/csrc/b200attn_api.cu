@@ -165,6 +165,9 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
     const unsigned grid = (unsigned)std::min<long long>(items, 2LL * sm_count());
     FwdParams pl = p;
     pl.sched = next_sched_pair(items, grid);
+    pl.div_bh = fastdiv_make((unsigned)(p.B * p.Hq));
+    pl.div_h = fastdiv_make((unsigned)p.Hq);
+    pl.div_group = fastdiv_make((unsigned)p.group);
     if (launch_pdl(attn_fwd_kernel<D>, grid, 256, Cfg::kSmemBytes, st, tq, tk, tv, pl) != cudaSuccess) {
         cudaGetLastError();
         return B200ATTN_ERR_CUDA;
@@ -343,8 +346,8 @@ void rope_norm_fill(RopeNormParams& p, int B, int T, int H, int D, int x_layout,
     p.H = H;
     p.x_st = sx.t, p.x_sh = sx.h, p.x_sb = sx.b;
     p.y_st = sy.t, p.y_sh = sy.h, p.y_sb = sy.b;
-    const RnFastDiv dh = rn_fastdiv_make((unsigned)H), dt = rn_fastdiv_make((unsigned)T);
-    p.div_h_mul = dh.mul, p.div_h_shr = dh.shr, p.div_t_mul = dt.mul, p.div_t_shr = dt.shr;
+    p.div_h = fastdiv_make((unsigned)H);
+    p.div_t = fastdiv_make((unsigned)T);
 }
 
 struct RopeNormTensor {  // what differs between q and k
@@ -540,6 +543,11 @@ extern "C" int b200attn_bwd(const void* q, const void* k, const void* v, const v
     p.status = status;
     p.sched = nullptr;
     p.sched2 = nullptr;
+    p.div_bhq = fastdiv_make((unsigned)(B * Hq));
+    p.div_hq = fastdiv_make((unsigned)Hq);
+    p.div_bhkv = fastdiv_make((unsigned)(B * Hkv));
+    p.div_hkv = fastdiv_make((unsigned)Hkv);
+    p.div_group = fastdiv_make((unsigned)p.group);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return D == 64 ? launch_bwd<64>(tq, tk64, tv64, tk, tv, tdo, to, tdq, tdk, tdv, p, st)
                    : launch_bwd<128>(tq, tk64, tv64, tk, tv, tdo, to, tdq, tdk, tdv, p, st);

@@ -220,6 +220,29 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, v
 }
 
 // ---------------------------------------------------------------------------
+// Division of n < 2^31 by a divisor fixed per launch, through one multiply-high and one shift (the round-up
+// method of Granlund and Montgomery: mul = ceil(2^(31 + ceil(log2 d)) / d), shr = ceil(log2 d) - 1).  The
+// kernels turn item and row numbers into (tile, head, batch) with it; a hardware division by a run-time
+// value costs some twenty dependent instructions and sat in front of every item's first load.
+// ---------------------------------------------------------------------------
+struct FastDiv {
+    unsigned d, mul, shr;
+};
+inline FastDiv fastdiv_make(unsigned d) {
+    FastDiv f = {d, 0u, 0u};
+    if (d <= 1) return f;
+    unsigned lg = 0;
+    while ((1u << lg) < d) ++lg;
+    const unsigned p = 31 + lg;
+    f.mul = static_cast<unsigned>(((1ull << p) + d - 1) / d);
+    f.shr = p - 32;
+    return f;
+}
+__device__ __forceinline__ unsigned fastdiv(unsigned n, const FastDiv& f) {
+    return f.d == 1 ? n : (__umulhi(n, f.mul) >> f.shr);
+}
+
+// ---------------------------------------------------------------------------
 // Work distribution of the persistent kernels.  Items are numbered by decreasing cost.  A CTA
 // starts with item blockIdx.x; every further item comes from a device-wide counter (sched[0]), so
 // that whichever CTA is free takes the most expensive item left.  The producer warp of a CTA

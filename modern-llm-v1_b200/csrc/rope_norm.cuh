@@ -24,6 +24,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "ptx.cuh"
+
 namespace b200attn {
 
 struct RopeNormParams {
@@ -37,7 +39,7 @@ struct RopeNormParams {
     float* partial;      // backward: [gridDim.x, D] partial d_gamma sums
     float* d_gamma;      // backward: [D], accumulated into by rope_norm_dgamma_kernel
     int B, T, H;
-    unsigned div_h_mul, div_h_shr, div_t_mul, div_t_shr;  // division by H and by T as multiply + shift (rn_fastdiv)
+    FastDiv div_h, div_t;  // division by H and by T as multiply + shift
     int walk_bthd;       // rows are walked in [B, T, H] order (else [B, H, T]): the order of the tensor that is WRITTEN
                          // (y in the forward, d_x in the backward), so that all stores are dense
     long long x_st, x_sh, x_sb;  // element strides of x (and of d_x): token, head, batch
@@ -69,37 +71,17 @@ __device__ __forceinline__ float rn_row_sum(float v) {
     return v;
 }
 
-// Division of n < 2^31 by a fixed d through one multiply-high and one shift (the round-up method of Granlund and
-// Montgomery: mul = ceil(2^(31 + ceil(log2 d)) / d), shr = ceil(log2 d) - 1).  A hardware division costs about
-// as many instructions as the rest of a row's work.
-struct RnFastDiv {
-    unsigned mul, shr;
-};
-inline RnFastDiv rn_fastdiv_make(unsigned d) {
-    RnFastDiv f = {0u, 0u};
-    if (d <= 1) return f;
-    unsigned lg = 0;
-    while ((1u << lg) < d) ++lg;
-    const unsigned p = 31 + lg;
-    f.mul = static_cast<unsigned>(((1ull << p) + d - 1) / d);
-    f.shr = p - 32;
-    return f;
-}
-__device__ __forceinline__ unsigned rn_fastdiv(unsigned n, unsigned d, unsigned mul, unsigned shr) {
-    return d == 1 ? n : (__umulhi(n, mul) >> shr);
-}
-
 // Row r of the walk -> (batch, token, head)
 __device__ __forceinline__ void rn_decode_row(const RopeNormParams& p, unsigned r, int& b, int& t, int& h) {
     if (p.walk_bthd) {
-        const unsigned bt = rn_fastdiv(r, unsigned(p.H), p.div_h_mul, p.div_h_shr);
+        const unsigned bt = fastdiv(r, p.div_h);
         h = int(r - bt * unsigned(p.H));
-        b = int(rn_fastdiv(bt, unsigned(p.T), p.div_t_mul, p.div_t_shr));
+        b = int(fastdiv(bt, p.div_t));
         t = int(bt - unsigned(b) * unsigned(p.T));
     } else {
-        const unsigned bh = rn_fastdiv(r, unsigned(p.T), p.div_t_mul, p.div_t_shr);
+        const unsigned bh = fastdiv(r, p.div_t);
         t = int(r - bh * unsigned(p.T));
-        b = int(rn_fastdiv(bh, unsigned(p.H), p.div_h_mul, p.div_h_shr));
+        b = int(fastdiv(bh, p.div_h));
         h = int(bh - unsigned(b) * unsigned(p.H));
     }
 }

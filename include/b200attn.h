@@ -121,7 +121,42 @@ size_t b200attn_decode_workspace_bytes(int B, int L, int Hq, int Hkv, int D, int
 /* The split count b200attn_decode uses for n_splits <= 0. */
 int b200attn_decode_default_splits(int B, int L, int Hq, int Hkv, int D);
 
+/* Element type of a projection output handed to the RoPE / QK-Norm / KV-cache calls. */
 enum { B200ATTN_DTYPE_BF16 = 0, B200ATTN_DTYPE_F32 = 1 };
+
+/*
+ * KV cache for inference.  The reference's sampler keeps no cache: it re-runs the whole
+ * forward per generated token (llm/apps/infer_modern_gpt.cu:13,253-255; TODO.md "KV cache
+ * for inference").  These three calls are what a cached ModernGPT block needs around
+ * attention.  Caches are [B, Hkv, L_cap, D] contiguous BF16; the B sequences advance in
+ * lock step (one length for all).
+ *
+ * b200attn_kv_append: for the n_new newest tokens at positions pos0 .. pos0 + n_new - 1, does
+ * what the block does before attention (llm/src/model/modern_gpt.cu:351-370: split_heads,
+ * rope_apply_inplace, rmsnorm_forward on q and k), with RoPE at the TRUE positions, in one
+ * launch: xq [B, n_new, Hq, D] -> q_out [B, Hq, n_new, D] BF16; xk, xv [B, n_new, Hkv, D] ->
+ * rows pos0 .. of kcache (rotated, normalised, times gamma_k) and vcache (converted).  x_dtype:
+ * B200ATTN_DTYPE_BF16 or _F32.  cos_t, sin_t: [>= pos0 + n_new, D / 2] FP32 (b200attn_rope_table).
+ * A row gets the same bits as from b200attn_rope_norm_fwd at the same position.
+ * pos0 + n_new > L_cap is B200ATTN_ERR_INVALID_ARG.
+ *
+ * b200attn_fwd_kvcache: b200attn_fwd over the first T positions with K and V read from the
+ * caches where they lie (prefill: append n_new = T at pos0 = 0, then this).  q, o: [.., T, ..]
+ * in q_layout.
+ *
+ * b200attn_decode_cached: b200attn_decode against the first L rows of caches of capacity L_cap
+ * (b200attn_decode is the case L_cap == L).  Workspace as for b200attn_decode.
+ */
+int b200attn_kv_append(const void* xq, const void* xk, const void* xv, int x_dtype, void* q_out, void* kcache,
+                       void* vcache, const float* gamma_q, const float* gamma_k, const float* cos_t,
+                       const float* sin_t, int B, int n_new, int pos0, int L_cap, int Hq, int Hkv, int D, float eps,
+                       void* stream);
+int b200attn_fwd_kvcache(const void* q, const void* kcache, const void* vcache, void* o, float* lse, int B, int T,
+                         int L_cap, int Hq, int Hkv, int D, int q_layout, float softmax_scale, void* stream);
+int b200attn_decode_cached(const void* q, const void* kcache, const void* vcache, void* o, float* lse, int B, int L,
+                           int L_cap, int Hq, int Hkv, int D, float softmax_scale, int n_splits, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
 
 /*
  * Fused RoPE + per-head RMSNorm ("QK-Norm") that prepares q or k for b200attn_fwd, and its backward.

@@ -16,6 +16,7 @@ from .flash_attn import (  # noqa: F401
     flash_attn_forward,
     flash_attn_forward_gqa,
 )
+from .kv_cache import KVCache  # noqa: F401
 from .rope_norm import (  # noqa: F401
     make_rope_cache,
     rope_qknorm_backward,
@@ -31,6 +32,7 @@ __all__ = [
     "flash_attn_backward_gqa",
     "flash_attn_decode",
     "device_status",
+    "KVCache",
     "make_rope_cache",
     "rope_qknorm_forward",
     "rope_qknorm_backward",

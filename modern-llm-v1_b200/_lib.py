@@ -41,6 +41,9 @@ SYMBOLS = (
     "b200attn_decode",
     "b200attn_decode_workspace_bytes",
     "b200attn_decode_default_splits",
+    "b200attn_decode_cached",
+    "b200attn_fwd_kvcache",
+    "b200attn_kv_append",
     "b200attn_rope_table",
     "b200attn_rope_norm_fwd",
     "b200attn_rope_norm_bwd",
@@ -82,6 +85,12 @@ def load() -> ctypes.CDLL:
     L.b200attn_decode_workspace_bytes.restype = sz
     L.b200attn_decode_default_splits.argtypes = [i, i, i, i, i]
     L.b200attn_decode_default_splits.restype = i
+    L.b200attn_decode_cached.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, f, i, vp, sz, vp]
+    L.b200attn_decode_cached.restype = i
+    L.b200attn_fwd_kvcache.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, i, f, vp]
+    L.b200attn_fwd_kvcache.restype = i
+    L.b200attn_kv_append.argtypes = [vp, vp, vp, i, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, f, vp]
+    L.b200attn_kv_append.restype = i
     L.b200attn_rope_table.argtypes = [i, i, f, vp, vp]
     L.b200attn_rope_table.restype = i
     L.b200attn_rope_norm_fwd.argtypes = [vp, i, i, vp, i, vp, vp, vp, vp, i, i, i, i, f, vp]

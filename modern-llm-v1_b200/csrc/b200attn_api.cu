@@ -13,6 +13,7 @@
 #include "attn_bwd.cuh"
 #include "attn_decode.cuh"
 #include "attn_fwd.cuh"
+#include "kv_cache.cuh"
 #include "rope_norm.cuh"
 #include "tmap.h"
 
@@ -177,15 +178,19 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
 
 }  // namespace
 
-extern "C" int b200attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T, int Hq,
-                            int Hkv, int D, int layout, float softmax_scale, void* stream) {
+namespace {
+
+// The forward with K and V at their own strides (sk): the training call passes the strides of `layout`, the
+// prefill over a KV cache those of the cache.
+int fwd_run(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T, int Hq, int Hkv, int D,
+            int layout, const Strides& sk, float softmax_scale, void* stream) {
     int rc = check_common(B, T, Hq, Hkv, D, layout);
     if (rc) return rc;
     if (!q || !k || !v || !o || !lse) return B200ATTN_ERR_INVALID_ARG;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return B200ATTN_ERR_ALIGNMENT;
     int* status = status_ptr(&rc);
     if (!status) return rc;
-    const Strides sq = strides_for(layout, Hq, T, D), sk = strides_for(layout, Hkv, T, D);
+    const Strides sq = strides_for(layout, Hq, T, D);
     CUtensorMap tq, tk, tv;
     if (!make_tmap_bf16_4d(&tq, q, D, T, Hq, B, sq.t, sq.h, sq.b, 128) ||
         !make_tmap_bf16_4d(&tk, k, D, T, Hkv, B, sk.t, sk.h, sk.b, 64) ||
@@ -209,6 +214,22 @@ extern "C" int b200attn_fwd(const void* q, const void* k, const void* v, void* o
     p.sched = nullptr;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return D == 64 ? launch_fwd<64>(tq, tk, tv, p, st) : launch_fwd<128>(tq, tk, tv, p, st);
+}
+
+}  // namespace
+
+extern "C" int b200attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T, int Hq,
+                            int Hkv, int D, int layout, float softmax_scale, void* stream) {
+    if (T <= 0 || Hkv <= 0 || D <= 0) return B200ATTN_ERR_INVALID_ARG;
+    return fwd_run(q, k, v, o, lse, B, T, Hq, Hkv, D, layout, strides_for(layout, Hkv, T, D), softmax_scale, stream);
+}
+
+extern "C" int b200attn_fwd_kvcache(const void* q, const void* kcache, const void* vcache, void* o, float* lse, int B,
+                                    int T, int L_cap, int Hq, int Hkv, int D, int q_layout, float softmax_scale,
+                                    void* stream) {
+    if (T <= 0 || Hkv <= 0 || D <= 0 || L_cap < T) return B200ATTN_ERR_INVALID_ARG;
+    return fwd_run(q, kcache, vcache, o, lse, B, T, Hq, Hkv, D, q_layout, strides_for(B200ATTN_LAYOUT_BHTD, Hkv, L_cap, D),
+                   softmax_scale, stream);
 }
 
 namespace {
@@ -652,8 +673,16 @@ extern "C" size_t b200attn_decode_workspace_bytes(int B, int L, int Hq, int Hkv,
 extern "C" int b200attn_decode(const void* q, const void* kcache, const void* vcache, void* o, float* lse, int B, int L,
                                int Hq, int Hkv, int D, float softmax_scale, int n_splits, void* workspace,
                                size_t workspace_bytes, void* stream) {
+    return b200attn_decode_cached(q, kcache, vcache, o, lse, B, L, L, Hq, Hkv, D, softmax_scale, n_splits, workspace,
+                                  workspace_bytes, stream);
+}
+
+extern "C" int b200attn_decode_cached(const void* q, const void* kcache, const void* vcache, void* o, float* lse, int B,
+                                      int L, int L_cap, int Hq, int Hkv, int D, float softmax_scale, int n_splits,
+                                      void* workspace, size_t workspace_bytes, void* stream) {
     int rc = check_common(B, L, Hq, Hkv, D, B200ATTN_LAYOUT_BHTD);
     if (rc) return rc;
+    if (L_cap < L) return B200ATTN_ERR_INVALID_ARG;
     if (!q || !kcache || !vcache || !o) return B200ATTN_ERR_INVALID_ARG;
     if (!aligned16(q) || !aligned16(kcache) || !aligned16(vcache) || !aligned16(o)) return B200ATTN_ERR_ALIGNMENT;
     if (!workspace || workspace_bytes < b200attn_decode_workspace_bytes(B, L, Hq, Hkv, D, n_splits) ||
@@ -661,7 +690,8 @@ extern "C" int b200attn_decode(const void* q, const void* kcache, const void* vc
         return B200ATTN_ERR_WORKSPACE;
     int* status = status_ptr(&rc);
     if (!status) return rc;
-    const Strides sk = strides_for(B200ATTN_LAYOUT_BHTD, Hkv, L, D);
+    // the maps end at row L of every (batch, head): rows of the cache beyond it are never read (TMA fills zeros)
+    const Strides sk = strides_for(B200ATTN_LAYOUT_BHTD, Hkv, L_cap, D);
     CUtensorMap tk, tv;
     if (!make_tmap_bf16_4d(&tk, kcache, D, L, Hkv, B, sk.t, sk.h, sk.b, 128) ||
         !make_tmap_bf16_4d(&tv, vcache, D, L, Hkv, B, sk.t, sk.h, sk.b, 128))
@@ -697,6 +727,65 @@ extern "C" int b200attn_decode(const void* q, const void* kcache, const void* vc
                                                                static_cast<uint16_t*>(o), lse, (int)rows, p.n_splits,
                                                                p.scale, p.scale_log2);
     return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
+}
+
+namespace {
+
+template <int D, bool F32>
+int launch_kv_append(const KvAppendParams& p, cudaStream_t st) {
+    const long long rows = (long long)p.rows_q + 2LL * p.rows_kv;
+    const long long rows_per_cta = (kKvAppendThreads / 32) * (256 / D);
+    long long grid = (rows + rows_per_cta - 1) / rows_per_cta;
+    const long long cap = 8LL * sm_count();  // 8 CTAs of 256 threads are resident per SM
+    if (grid > cap) grid = cap;
+    kv_append_kernel<D, F32><<<(unsigned)grid, kKvAppendThreads, 0, st>>>(p);
+    return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
+}
+
+}  // namespace
+
+extern "C" int b200attn_kv_append(const void* xq, const void* xk, const void* xv, int x_dtype, void* q_out, void* kcache,
+                                  void* vcache, const float* gamma_q, const float* gamma_k, const float* cos_t,
+                                  const float* sin_t, int B, int n_new, int pos0, int L_cap, int Hq, int Hkv, int D,
+                                  float eps, void* stream) {
+    if (B <= 0 || n_new <= 0 || pos0 < 0 || L_cap <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0) return B200ATTN_ERR_INVALID_ARG;
+    if (Hq % Hkv != 0 || (long long)pos0 + n_new > L_cap) return B200ATTN_ERR_INVALID_ARG;
+    if (x_dtype != B200ATTN_DTYPE_BF16 && x_dtype != B200ATTN_DTYPE_F32) return B200ATTN_ERR_INVALID_ARG;
+    if (D != 64 && D != 128) return B200ATTN_ERR_UNSUPPORTED;
+    if (!xq || !xk || !xv || !q_out || !kcache || !vcache || !gamma_q || !gamma_k || !cos_t || !sin_t)
+        return B200ATTN_ERR_INVALID_ARG;
+    if (!aligned16(xq) || !aligned16(xk) || !aligned16(xv) || !aligned16(q_out) || !aligned16(kcache) ||
+        !aligned16(vcache) || !aligned16(gamma_q) || !aligned16(gamma_k) || !aligned16(cos_t) || !aligned16(sin_t))
+        return B200ATTN_ERR_ALIGNMENT;
+    const long long rows_q = (long long)B * n_new * Hq, rows_kv = (long long)B * n_new * Hkv;
+    if (rows_q + 2 * rows_kv >= (1LL << 31)) return B200ATTN_ERR_TOO_LARGE;
+    KvAppendParams p;
+    p.xq = xq;
+    p.xk = xk;
+    p.xv = xv;
+    p.q_out = static_cast<uint16_t*>(q_out);
+    p.kcache = static_cast<uint16_t*>(kcache);
+    p.vcache = static_cast<uint16_t*>(vcache);
+    p.gamma_q = gamma_q;
+    p.gamma_k = gamma_k;
+    p.cos_t = cos_t;
+    p.sin_t = sin_t;
+    p.B = B;
+    p.n_new = n_new;
+    p.pos0 = pos0;
+    p.L_cap = L_cap;
+    p.Hq = Hq;
+    p.Hkv = Hkv;
+    p.rows_q = (unsigned)rows_q;
+    p.rows_kv = (unsigned)rows_kv;
+    p.div_hq = fastdiv_make((unsigned)Hq);
+    p.div_hkv = fastdiv_make((unsigned)Hkv);
+    p.div_n = fastdiv_make((unsigned)n_new);
+    p.eps = eps;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool f32 = x_dtype == B200ATTN_DTYPE_F32;
+    if (D == 64) return f32 ? launch_kv_append<64, true>(p, st) : launch_kv_append<64, false>(p, st);
+    return f32 ? launch_kv_append<128, true>(p, st) : launch_kv_append<128, false>(p, st);
 }
 
 extern "C" int b200attn_last_device_status(void* stream) {

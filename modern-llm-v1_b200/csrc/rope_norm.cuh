@@ -112,6 +112,30 @@ __device__ __forceinline__ void rn_store8(void* base, long long off, const float
     }
 }
 
+// The forward arithmetic of one row, shared by every kernel that prepares q or k (so that a row gives the same
+// bits whichever kernel computes it).  rn_rotate8: RoPE on a lane's 8 elements (4 pairs; cs, sn = the 4 cosines
+// and sines of the lane's pairs at the row's position) and the lane's share of the row's sum of squares.
+__device__ __forceinline__ float rn_rotate8(const float (&v)[8], const float4& cs, const float4& sn, float (&rot)[8]) {
+    const float c[4] = {cs.x, cs.y, cs.z, cs.w}, s[4] = {sn.x, sn.y, sn.z, sn.w};
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float x0 = v[2 * i], x1 = v[2 * i + 1];
+        rot[2 * i] = x0 * c[i] - x1 * s[i];
+        rot[2 * i + 1] = x0 * s[i] + x1 * c[i];
+        ss += rot[2 * i] * rot[2 * i] + rot[2 * i + 1] * rot[2 * i + 1];
+    }
+    return ss;
+}
+template <int D>
+__device__ __forceinline__ float rn_rstd(float row_sum_sq, float eps) {
+    return rsqrtf(row_sum_sq / float(D) + eps);
+}
+__device__ __forceinline__ void rn_scale8(const float (&rot)[8], float rstd, const float (&gm)[8], float (&out)[8]) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) out[e] = rot[e] * rstd * gm[e];
+}
+
 // One tensor's forward.  (A function of its own, called once per tensor with the kernel parameter itself, so that
 // every field stays a constant-bank operand; selecting the struct at run time would move it to local memory.)
 template <int D, bool F32>
@@ -149,22 +173,12 @@ __device__ __forceinline__ void rope_norm_fwd_tensor(const RopeNormParams& p) {
         for (int k = 0; k < kFwdSteps; ++k) {
             float rot[8];
             float ss = 0.f;
-            if (live[k]) {
-                const float c[4] = {cs[k].x, cs[k].y, cs[k].z, cs[k].w}, s[4] = {sn[k].x, sn[k].y, sn[k].z, sn[k].w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float x0 = v[k][2 * i], x1 = v[k][2 * i + 1];
-                    rot[2 * i] = x0 * c[i] - x1 * s[i];
-                    rot[2 * i + 1] = x0 * s[i] + x1 * c[i];
-                    ss += rot[2 * i] * rot[2 * i] + rot[2 * i + 1] * rot[2 * i + 1];
-                }
-            }
+            if (live[k]) ss = rn_rotate8(v[k], cs[k], sn[k], rot);
             ss = rn_row_sum<LPR>(ss);  // every lane takes part in the shuffles
             if (live[k]) {
-                const float rstd = rsqrtf(ss / float(D) + p.eps);
+                const float rstd = rn_rstd<D>(ss, p.eps);
                 float out[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) out[e] = rot[e] * rstd * gm[e];
+                rn_scale8(rot, rstd, gm, out);
                 rn_store8<false>(p.y, (static_cast<long long>(r0) + k * RPS + sub) * D + li * 8, out);  // y is dense in walk order
                 if (li == 0) p.rstd[(static_cast<long long>(bb[k]) * p.H + hh[k]) * p.T + tt[k]] = rstd;
             }

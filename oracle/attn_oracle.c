@@ -125,8 +125,17 @@ void oracle_rmsnorm_rows(float* x, long long rows, int D, float eps) {
  * rope_apply_inplace -> rmsnorm_forward of llm/src/model/modern_gpt.cu:358-370.
  * Rotation and table: llm/src/model/rope.cu:25-44,112-128; norm: llm/src/model/rmsnorm.cu:24-53
  * (rstd = rsqrt(mean r^2 + eps), y = r rstd gamma).  Sums in double. */
+void oracle_rope_norm_fwd_at(const float* x, const float* gamma, float* y, float* rstd, long long n_outer, int T,
+                             int D, float base, float eps, int pos0);
 void oracle_rope_norm_fwd(const float* x, const float* gamma, float* y, float* rstd, long long n_outer, int T, int D,
                           float base, float eps) {
+    oracle_rope_norm_fwd_at(x, gamma, y, rstd, n_outer, T, D, base, eps, 0);
+}
+/* The same with row (n, t) at position pos0 + t: what a KV cache needs for the newest tokens of a sequence
+ * (the reference's rope_apply_inplace takes the position from the row index, llm/src/model/rope.cu:25-44, and
+ * its sampler has no cache, llm/apps/infer_modern_gpt.cu:13). */
+void oracle_rope_norm_fwd_at(const float* x, const float* gamma, float* y, float* rstd, long long n_outer, int T,
+                             int D, float base, float eps, int pos0) {
     int half = D / 2;
 #pragma omp parallel for schedule(static)
     for (long long n = 0; n < n_outer; ++n) {
@@ -137,7 +146,7 @@ void oracle_rope_norm_fwd(const float* x, const float* gamma, float* y, float* r
             double sq = 0.0;
             for (int i = 0; i < half; ++i) {
                 float theta = powf(base, -(float)(2 * i) / (float)D);
-                float angle = (float)t * theta;
+                float angle = (float)(pos0 + t) * theta;
                 float c = cosf(angle), s = sinf(angle);
                 r[2 * i] = xr[2 * i] * c - xr[2 * i + 1] * s;
                 r[2 * i + 1] = xr[2 * i] * s + xr[2 * i + 1] * c;

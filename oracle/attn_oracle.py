@@ -61,6 +61,7 @@ def lib():
         L.oracle_rope_inplace.argtypes = [fp, ctypes.c_longlong, i, i, ctypes.c_float, i]
         L.oracle_rmsnorm_rows.argtypes = [fp, ctypes.c_longlong, i, ctypes.c_float]
         L.oracle_rope_norm_fwd.argtypes = [fp, fp, fp, fp, ctypes.c_longlong, i, i, ctypes.c_float, ctypes.c_float]
+        L.oracle_rope_norm_fwd_at.argtypes = [fp, fp, fp, fp, ctypes.c_longlong, i, i, ctypes.c_float, ctypes.c_float, i]
         L.oracle_rope_norm_bwd.argtypes = [fp, fp, fp, fp, fp, fp, ctypes.c_longlong, i, i, ctypes.c_float]
         L.oracle_attn_fwd.argtypes = [fp, fp, fp, fp, fp, i, i, i, i, i, ctypes.c_float, sp, sp, sp]
         L.oracle_attn_fwd_bwd.argtypes = [fp] * 9 + [i, i, i, i, i, ctypes.c_float, sp, sp, sp]
@@ -144,6 +145,28 @@ def rope_norm_fwd(x: np.ndarray, gamma: np.ndarray, base: float = 10000.0, eps: 
     rstd = np.empty(x.shape[:-1], dtype=np.float32)
     lib().oracle_rope_norm_fwd(_fp(x), _fp(g), _fp(y), _fp(rstd), x.size // (T * D), T, D, base, eps)
     return y, rstd
+
+
+def kv_append(xq, xk, xv, gamma_q, gamma_k, kcache, vcache, pos0, base: float = 10000.0, eps: float = 1e-5):
+    """What a cached ModernGPT block does to its n_new newest tokens before attention
+    (llm/src/model/modern_gpt.cu:351-370, with RoPE at the true positions pos0 + t): xq [B, n_new, Hq, D],
+    xk / xv [B, n_new, Hkv, D] -> returns q [B, Hq, n_new, D] and writes rows pos0 .. of kcache / vcache
+    [B, Hkv, L_cap, D] (FP32 arrays, updated in place; k rotated and normalised, v as it is)."""
+    n_new = xq.shape[1]
+
+    def prep(x, g):
+        xt = _c32(np.swapaxes(_c32(x), 1, 2))  # [B, H, n_new, D]
+        y = np.empty_like(xt)
+        rstd = np.empty(xt.shape[:-1], dtype=np.float32)
+        D = xt.shape[-1]
+        lib().oracle_rope_norm_fwd_at(_fp(xt), _fp(_c32(g)), _fp(y), _fp(rstd), xt.size // (n_new * D), n_new, D, base,
+                                      eps, int(pos0))
+        return y
+
+    q = prep(xq, gamma_q)
+    kcache[:, :, pos0:pos0 + n_new, :] = prep(xk, gamma_k)
+    vcache[:, :, pos0:pos0 + n_new, :] = np.swapaxes(_c32(xv), 1, 2)
+    return q
 
 
 def rope_norm_bwd(dy: np.ndarray, x: np.ndarray, gamma: np.ndarray, rstd: np.ndarray, base: float = 10000.0):

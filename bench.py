@@ -60,8 +60,10 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c2_50m_train")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--op", default="attention", choices=["attention", "qkprep"],
-                    help="qkprep: the fused RoPE + QK-Norm operator on the config's q and k (HBM GB/s)")
+    ap.add_argument("--op", default="attention", choices=["attention", "qkprep", "decode_step"],
+                    help="qkprep: the fused RoPE + QK-Norm operator on the config's q and k (HBM GB/s); "
+                         "decode_step (with --config c5_decode): one cached sampling step of a layer, KV-cache "
+                         "append + split-KV decode (HBM GB/s)")
     return ap.parse_args()
 
 
@@ -483,6 +485,108 @@ def run_qkprep(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier)
         print(json.dumps(out), flush=True)
 
 
+def run_decode_step(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier):
+    """One cached sampling step of a layer: KVCache.append (split heads + RoPE at the true position + QK-Norm +
+    cache write for the newest token of every sequence) followed by KVCache.attend (split-KV decode over the
+    cache): HBM GB/s.  The cache length is held at the config's (each step rewrites row L-1 and reads L rows);
+    algorithmic bytes per step = K and V cache + the new token's FP32 q, k, v rows in + BF16 q, k, v, o out."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from modern_llm_v1_b200 import inputs
+
+    B, L, Hq, Hkv, D = cfg.B, cfg.T, cfg.Hq, cfg.Hkv, cfg.D
+    _, kc, vc, _, _ = inputs.make_decode_inputs(cfg, 20260005 + 1000 * rank)
+    cache = m.KVCache(1, B, Hq, Hkv, D, L, device=device)
+    cache.k[0].copy_(kc)
+    cache.v[0].copy_(vc)
+    del kc, vc
+    g = torch.Generator().manual_seed(20260007 + 1000 * rank)
+    host = [torch.randn(B, 1, H, D, generator=g).pin_memory() for H in (Hq, Hkv, Hkv)]
+    xq, xk, xv = (t.to(device) for t in host)
+    gamma = torch.ones(D, device=device)
+    q = torch.empty(B, Hq, 1, D, dtype=torch.bfloat16, device=device)
+    o = torch.empty_like(q)
+    o_host = torch.empty(B, Hq, 1, D, dtype=torch.bfloat16).pin_memory()
+
+    def step(e2e=False):
+        cache.length = L - 1
+        if e2e:
+            for d, h in zip((xq, xk, xv), host):
+                d.copy_(h, non_blocking=True)
+        cache.append(0, xq, xk, xv, gamma, gamma, q)
+        cache.attend(0, q, o, None)
+        if e2e:
+            o_host.copy_(o, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+    def timed(n, e2e=False):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(n):
+            step(e2e)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1) / n
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(warmup):
+        step()
+    m.device_status()
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    ms = timed(steps)
+    clocks = sampler.stop()
+    m.device_status()
+    ms_e2e = timed(max(10, steps // 10), e2e=True)
+    m.device_status()
+    rows = B * (Hq + 2 * Hkv)
+    h2d, d2h = rows * D * 4, B * Hq * D * 2
+    nbytes = cfg.decode_bytes() + rows * D * 4 + rows * D * 2
+    gbs = world * nbytes / (ms * 1e-3) / 1e9
+    peak = float(peaks["hbm_gbs"])
+    out = {
+        "metric": "decode_step_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": cfg.name + "_step", "B_per_gpu": B, "cache_len": L, "Hq": Hq, "Hkv": Hkv, "D": D,
+                   "io": "new token's q, k, v FP32 [B,1,H,D] in; caches BF16 [B,Hkv,L,D]; o BF16 out",
+                   "l2": f"cache of {cfg.decode_bytes() / 1e6:.0f} MB > 126 MB L2"},
+        "clocks": clocks, "gpu_launches": 3 * steps,
+        "e2e": {"value": world * nbytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "note": "the new token's rows from pinned host memory, o read back, a stream synchronise per step"},
+        "roofline": {"bound": "hbm", "kernel": "attn_decode_kernel", "achieved": gbs / world, "peak": peak,
+                     "unit": "GB/s", "frac": gbs / world / peak, "traffic": None,
+                     "peak_source": f"hbm_gbs of {peaks['_source']}", "bytes_per_step": nbytes,
+                     "note": "3 launches per step: kv_append_kernel, attn_decode_kernel, attn_decode_combine_kernel"},
+    }
+    if rank == 0 and not args.no_cpu_baseline:
+        from oracle import attn_oracle as ao
+        use_all_host_cores()
+        nb = min(B, 8)
+        kc32, vc32 = cache.k[0, :nb].float().cpu().numpy(), cache.v[0, :nb].float().cpu().numpy()
+        hq, hk, hv = (t[:nb].numpy() for t in host)
+        ones = np.ones(D, np.float32)
+        t0 = time.perf_counter()
+        reps = 0
+        while time.perf_counter() - t0 < 5.0:
+            q32 = ao.kv_append(hq, hk, hv, ones, ones, kc32, vc32, L - 1)
+            ao.decode_c(np.ascontiguousarray(q32[:, :, 0]), kc32, vc32)
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        out["cpu_baseline"] = {"value": nbytes * nb / B / dt / 1e9, "unit": "GB/s (same byte convention)",
+                               "cores": ao.num_threads(), "kind": "port",
+                               "sample": f"{nb} of {B} sequences, {reps} steps, FP32 caches on the host"}
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+
+
 def main():
     args = parse_args()
     import modern_llm_v1_b200 as m
@@ -518,6 +622,14 @@ def main():
     steps = max(1, args.steps)
     if args.op == "qkprep":
         run_qkprep(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+    if args.op == "decode_step":
+        if cfg.kind != "decode":
+            raise SystemExit("--op decode_step needs a decode config (--config c5_decode)")
+        run_decode_step(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier)
         if world > 1:
             dist.barrier()
             dist.destroy_process_group()

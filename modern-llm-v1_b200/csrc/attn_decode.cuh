@@ -104,18 +104,21 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     const int n_all = (p.L + 127) / 128;
     const int n_tiles = max(0, min(p.tiles_per_split, n_all - tile0));
 
-    if (tid == 0) *abort_flag = *reinterpret_cast<volatile int*>(p.status);
-    __syncthreads();
-    if (*abort_flag != 0) return;
-    __syncthreads();
-
     if (tid == 0) {
         for (int s = 0; s < NST; ++s) {
             mbar_init(&bar_full[s], 1);
             mbar_init(&bar_free[s], 128);
         }
         fence_mbar_init();
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
     }
+    // launched with programmatic stream serialization: everything above overlaps the previous kernel's end (the
+    // cache append that wrote q and the newest K / V row); nothing in global memory is touched before this wait
+    grid_dep_wait();
+    if (tid == 0) *abort_flag = *reinterpret_cast<volatile int*>(p.status);
+    __syncthreads();
+    if (*abort_flag != 0) return;
     // q rows of the G heads -> shared memory (BF16, 16-byte chunks, swizzled); rows >= G are zero
     for (int i = tid; i < 16 * (D / 8); i += blockDim.x) {
         const int r = i / (D / 8), c = i % (D / 8);
@@ -127,8 +130,6 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
 
     if (warp == 4) {
         if (lane == 0) {
-            tma_prefetch_desc(&tmK);
-            tma_prefetch_desc(&tmV);
             for (int j = 0; j < n_tiles; ++j) {
                 const int s = j % NST;
                 if (j >= NST &&
@@ -302,6 +303,7 @@ attn_decode_combine_kernel(const float* __restrict__ part_o, const float* __rest
                            int n_rows, int n_splits, float scale, float scale_log2) {
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
+    grid_dep_wait();  // the partials come from the kernel before this one
     if (row >= n_rows) return;
     float m = -INFINITY;
     for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_m[(size_t)row * n_splits + s]);

@@ -131,10 +131,10 @@ int check_common(int B, int T, int Hq, int Hkv, int D, int layout) {
 // Launch with programmatic stream serialization: the kernel may become resident while the
 // previous kernel of the stream drains; it calls griddepcontrol.wait before touching global memory.
 template <typename... KArgs, typename... Args>
-cudaError_t launch_pdl(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t st,
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, unsigned block, size_t smem, cudaStream_t st,
                        Args&&... args) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.gridDim = grid;
     cfg.blockDim = dim3(block, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -652,8 +652,12 @@ int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, const DecodePara
     static bool set[kMaxDevices] = {false};
     int rc = set_smem_once(attn_decode_kernel<D>, Cfg::kSmemBytes, set);
     if (rc) return rc;
-    attn_decode_kernel<D><<<dim3(p.n_splits, p.Hkv * p.n_chunks, p.B), 160, Cfg::kSmemBytes, st>>>(tk, tv, p);
-    return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
+    if (launch_pdl(attn_decode_kernel<D>, dim3(p.n_splits, p.Hkv * p.n_chunks, p.B), 160, Cfg::kSmemBytes, st, tk, tv,
+                   p) != cudaSuccess) {
+        cudaGetLastError();
+        return B200ATTN_ERR_CUDA;
+    }
+    return B200ATTN_OK;
 }
 
 }  // namespace
@@ -718,15 +722,21 @@ extern "C" int b200attn_decode_cached(const void* q, const void* kcache, const v
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     rc = D == 64 ? launch_decode<64>(tk, tv, p, st) : launch_decode<128>(tk, tv, p, st);
     if (rc) return rc;
-    const unsigned blocks = (unsigned)((rows + 3) / 4);
-    if (D == 64)
-        attn_decode_combine_kernel<64><<<blocks, 128, 0, st>>>(p.part_o, p.part_m, p.part_l, static_cast<uint16_t*>(o),
-                                                              lse, (int)rows, p.n_splits, p.scale, p.scale_log2);
-    else
-        attn_decode_combine_kernel<128><<<blocks, 128, 0, st>>>(p.part_o, p.part_m, p.part_l,
-                                                               static_cast<uint16_t*>(o), lse, (int)rows, p.n_splits,
-                                                               p.scale, p.scale_log2);
-    return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
+    const dim3 blocks((unsigned)((rows + 3) / 4), 1, 1);
+    const float* po = p.part_o;
+    const float* pm = p.part_m;
+    const float* pl = p.part_l;
+    uint16_t* o16 = static_cast<uint16_t*>(o);
+    const cudaError_t e =
+        D == 64 ? launch_pdl(attn_decode_combine_kernel<64>, blocks, 128, 0, st, po, pm, pl, o16, lse, (int)rows,
+                             p.n_splits, p.scale, p.scale_log2)
+                : launch_pdl(attn_decode_combine_kernel<128>, blocks, 128, 0, st, po, pm, pl, o16, lse, (int)rows,
+                             p.n_splits, p.scale, p.scale_log2);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return B200ATTN_ERR_CUDA;
+    }
+    return B200ATTN_OK;
 }
 
 namespace {
@@ -738,8 +748,11 @@ int launch_kv_append(const KvAppendParams& p, cudaStream_t st) {
     long long grid = (rows + rows_per_cta - 1) / rows_per_cta;
     const long long cap = 8LL * sm_count();  // 8 CTAs of 256 threads are resident per SM
     if (grid > cap) grid = cap;
-    kv_append_kernel<D, F32><<<(unsigned)grid, kKvAppendThreads, 0, st>>>(p);
-    return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ERR_CUDA;
+    if (launch_pdl(kv_append_kernel<D, F32>, dim3((unsigned)grid, 1, 1), kKvAppendThreads, 0, st, p) != cudaSuccess) {
+        cudaGetLastError();
+        return B200ATTN_ERR_CUDA;
+    }
+    return B200ATTN_OK;
 }
 
 }  // namespace

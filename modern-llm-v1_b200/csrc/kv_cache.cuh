@@ -53,6 +53,7 @@ kv_append_kernel(const __grid_constant__ KvAppendParams p) {
     const unsigned warp0 = (blockIdx.x * kKvAppendThreads + threadIdx.x) >> 5;
     const unsigned n_warps = (gridDim.x * kKvAppendThreads) >> 5;
     const unsigned n_rows = p.rows_q + 2u * p.rows_kv;
+    grid_dep_wait();  // launched with programmatic stream serialization: the inputs come from the kernel before
 
     for (unsigned long long r0 = static_cast<unsigned long long>(warp0) * RPS; r0 < n_rows;
          r0 += static_cast<unsigned long long>(n_warps) * RPS) {

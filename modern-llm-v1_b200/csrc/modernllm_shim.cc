@@ -157,5 +157,64 @@ void rope_qknorm_backward(const Tensor& d_y, const Tensor& x, const Tensor& cos,
     raise(b200attn_last_device_status(nullptr), fn);  // the workspace is freed on return: the kernels must be done
 }
 
+void kv_cache_append(const Tensor& q_proj, const Tensor& k_proj, const Tensor& v_proj, const Tensor& cos, const Tensor& sin,
+                     const Tensor& gamma_q, const Tensor& gamma_k, float eps, Tensor& q_out, Tensor& kcache, Tensor& vcache,
+                     int B, int n_new, int pos0, int L_cap, int Hq, int Hkv, int d_h) {
+    const char* fn = "kv_cache_append";
+    const int xd = x_dtype_of(q_proj, fn);
+    check(k_proj, q_proj.dtype(), fn, "k_proj"); check(v_proj, q_proj.dtype(), fn, "v_proj");
+    check(q_out, DType::BF16, fn, "q_out"); check(kcache, DType::BF16, fn, "kcache"); check(vcache, DType::BF16, fn, "vcache");
+    check(cos, DType::FP32, fn, "cos"); check(sin, DType::FP32, fn, "sin");
+    check(gamma_q, DType::FP32, fn, "gamma_q"); check(gamma_k, DType::FP32, fn, "gamma_k");
+    check_cuda(q_proj, fn, "q_proj"); check_cuda(k_proj, fn, "k_proj"); check_cuda(v_proj, fn, "v_proj");
+    check_cuda(q_out, fn, "q_out"); check_cuda(kcache, fn, "kcache"); check_cuda(vcache, fn, "vcache");
+    check_cuda(cos, fn, "cos"); check_cuda(sin, fn, "sin"); check_cuda(gamma_q, fn, "gamma_q"); check_cuda(gamma_k, fn, "gamma_k");
+    if (q_proj.numel() != 1LL * B * n_new * Hq * d_h || q_out.numel() != q_proj.numel() ||
+        k_proj.numel() != 1LL * B * n_new * Hkv * d_h || v_proj.numel() != k_proj.numel())
+        throw std::invalid_argument("kv_cache_append: shape mismatch (q/k/v)");
+    if (kcache.numel() != 1LL * B * Hkv * L_cap * d_h || vcache.numel() != kcache.numel())
+        throw std::invalid_argument("kv_cache_append: shape mismatch (caches)");
+    if (gamma_q.numel() != d_h || gamma_k.numel() != d_h || cos.numel() < 1LL * (pos0 + n_new) * (d_h / 2) ||
+        sin.numel() < 1LL * (pos0 + n_new) * (d_h / 2))
+        throw std::invalid_argument("kv_cache_append: shape mismatch (gamma/cos/sin)");
+    raise(b200attn_kv_append(q_proj.data(), k_proj.data(), v_proj.data(), xd, q_out.data(), kcache.data(), vcache.data(),
+                             static_cast<const float*>(gamma_q.data()), static_cast<const float*>(gamma_k.data()),
+                             static_cast<const float*>(cos.data()), static_cast<const float*>(sin.data()), B, n_new, pos0,
+                             L_cap, Hq, Hkv, d_h, eps, nullptr),
+          fn);
+}
+
+void flash_attn_decode_cached(const Tensor& q, const Tensor& kcache, const Tensor& vcache, Tensor& o, int B, int L, int L_cap,
+                              int Hq, int Hkv, int D) {
+    const char* fn = "flash_attn_decode_cached";
+    check(q, DType::BF16, fn, "q"); check(kcache, DType::BF16, fn, "kcache"); check(vcache, DType::BF16, fn, "vcache");
+    check(o, DType::BF16, fn, "o");
+    check_cuda(q, fn, "q"); check_cuda(kcache, fn, "kcache"); check_cuda(vcache, fn, "vcache"); check_cuda(o, fn, "o");
+    if (q.numel() != 1LL * B * Hq * D || o.numel() != q.numel() || kcache.numel() != 1LL * B * Hkv * L_cap * D ||
+        vcache.numel() != kcache.numel())
+        throw std::invalid_argument("flash_attn_decode_cached: shape mismatch");
+    const long long ws_bytes = static_cast<long long>(b200attn_decode_workspace_bytes(B, L, Hq, Hkv, D, 0));
+    Tensor ws({(ws_bytes + 3) / 4}, DType::FP32, Device::Cuda);
+    raise(b200attn_decode_cached(q.data(), kcache.data(), vcache.data(), o.data(), nullptr, B, L, L_cap, Hq, Hkv, D, 0.f, 0,
+                                 ws.data(), static_cast<size_t>(ws_bytes), nullptr),
+          fn);
+    raise(b200attn_last_device_status(nullptr), fn);  // the workspace is freed on return
+}
+
+void flash_attn_forward_kvcache(const Tensor& q, const Tensor& kcache, const Tensor& vcache, Tensor& ctx, Tensor& L, int B,
+                                int T, int L_cap, int Hq, int Hkv, int D) {
+    const char* fn = "flash_attn_forward_kvcache";
+    check(q, DType::BF16, fn, "q"); check(kcache, DType::BF16, fn, "kcache"); check(vcache, DType::BF16, fn, "vcache");
+    check(ctx, DType::BF16, fn, "ctx"); check(L, DType::FP32, fn, "L");
+    check_cuda(q, fn, "q"); check_cuda(kcache, fn, "kcache"); check_cuda(vcache, fn, "vcache"); check_cuda(ctx, fn, "ctx");
+    check_cuda(L, fn, "L");
+    if (q.numel() != 1LL * B * Hq * T * D || ctx.numel() != q.numel() || L.numel() != 1LL * B * Hq * T ||
+        kcache.numel() != 1LL * B * Hkv * L_cap * D || vcache.numel() != kcache.numel())
+        throw std::invalid_argument("flash_attn_forward_kvcache: shape mismatch");
+    raise(b200attn_fwd_kvcache(q.data(), kcache.data(), vcache.data(), ctx.data(), static_cast<float*>(L.data()), B, T, L_cap,
+                               Hq, Hkv, D, B200ATTN_LAYOUT_BHTD, 0.f, nullptr),
+          fn);
+}
+
 }  // namespace b200
 }  // namespace modernllm

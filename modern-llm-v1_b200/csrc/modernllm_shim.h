@@ -52,5 +52,20 @@ void rope_qknorm_backward(const Tensor& d_y, const Tensor& x, const Tensor& cos,
                           const Tensor& rstd, Tensor& d_x, Tensor& d_gamma, int B, int T, int H, int d_h,
                           Layout x_layout = Layout::BTHD, Layout y_layout = Layout::BHTD);
 
+// KV cache for the sampler (the reference re-runs the whole forward per token, llm/apps/infer_modern_gpt.cu:13,253-255).
+// kv_cache_append: what a block does to the n_new newest tokens before attention (llm/src/model/modern_gpt.cu:351-370:
+// split_heads, RoPE at positions pos0 .. pos0 + n_new - 1, QK-Norm) in one call: q_proj [B, n_new, Hq*d_h],
+// k_proj / v_proj [B, n_new, Hkv*d_h] (FP32 or BF16) -> q_out [B*Hq, n_new, d_h] BF16 and rows pos0 .. of the caches
+// [B*Hkv, L_cap, d_h] BF16.  cos, sin: make_rope_cache(L_cap, d_h, ...).
+void kv_cache_append(const Tensor& q_proj, const Tensor& k_proj, const Tensor& v_proj, const Tensor& cos, const Tensor& sin,
+                     const Tensor& gamma_q, const Tensor& gamma_k, float eps, Tensor& q_out, Tensor& kcache, Tensor& vcache,
+                     int B, int n_new, int pos0, int L_cap, int Hq, int Hkv, int d_h);
+// One query token per sequence against the first L rows of caches of capacity L_cap; q, o: [B, Hq, d_h].
+void flash_attn_decode_cached(const Tensor& q, const Tensor& kcache, const Tensor& vcache, Tensor& o, int B, int L, int L_cap,
+                              int Hq, int Hkv, int D);
+// Causal attention over a prompt of T tokens with K and V read from the caches (rows 0 .. T-1); q, ctx: [B*Hq, T, D].
+void flash_attn_forward_kvcache(const Tensor& q, const Tensor& kcache, const Tensor& vcache, Tensor& ctx, Tensor& L, int B,
+                                int T, int L_cap, int Hq, int Hkv, int D);
+
 }  // namespace b200
 }  // namespace modernllm

@@ -346,7 +346,7 @@ void rope_norm_launch_fwd(const RopeNormParams& p0, const RopeNormParams& p1, in
                           cudaStream_t st) {
     static int occ[kMaxDevices] = {0};
     const unsigned grid = rope_norm_grid(rope_norm_fwd_kernel<D, F32>, rows, (kRopeNormThreads / 32) * kFwdSteps * (256 / D), occ);
-    rope_norm_fwd_kernel<D, F32><<<grid, kRopeNormThreads, 0, st>>>(p0, p1, n_tensors);
+    launch_pdl(rope_norm_fwd_kernel<D, F32>, dim3(grid, 1, 1), kRopeNormThreads, 0, st, p0, p1, n_tensors);
 }
 template <int D, bool F32>
 void rope_norm_launch_bwd(RopeNormParams p0, RopeNormParams p1, int n_tensors, long long rows, float* workspace,
@@ -356,8 +356,11 @@ void rope_norm_launch_bwd(RopeNormParams p0, RopeNormParams p1, int n_tensors, l
     grid = std::min(grid, (unsigned)(kRopeNormMaxCtasPerSm * sm_count()));  // the workspace holds that many partial sums
     p0.partial = workspace;
     p1.partial = workspace + (size_t)kRopeNormMaxCtasPerSm * sm_count() * D;
-    rope_norm_bwd_kernel<D, F32><<<grid, kRopeNormThreads, 0, st>>>(p0, p1, n_tensors);
-    rope_norm_dgamma_kernel<D><<<n_tensors * D, 32, 0, st>>>(p0.partial, p0.d_gamma, p1.partial, p1.d_gamma, (int)grid);
+    launch_pdl(rope_norm_bwd_kernel<D, F32>, dim3(grid, 1, 1), kRopeNormThreads, 0, st, p0, p1, n_tensors);
+    const float* part0 = p0.partial;
+    const float* part1 = p1.partial;
+    launch_pdl(rope_norm_dgamma_kernel<D>, dim3(n_tensors * D, 1, 1), 32, 0, st, part0, p0.d_gamma, part1, p1.d_gamma,
+               (int)grid);
 }
 
 void rope_norm_fill(RopeNormParams& p, int B, int T, int H, int D, int x_layout, int y_layout) {

@@ -191,6 +191,7 @@ template <int D, bool F32>
 __global__ void __launch_bounds__(kRopeNormThreads, 3)
 rope_norm_fwd_kernel(const __grid_constant__ RopeNormParams p0, const __grid_constant__ RopeNormParams p1,
                      const int n_tensors) {
+    grid_dep_wait();  // launched with programmatic stream serialization: the inputs come from the kernel before
     rope_norm_fwd_tensor<D, F32>(p0);
     if (n_tensors > 1) rope_norm_fwd_tensor<D, F32>(p1);
 }
@@ -291,6 +292,7 @@ __global__ void __launch_bounds__(kRopeNormThreads, 2)
 rope_norm_bwd_kernel(const __grid_constant__ RopeNormParams p0, const __grid_constant__ RopeNormParams p1,
                      const int n_tensors) {
     __shared__ float s_part[kRopeNormThreads / 32][D];
+    grid_dep_wait();
     rope_norm_bwd_tensor<D, F32>(p0, s_part);
     if (n_tensors > 1) rope_norm_bwd_tensor<D, F32>(p1, s_part);
 }
@@ -308,6 +310,7 @@ __global__ void __launch_bounds__(32) rope_norm_dgamma_kernel(const float* __res
     const float* partial = ts ? partial1 : partial0;
     float* d_gamma = ts ? d_gamma1 : d_gamma0;
     float acc = 0.f;
+    grid_dep_wait();  // the partial sums come from the kernel before this one
     for (int i = lane; i < n_parts; i += 32) acc += partial[static_cast<long long>(i) * D + d];
     acc = rn_warp_sum(acc);
     if (lane == 0) d_gamma[d] += acc;

@@ -562,7 +562,9 @@ def run_decode_step(m, cfg, args, rank, world, device, peaks, warmup, steps, bar
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "note": "the new token's rows from pinned host memory, o read back, a stream synchronise per step"},
         "roofline": {"bound": "hbm", "kernel": "attn_decode_kernel", "achieved": gbs / world, "peak": peak,
-                     "unit": "GB/s", "frac": gbs / world / peak, "traffic": None,
+                     "unit": "GB/s", "frac": gbs / world / peak,
+                     # the three kernels of a step, profiles/kv_append_decode_step_c5_decode.md
+                     "traffic": 272819456 if cfg.name == "c5_decode" else None,
                      "peak_source": f"hbm_gbs of {peaks['_source']}", "bytes_per_step": nbytes,
                      "note": "3 launches per step: kv_append_kernel, attn_decode_kernel, attn_decode_combine_kernel"},
     }

@@ -70,7 +70,7 @@ kv_append_kernel(const __grid_constant__ KvAppendParams p) {
                 which = 2;
             }
         }
-        float v[8], rot[8];
+        float v[8], rot[8], gm[8];
         float ss = 0.f;
         int b = 0, t = 0, h = 0;
         if (live) {
@@ -82,6 +82,11 @@ kv_append_kernel(const __grid_constant__ KvAppendParams p) {
             const void* x = which == 0 ? p.xq : (which == 1 ? p.xk : p.xv);
             rn_load8<F32>(x, static_cast<long long>(r) * D + li * 8, v);
             if (which != 2) {
+                // every load of the row is issued before the first use (one round trip to memory, not two)
+                const float* gamma = which == 0 ? p.gamma_q : p.gamma_k;
+                const float4 g0 = *reinterpret_cast<const float4*>(gamma + li * 8);
+                const float4 g1 = *reinterpret_cast<const float4*>(gamma + li * 8 + 4);
+                gm[0] = g0.x, gm[1] = g0.y, gm[2] = g0.z, gm[3] = g0.w, gm[4] = g1.x, gm[5] = g1.y, gm[6] = g1.z, gm[7] = g1.w;
                 const long long pos = p.pos0 + t;
                 const float4 cs = *reinterpret_cast<const float4*>(p.cos_t + pos * (D / 2) + li * 4);
                 const float4 sn = *reinterpret_cast<const float4*>(p.sin_t + pos * (D / 2) + li * 4);
@@ -94,10 +99,7 @@ kv_append_kernel(const __grid_constant__ KvAppendParams p) {
             rn_store8<false>(p.vcache, ((static_cast<long long>(b) * p.Hkv + h) * p.L_cap + p.pos0 + t) * D + li * 8, v);
             continue;
         }
-        const float* gamma = which == 0 ? p.gamma_q : p.gamma_k;
-        float gm[8], out[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) gm[e] = gamma[li * 8 + e];
+        float out[8];
         rn_scale8(rot, rn_rstd<D>(ss, p.eps), gm, out);
         if (which == 0)
             rn_store8<false>(p.q_out, ((static_cast<long long>(b) * p.Hq + h) * p.n_new + t) * D + li * 8, out);

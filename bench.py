@@ -21,6 +21,7 @@ so scaling is "weak"; NCCL only carries the timing reduction and a checksum gath
 from __future__ import annotations
 
 import argparse
+import dataclasses
 import json
 import os
 import sys
@@ -60,6 +61,9 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c2_50m_train")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak (default): every rank runs the whole config; strong: the config's batch is split over "
+                         "the ranks (contiguous (batch, KV head) units), so the total work is fixed")
     ap.add_argument("--op", default="attention", choices=["attention", "qkprep", "decode_step"],
                     help="qkprep: the fused RoPE + QK-Norm operator on the config's q and k (HBM GB/s); "
                          "decode_step (with --config c5_decode): one cached sampling step of a layer, KV-cache "
@@ -598,6 +602,12 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    global_B = cfg.B * world
+    if args.scaling == "strong" and world > 1:
+        if cfg.B % world != 0:
+            raise SystemExit(f"--scaling strong: the batch {cfg.B} does not divide over {world} ranks")
+        global_B = cfg.B
+        cfg = dataclasses.replace(cfg, B=cfg.B // world)  # this rank's contiguous block of (batch, KV head) units
 
     if args.impl == "reference":
         run_reference_arm(args, cfg, rank, world)
@@ -696,7 +706,7 @@ def main():
     achieved = kflops[dom] / (kt[dom] * 1e-3) / 1e12
     roofline = {
         "bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-        "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(cfg.name, {}).get(dom),
+        "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(cfg.name, {}).get(dom) if cfg.B == inputs.CONFIGS[args.config].B else None,
         "peak_source": f"bf16_tflops_sustained of {peaks['_source']} (kernel timed inside a long loop); burst "
                        f"{peaks['bf16_tflops']}",
         "flops_per_launch": kflops[dom], "ms_per_launch": kt[dom],
@@ -734,10 +744,10 @@ def main():
     if rank == 0:
         line = {
             "metric": "causal_gqa_attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
-            "steps": steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "steps": steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling,
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": cfg.name, "B_per_gpu": cfg.B, "T": cfg.T, "Hq": cfg.Hq, "Hkv": cfg.Hkv, "D": cfg.D,
-                       "layout": "BHTD", "parallelism": f"{world} x independent (batch, KV head) shards",
+            "config": {"workload": cfg.name, "B_per_gpu": cfg.B, "global_B": global_B, "T": cfg.T, "Hq": cfg.Hq,
+                       "Hkv": cfg.Hkv, "D": cfg.D, "layout": "BHTD", "parallelism": f"{world} x independent (batch, KV head) shards",
                        "l2": f"rotating over {n_sets} buffer sets, {n_sets * probe.nbytes() / 1e6:.0f} MB > 126 MB L2",
                        "inputs": "q,k: N(0,1) -> RoPE(base 1e4) -> per-head RMSNorm(gamma 1); v: N(0,1); "
                                  "dO: N(0,1e-2); rounded to BF16"},

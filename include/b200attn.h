@@ -157,6 +157,25 @@ int b200attn_decode_cached(const void* q, const void* kcache, const void* vcache
                            int L_cap, int Hq, int Hkv, int D, float softmax_scale, int n_splits, void* workspace,
                            size_t workspace_bytes, void* stream);
 
+/*
+ * The same two calls for sequences of different lengths (a batch that does not advance in lock step).
+ * b200attn_kv_append_at: pos [B] (device, int32) is the first position of each sequence's n_new tokens.  A
+ * sequence whose pos[b] + n_new exceeds L_cap is skipped and sets the device status word to 105
+ * (b200attn_last_device_status reports and clears it).
+ * b200attn_decode_ragged: lens [B] (device, int32), 1 <= lens[b] <= L, is each sequence's cache length
+ * (the newest token included); L is the host's upper bound on them: it sizes the grid, the splits and the
+ * workspace (b200attn_decode_workspace_bytes with this L).  Rows lens[b] .. L-1 of a sequence's caches are
+ * read but carry no weight; they must hold finite values (a cache that starts zeroed does).  lens == NULL is
+ * b200attn_decode_cached.
+ */
+int b200attn_kv_append_at(const void* xq, const void* xk, const void* xv, int x_dtype, void* q_out, void* kcache,
+                          void* vcache, const float* gamma_q, const float* gamma_k, const float* cos_t,
+                          const float* sin_t, const int* pos, int B, int n_new, int L_cap, int Hq, int Hkv, int D,
+                          float eps, void* stream);
+int b200attn_decode_ragged(const void* q, const void* kcache, const void* vcache, void* o, float* lse, const int* lens,
+                           int B, int L, int L_cap, int Hq, int Hkv, int D, float softmax_scale, int n_splits,
+                           void* workspace, size_t workspace_bytes, void* stream);
+
 
 /*
  * Fused RoPE + per-head RMSNorm ("QK-Norm") that prepares q or k for b200attn_fwd, and its backward.
@@ -210,8 +229,9 @@ int b200attn_set_bwd_profile_events(void* ev_start, void* ev_after_dq, void* ev_
 
 /*
  * Synchronises `stream` and returns the device status word of the current device:
- * 0, or the code of the first bounded wait that gave up since the last call (the
- * word is then cleared).  The reference surfaces execution errors at a later
+ * 0, or the code of the first bounded wait that gave up since the last call (101 load,
+ * 102 tensor core, 103 softmax hand-off, 104 buffer free), or 105 when b200attn_kv_append_at met a
+ * position beyond the cache capacity (the word is then cleared).  The reference surfaces execution errors at a later
  * synchronisation too (llm/src/core/cuda_check.h:31-45).
  */
 int b200attn_last_device_status(void* stream);

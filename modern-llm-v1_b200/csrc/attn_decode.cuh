@@ -25,6 +25,7 @@ struct DecodeParams {
     int n_splits;
     int tiles_per_split;
     float scale, scale_log2;
+    const int* lens;    // [B] cache length per sequence (1 <= lens[b]; clamped to L), or nullptr: every sequence has L
     const uint16_t* q;  // [B, Hq, D]
     float* part_o;      // [B, Hq, n_splits, D]
     float* part_m;      // [B, Hq, n_splits]   row maximum, raw score units
@@ -101,8 +102,6 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     const int b = blockIdx.z;
     const int h0 = hk * p.group + chunk * G;  // first query head served here
     const int tile0 = split * p.tiles_per_split;
-    const int n_all = (p.L + 127) / 128;
-    const int n_tiles = max(0, min(p.tiles_per_split, n_all - tile0));
 
     if (tid == 0) {
         for (int s = 0; s < NST; ++s) {
@@ -119,6 +118,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     if (tid == 0) *abort_flag = *reinterpret_cast<volatile int*>(p.status);
     __syncthreads();
     if (*abort_flag != 0) return;
+    // this sequence's length: a split that lies beyond it writes an empty partial (m = -inf, l = 0)
+    const int L = p.lens ? max(1, min(__ldg(p.lens + b), p.L)) : p.L;
+    const int n_all = (L + 127) / 128;
+    const int n_tiles = max(0, min(p.tiles_per_split, n_all - tile0));
     // q rows of the G heads -> shared memory (BF16, 16-byte chunks, swizzled); rows >= G are zero
     for (int i = tid; i < 16 * (D / 8); i += blockDim.x) {
         const int r = i / (D / 8), c = i % (D / 8);
@@ -189,11 +192,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         }
         // ---- mask keys beyond the cache length (last tile only)
         const int key0 = (tile0 + j) * 128 + kw + (lane & 3) * 2;
-        if ((tile0 + j) * 128 + 128 > p.L) {
+        if ((tile0 + j) * 128 + 128 > L) {
 #pragma unroll
             for (int nt = 0; nt < 4; ++nt) {
-                if (key0 + nt * 8 >= p.L) sc[nt][0] = sc[nt][2] = -INFINITY;
-                if (key0 + nt * 8 + 1 >= p.L) sc[nt][1] = sc[nt][3] = -INFINITY;
+                if (key0 + nt * 8 >= L) sc[nt][0] = sc[nt][2] = -INFINITY;
+                if (key0 + nt * 8 + 1 >= L) sc[nt][1] = sc[nt][3] = -INFINITY;
             }
         }
         // ---- online softmax per head row (rows r0 and r1), over this warp's 32 keys

@@ -687,6 +687,14 @@ extern "C" int b200attn_decode(const void* q, const void* kcache, const void* vc
 extern "C" int b200attn_decode_cached(const void* q, const void* kcache, const void* vcache, void* o, float* lse, int B,
                                       int L, int L_cap, int Hq, int Hkv, int D, float softmax_scale, int n_splits,
                                       void* workspace, size_t workspace_bytes, void* stream) {
+    return b200attn_decode_ragged(q, kcache, vcache, o, lse, nullptr, B, L, L_cap, Hq, Hkv, D, softmax_scale, n_splits,
+                                  workspace, workspace_bytes, stream);
+}
+
+extern "C" int b200attn_decode_ragged(const void* q, const void* kcache, const void* vcache, void* o, float* lse,
+                                      const int* lens, int B, int L, int L_cap, int Hq, int Hkv, int D,
+                                      float softmax_scale, int n_splits, void* workspace, size_t workspace_bytes,
+                                      void* stream) {
     int rc = check_common(B, L, Hq, Hkv, D, B200ATTN_LAYOUT_BHTD);
     if (rc) return rc;
     if (L_cap < L) return B200ATTN_ERR_INVALID_ARG;
@@ -716,6 +724,7 @@ extern "C" int b200attn_decode_cached(const void* q, const void* kcache, const v
     p.scale = softmax_scale > 0.f ? softmax_scale : 1.f / sqrtf((float)D);
     p.scale_log2 = p.scale * 1.4426950408889634f;
     p.q = static_cast<const uint16_t*>(q);
+    p.lens = lens;
     float* ws = static_cast<float*>(workspace);
     const size_t rows = (size_t)B * Hq;
     p.part_o = ws;
@@ -760,10 +769,33 @@ int launch_kv_append(const KvAppendParams& p, cudaStream_t st) {
 
 }  // namespace
 
+namespace {
+int kv_append_run(const void* xq, const void* xk, const void* xv, int x_dtype, void* q_out, void* kcache, void* vcache,
+                  const float* gamma_q, const float* gamma_k, const float* cos_t, const float* sin_t, const int* pos,
+                  int B, int n_new, int pos0, int L_cap, int Hq, int Hkv, int D, float eps, void* stream);
+}
+
 extern "C" int b200attn_kv_append(const void* xq, const void* xk, const void* xv, int x_dtype, void* q_out, void* kcache,
                                   void* vcache, const float* gamma_q, const float* gamma_k, const float* cos_t,
                                   const float* sin_t, int B, int n_new, int pos0, int L_cap, int Hq, int Hkv, int D,
                                   float eps, void* stream) {
+    return kv_append_run(xq, xk, xv, x_dtype, q_out, kcache, vcache, gamma_q, gamma_k, cos_t, sin_t, nullptr, B, n_new, pos0,
+                         L_cap, Hq, Hkv, D, eps, stream);
+}
+
+extern "C" int b200attn_kv_append_at(const void* xq, const void* xk, const void* xv, int x_dtype, void* q_out, void* kcache,
+                                     void* vcache, const float* gamma_q, const float* gamma_k, const float* cos_t,
+                                     const float* sin_t, const int* pos, int B, int n_new, int L_cap, int Hq, int Hkv,
+                                     int D, float eps, void* stream) {
+    if (!pos) return B200ATTN_ERR_INVALID_ARG;
+    return kv_append_run(xq, xk, xv, x_dtype, q_out, kcache, vcache, gamma_q, gamma_k, cos_t, sin_t, pos, B, n_new, 0, L_cap,
+                         Hq, Hkv, D, eps, stream);
+}
+
+namespace {
+int kv_append_run(const void* xq, const void* xk, const void* xv, int x_dtype, void* q_out, void* kcache, void* vcache,
+                  const float* gamma_q, const float* gamma_k, const float* cos_t, const float* sin_t, const int* pos,
+                  int B, int n_new, int pos0, int L_cap, int Hq, int Hkv, int D, float eps, void* stream) {
     if (B <= 0 || n_new <= 0 || pos0 < 0 || L_cap <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0) return B200ATTN_ERR_INVALID_ARG;
     if (Hq % Hkv != 0 || (long long)pos0 + n_new > L_cap) return B200ATTN_ERR_INVALID_ARG;
     if (x_dtype != B200ATTN_DTYPE_BF16 && x_dtype != B200ATTN_DTYPE_F32) return B200ATTN_ERR_INVALID_ARG;
@@ -775,7 +807,12 @@ extern "C" int b200attn_kv_append(const void* xq, const void* xk, const void* xv
         return B200ATTN_ERR_ALIGNMENT;
     const long long rows_q = (long long)B * n_new * Hq, rows_kv = (long long)B * n_new * Hkv;
     if (rows_q + 2 * rows_kv >= (1LL << 31)) return B200ATTN_ERR_TOO_LARGE;
+    int rc = 0;
+    int* status = status_ptr(&rc);
+    if (!status) return rc;
     KvAppendParams p;
+    p.pos = pos;
+    p.status = status;
     p.xq = xq;
     p.xk = xk;
     p.xv = xv;
@@ -803,6 +840,7 @@ extern "C" int b200attn_kv_append(const void* xq, const void* xk, const void* xv
     if (D == 64) return f32 ? launch_kv_append<64, true>(p, st) : launch_kv_append<64, false>(p, st);
     return f32 ? launch_kv_append<128, true>(p, st) : launch_kv_append<128, false>(p, st);
 }
+}  // namespace
 
 extern "C" int b200attn_last_device_status(void* stream) {
     int rc = 0;
@@ -845,6 +883,7 @@ extern "C" const char* b200attn_strerror(int status) {
         case DEV_WAIT_TIMEOUT_MMA: return "device: a tensor-core completion barrier never completed";
         case DEV_WAIT_TIMEOUT_SOFTMAX: return "device: a softmax hand-off barrier never completed";
         case DEV_WAIT_TIMEOUT_FREE: return "device: a buffer-free barrier never completed";
+        case DEV_KV_CACHE_OVERFLOW: return "device: a KV-cache position plus the new tokens exceeds the cache capacity";
         default: return "unknown status";
     }
 }

@@ -33,6 +33,8 @@ struct KvAppendParams {
     const float* gamma_k;  // [D]
     const float* cos_t;    // [>= pos0 + n_new, D/2]
     const float* sin_t;
+    const int* pos;        // [B] first position per sequence, or nullptr: pos0 for every sequence
+    int* status;           // set to DEV_KV_CACHE_OVERFLOW when a row would land beyond the capacity (the row is skipped)
     int B, n_new, pos0, L_cap, Hq, Hkv;
     unsigned rows_q, rows_kv;  // B * n_new * Hq, B * n_new * Hkv
     FastDiv div_hq, div_hkv, div_n;
@@ -72,13 +74,17 @@ kv_append_kernel(const __grid_constant__ KvAppendParams p) {
         }
         float v[8], rot[8], gm[8];
         float ss = 0.f;
-        int b = 0, t = 0, h = 0;
+        int b = 0, t = 0, h = 0, pos0 = 0;
+        bool fits = true;
         if (live) {
             const int H = which == 0 ? p.Hq : p.Hkv;
             const unsigned bt = fastdiv(r, which == 0 ? p.div_hq : p.div_hkv);
             h = int(r - bt * unsigned(H));
             b = int(fastdiv(bt, p.div_n));
             t = int(bt - unsigned(b) * unsigned(p.n_new));
+            pos0 = p.pos ? __ldg(p.pos + b) : p.pos0;
+            fits = pos0 >= 0 && pos0 + p.n_new <= p.L_cap;  // the host checked pos0; an array of positions is checked here
+            if (!fits) pos0 = 0;
             const void* x = which == 0 ? p.xq : (which == 1 ? p.xk : p.xv);
             rn_load8<F32>(x, static_cast<long long>(r) * D + li * 8, v);
             if (which != 2) {
@@ -87,7 +93,7 @@ kv_append_kernel(const __grid_constant__ KvAppendParams p) {
                 const float4 g0 = *reinterpret_cast<const float4*>(gamma + li * 8);
                 const float4 g1 = *reinterpret_cast<const float4*>(gamma + li * 8 + 4);
                 gm[0] = g0.x, gm[1] = g0.y, gm[2] = g0.z, gm[3] = g0.w, gm[4] = g1.x, gm[5] = g1.y, gm[6] = g1.z, gm[7] = g1.w;
-                const long long pos = p.pos0 + t;
+                const long long pos = pos0 + t;
                 const float4 cs = *reinterpret_cast<const float4*>(p.cos_t + pos * (D / 2) + li * 4);
                 const float4 sn = *reinterpret_cast<const float4*>(p.sin_t + pos * (D / 2) + li * 4);
                 ss = rn_rotate8(v, cs, sn, rot);
@@ -95,8 +101,12 @@ kv_append_kernel(const __grid_constant__ KvAppendParams p) {
         }
         ss = rn_row_sum<LPR>(ss);  // every lane takes part in the shuffles
         if (!live) continue;
+        if (!fits) {
+            if (li == 0) atomicExch(p.status, int(DEV_KV_CACHE_OVERFLOW));
+            continue;
+        }
         if (which == 2) {
-            rn_store8<false>(p.vcache, ((static_cast<long long>(b) * p.Hkv + h) * p.L_cap + p.pos0 + t) * D + li * 8, v);
+            rn_store8<false>(p.vcache, ((static_cast<long long>(b) * p.Hkv + h) * p.L_cap + pos0 + t) * D + li * 8, v);
             continue;
         }
         float out[8];
@@ -104,7 +114,7 @@ kv_append_kernel(const __grid_constant__ KvAppendParams p) {
         if (which == 0)
             rn_store8<false>(p.q_out, ((static_cast<long long>(b) * p.Hq + h) * p.n_new + t) * D + li * 8, out);
         else
-            rn_store8<false>(p.kcache, ((static_cast<long long>(b) * p.Hkv + h) * p.L_cap + p.pos0 + t) * D + li * 8, out);
+            rn_store8<false>(p.kcache, ((static_cast<long long>(b) * p.Hkv + h) * p.L_cap + pos0 + t) * D + li * 8, out);
     }
 }
 

@@ -24,6 +24,7 @@ enum DeviceStatus : int {
     DEV_WAIT_TIMEOUT_MMA = 102,    // a tcgen05.commit barrier never completed
     DEV_WAIT_TIMEOUT_SOFTMAX = 103,// a softmax->MMA hand-off barrier never completed
     DEV_WAIT_TIMEOUT_FREE = 104,   // a stage/TMEM "free" barrier never completed
+    DEV_KV_CACHE_OVERFLOW = 105,   // kv_append with per-sequence positions: a position + n_new exceeds the capacity
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

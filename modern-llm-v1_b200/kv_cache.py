@@ -7,7 +7,9 @@ ModernGPT block (llm/src/model/modern_gpt.cu:351-378): per layer a BF16 K and V 
 [B, Hkv, L_cap, D]; `append` does split_heads + RoPE at the true positions + QK-Norm for the newest
 tokens and stores their k and v, `attend` runs attention for them (causal forward over the prompt,
 or the split-KV decode kernel for one token), `advance` moves the length once every layer is done.
-The B sequences advance in lock step.  Like the reference's operators, the caller allocates every
+The B sequences advance in lock step until `set_lengths` gives each its own length (a batch of
+prompts of different lengths); from then on `append` and `attend` take one token per sequence at the
+sequence's own position.  Like the reference's operators, the caller allocates every
 input and output; bad arguments raise ValueError, CUDA failures RuntimeError; there is no CPU or
 PyTorch fallback.
 """
@@ -36,11 +38,27 @@ class KVCache:
         self.k = torch.zeros((n_layers, B, Hkv, L_cap, D), dtype=torch.bfloat16, device=self.device)
         self.v = torch.zeros_like(self.k)
         self.cos, self.sin = make_rope_cache(L_cap, D, rope_base, device=self.device)
-        self.length = 0  # tokens held by every layer
+        self.length = 0  # tokens held by every layer (the longest sequence's, once lengths differ)
+        self.lengths = None  # per-sequence lengths [B] int32 on the device, once set_lengths was called
+        self._lens_next = None  # lengths + 1: what the decode kernel reads while the newest token is being attended
+        self._lengths_host = None
 
     def reset(self) -> None:
         """Forgets every token (the buffers keep their bytes; rows >= length are never read)."""
         self.length = 0
+        self.lengths = self._lens_next = self._lengths_host = None
+
+    def set_lengths(self, lengths) -> None:
+        """Gives every sequence its own length (e.g. after a padded prompt batch went through `append` /
+        `attend` / `advance` with the longest prompt's length): rows at and beyond a sequence's length are
+        treated as not yet written."""
+        host = [int(x) for x in lengths]
+        if len(host) != self.B or min(host) < 0 or max(host) > self.L_cap:
+            raise ValueError("KVCache.set_lengths: need B lengths in [0, L_cap]")
+        self._lengths_host = host
+        self.length = max(host)
+        self.lengths = torch.tensor(host, dtype=torch.int32, device=self.device)
+        self._lens_next = self.lengths + 1
 
     def _layer(self, fn: str, layer: int) -> None:
         if not 0 <= layer < self.n_layers:
@@ -72,6 +90,17 @@ class KVCache:
         if self.length + n_new > self.L_cap:
             raise ValueError(f"{fn}: {self.length} + {n_new} tokens exceed the capacity {self.L_cap}")
         lib = _lib.load()
+        if self.lengths is not None:
+            if n_new != 1:
+                raise ValueError(f"{fn}: one token per sequence once the lengths differ")
+            with torch.cuda.device(self.device):
+                rc = lib.b200attn_kv_append_at(xq.data_ptr(), xk.data_ptr(), xv.data_ptr(), xd, q_out.data_ptr(),
+                                               self.k[layer].data_ptr(), self.v[layer].data_ptr(), gamma_q.data_ptr(),
+                                               gamma_k.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(),
+                                               self.lengths.data_ptr(), B, 1, self.L_cap, Hq, Hkv, D,
+                                               ctypes.c_float(self.eps), _stream_ptr())
+            _lib.check(rc, fn)
+            return
         with torch.cuda.device(self.device):
             rc = lib.b200attn_kv_append(xq.data_ptr(), xk.data_ptr(), xv.data_ptr(), xd, q_out.data_ptr(),
                                         self.k[layer].data_ptr(), self.v[layer].data_ptr(), gamma_q.data_ptr(),
@@ -105,9 +134,11 @@ class KVCache:
                 L = self.length + 1
                 nbytes = int(lib.b200attn_decode_workspace_bytes(B, L, Hq, Hkv, D, 0))
                 ws = _workspace("decode", nbytes, self.device)
-                rc = lib.b200attn_decode_cached(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), ctx.data_ptr(),
-                                                lse.data_ptr() if lse is not None else None, B, L, self.L_cap, Hq, Hkv,
-                                                D, scale, 0, ws.data_ptr(), ws.numel(), _stream_ptr())
+                rc = lib.b200attn_decode_ragged(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), ctx.data_ptr(),
+                                                lse.data_ptr() if lse is not None else None,
+                                                self._lens_next.data_ptr() if self.lengths is not None else None, B, L,
+                                                self.L_cap, Hq, Hkv, D, scale, 0, ws.data_ptr(), ws.numel(),
+                                                _stream_ptr())
             else:
                 if self.length != 0:
                     raise ValueError(f"{fn}: several tokens at once only into an empty cache (prompt)")
@@ -123,3 +154,7 @@ class KVCache:
         if n_new <= 0 or self.length + n_new > self.L_cap:
             raise ValueError("KVCache.advance: n_new out of range")
         self.length += n_new
+        if self.lengths is not None:
+            self._lengths_host = [x + n_new for x in self._lengths_host]
+            self.lengths += n_new
+            self._lens_next += n_new

@@ -176,3 +176,55 @@ def test_capacity_and_argument_errors():
                                     1, 64, 0.0, 0, cache.k.data_ptr(), 1 << 20, None)
     assert rc == 1  # L > L_cap
     m.device_status()
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,D,lens", [
+    (5, 6, 2, 64, (1, 128, 129, 777, 300)),
+    (4, 16, 4, 128, (513, 2, 64, 1000)),
+    (3, 8, 8, 64, (255, 256, 257)),
+])
+def test_sequences_of_different_lengths_match_the_oracle_one_by_one(B, Hq, Hkv, D, lens):
+    """Per-sequence lengths: the new token of sequence b is rotated at position lens[b] - 1, lands in row
+    lens[b] - 1 of its cache and attends to lens[b] rows; every sequence is checked against the oracle alone."""
+    L_cap = 1024
+    g = torch.Generator().manual_seed(31)
+    kc = torch.randn((B, Hkv, L_cap, D), generator=g).bfloat16().cuda()
+    vc = torch.randn((B, Hkv, L_cap, D), generator=g).bfloat16().cuda()
+    xq, xk, xv, gq, gk = _inputs(B, 1, Hq, Hkv, D, torch.float32, 32)
+    cache = m.KVCache(1, B, Hq, Hkv, D, L_cap)
+    cache.k[0].copy_(kc)
+    cache.v[0].copy_(vc)
+    cache.set_lengths([n - 1 for n in lens])  # the tokens before the new one
+    q = _append(cache, 0, xq, xk, xv, gq, gk)
+    o = torch.full_like(q, float("nan"))
+    lse = torch.full((B, Hq, 1), float("nan"), device="cuda")
+    cache.attend(0, q, o, lse)
+    cache.advance()
+    m.device_status()
+    assert cache._lengths_host == list(lens) and cache.lengths.tolist() == list(lens)
+    for b, n in enumerate(lens):
+        kb, vb = np32(kc[b:b + 1]).copy(), np32(vc[b:b + 1]).copy()
+        wq = ao.kv_append(np32(xq[b:b + 1]), np32(xk[b:b + 1]), np32(xv[b:b + 1]), np32(gq), np32(gk), kb, vb, n - 1)
+        assert_close(f"q[{b}]", q[b:b + 1], wq)
+        assert_close(f"K row[{b}]", cache.k[0, b, :, n - 1], kb[0, :, n - 1])
+        # only row n - 1 of the sequence's caches changed
+        keep = torch.ones(L_cap, dtype=torch.bool)
+        keep[n - 1] = False
+        assert torch.equal(cache.k[0, b][:, keep.cuda()], kc[b][:, keep.cuda()])
+        assert torch.equal(cache.v[0, b][:, keep.cuda()], vc[b][:, keep.cuda()])
+        wo, wl = ao.decode_c(ao.round_bf16(wq[:, :, 0]), ao.round_bf16(kb[:, :, :n]), ao.round_bf16(vb[:, :, :n]))
+        assert_close(f"O[{b}]", o[b:b + 1, :, 0], wo)
+        assert_close(f"LSE[{b}]", lse[b:b + 1, :, 0], wl, max_abs=2 * TOL_LSE, rel_l2=1.0)
+
+
+def test_a_position_beyond_the_capacity_is_reported_and_skipped():
+    B, Hq, Hkv, D, L_cap = 2, 2, 1, 64, 8
+    xq, xk, xv, gq, gk = _inputs(B, 1, Hq, Hkv, D, torch.float32, 33)
+    cache = m.KVCache(1, B, Hq, Hkv, D, L_cap)
+    cache.set_lengths([3, 7])
+    cache.lengths[1] = 8  # the device copy says "full" behind the host's back
+    q = _append(cache, 0, xq, xk, xv, gq, gk)
+    with pytest.raises(RuntimeError, match="exceeds the cache capacity"):
+        m.device_status()
+    assert m.device_status() == 0  # reported once, then cleared
+    assert cache.k[0, 0, :, 3].abs().sum().item() > 0 and cache.k[0, 1].abs().sum().item() == 0

@@ -70,6 +70,7 @@ def test_kvcache_argument_checks_come_before_any_cuda_call():
     c = m.KVCache.__new__(m.KVCache)
     c.n_layers, c.B, c.Hq, c.Hkv, c.D, c.L_cap, c.eps, c.length = 2, 2, 4, 2, 64, 8, 1e-5, 0
     c.device = torch.device("cpu")
+    c.lengths = c._lens_next = c._lengths_host = None
     xq = torch.zeros(2, 1, 4, 64)
     xk = torch.zeros(2, 1, 2, 64)
     g = torch.ones(64)
@@ -94,3 +95,7 @@ def test_kvcache_argument_checks_come_before_any_cuda_call():
         c.advance(1)
     c.reset()
     assert c.length == 0
+    with pytest.raises(ValueError, match="B lengths"):
+        c.set_lengths([1, 2, 3])
+    with pytest.raises(ValueError, match="B lengths"):
+        c.set_lengths([1, 9])

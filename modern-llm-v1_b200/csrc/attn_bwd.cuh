@@ -171,7 +171,7 @@ template <int D>
 __global__ void __launch_bounds__(DqCfg<D>::kThreads, DqCfg<D>::kCtasPerSm)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                   const __grid_constant__ CUtensorMap tmO, const BwdParams p) {
+                   const __grid_constant__ CUtensorMap tmO, const BwdParams p, const __grid_constant__ ItemTable tab) {
     using Cfg = DqCfg<D>;
     constexpr int NST = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -252,11 +252,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         // ------------------------------------------------------------------ producer
         int g = 0;  // tiles issued so far by this CTA (ring position)
         bool ok = true;
-        int id = blockIdx.x;  // the first item needs no fetch
+        int id = sched_first(tab, p.sched, int(blockIdx.x));  // the first item needs no fetch
         int id_next = 0;      // lane 0: the id fetched for the next item
         if (lane == 0) {
             item_publish(bar_item, item_ring, 0, id);
-            id_next = sched_fetch(p.sched, 1, int(blockIdx.x), int(gridDim.x));
+            id_next = sched_fetch(tab, p.sched, 1, int(blockIdx.x), int(gridDim.x));
         }
         __syncwarp();
         for (int n = 0; ok; ++n) {
@@ -297,7 +297,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     id_new = __shfl_sync(0xffffffffu, id_next, 0);
                     if (lane == 0) {
                         item_publish(bar_item, item_ring, n + 1, id_new < n_items ? id_new : -1);
-                        if (id_new < n_items) id_next = sched_fetch(p.sched, n + 2, int(blockIdx.x), int(gridDim.x));
+                        if (id_new < n_items) id_next = sched_fetch(tab, p.sched, n + 2, int(blockIdx.x), int(gridDim.x));
                     }
                     __syncwarp();
                 }

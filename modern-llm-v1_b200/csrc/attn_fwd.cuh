@@ -67,7 +67,7 @@ constexpr float kRescaleThresholdLog2 = 8.0f;
 template <int D>
 __global__ void __launch_bounds__(256, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
+                const __grid_constant__ CUtensorMap tmV, const FwdParams p, const __grid_constant__ ItemTable tab) {
     using Cfg = FwdCfg<D>;
     constexpr int NST = Cfg::kStages;
     constexpr int NQB = Cfg::kQBufs;
@@ -172,10 +172,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             }
             __syncwarp();
         };
-        int id = blockIdx.x;  // the first item needs no fetch
+        int id = sched_first(tab, p.sched, int(blockIdx.x));  // the first item needs no fetch
         if (lane == 0) {
             item_publish(bar_item, item_ring, 0, id);
-            id_next = sched_fetch(p.sched, 1, int(blockIdx.x), int(gridDim.x));
+            id_next = sched_fetch(tab, p.sched, 1, int(blockIdx.x), int(gridDim.x));
         }
         __syncwarp();
         load_q(0, id);
@@ -214,7 +214,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     const bool more = id_new < n_items;
                     if (lane == 0) {
                         item_publish(bar_item, item_ring, n + 1, more ? id_new : -1);
-                        if (more) id_next = sched_fetch(p.sched, n + 2, int(blockIdx.x), int(gridDim.x));
+                        if (more) id_next = sched_fetch(tab, p.sched, n + 2, int(blockIdx.x), int(gridDim.x));
                     }
                     __syncwarp();
                     if (more) load_q(n + 1, id_new);

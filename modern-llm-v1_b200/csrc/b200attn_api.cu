@@ -6,6 +6,10 @@
 
 #include <algorithm>
 #include <atomic>
+#include <functional>
+#include <queue>
+#include <utility>
+#include <vector>
 #include <math.h>
 #include <stdint.h>
 #include <stdlib.h>
@@ -85,6 +89,69 @@ int* next_sched_pair(long long n_items, unsigned n_ctas) {
     int dev = 0;
     cudaGetDevice(&dev);
     return g_sched_ptr[dev] + 2 * (g_sched_seq.fetch_add(1, std::memory_order_relaxed) % kSchedSlots);
+}
+
+// The static deal of the forward and the dQ pass (two CTAs per SM) as a table: items (ids are heaviest first;
+// item id covers query tile n_qtiles - 1 - id / n_groups, i.e. that many 64-key tiles plus item_cost half tiles
+// for its loads and epilogue; the deal at the training shapes is the same for costs from 1 to 8) go, longest first, to the list with the least work; then the lists are handed out by
+// falling work, so that block i (one of the first n_SMs blocks) and block i + n_SMs, which share an SM, get a
+// heavy and a light list.  Returns a table with per_cta == 0 when the deal does not fit the table (the kernel
+// then uses the closed formula) or when B200ATTN_ITEMS=static asks for the formula.
+const ItemTable& item_table_for(long long n_items, unsigned n_ctas, int n_groups, int n_qtiles, int T, int item_cost) {
+    static const ItemTable none = [] {
+        ItemTable t;
+        t.per_cta = 0;
+        return t;
+    }();
+    static const bool formula = [] {
+        const char* e = getenv("B200ATTN_ITEMS");
+        return e && e[0] == 's';
+    }();
+    if (formula || n_ctas > (unsigned)kItemTableCtas || n_items >= 0xffff || n_items < (long long)n_ctas) return none;
+    struct Entry {
+        long long n_items = -1;
+        unsigned n_ctas = 0;
+        int n_groups = 0, n_qtiles = 0, T = 0, cost = 0;
+        ItemTable tab;
+    };
+    thread_local Entry cache[4];
+    thread_local unsigned next = 0;
+    for (Entry& e : cache)
+        if (e.n_items == n_items && e.n_ctas == n_ctas && e.n_groups == n_groups && e.n_qtiles == n_qtiles && e.T == T &&
+            e.cost == item_cost)
+            return e.tab.per_cta >= 0 ? e.tab : none;
+    Entry& e = cache[next++ % 4];
+    e.n_items = n_items, e.n_ctas = n_ctas, e.n_groups = n_groups, e.n_qtiles = n_qtiles, e.T = T, e.cost = item_cost;
+    // longest processing time first; work in half tiles: an item costs its tiles plus half a tile
+    std::vector<std::vector<unsigned short>> lists(n_ctas);
+    std::vector<long long> load(n_ctas, 0);
+    using Slot = std::pair<long long, unsigned>;  // (work, list), least work first, then lowest index
+    std::priority_queue<Slot, std::vector<Slot>, std::greater<Slot>> heap;
+    for (unsigned c = 0; c < n_ctas; ++c) heap.push({0, c});
+    size_t longest = 0;
+    for (long long id = 0; id < n_items; ++id) {
+        const int qt = n_qtiles - 1 - (int)(id / n_groups);
+        const int rows = std::min(T, qt * 128 + 128);
+        const long long work = 2 * ((rows + 63) / 64) + item_cost;
+        const Slot s = heap.top();
+        heap.pop();
+        lists[s.second].push_back((unsigned short)id);
+        load[s.second] = s.first + work;
+        heap.push({load[s.second], s.second});
+        longest = std::max(longest, lists[s.second].size());
+    }
+    if (longest > (size_t)kItemTableMaxPerCta) {
+        e.tab.per_cta = -1;  // remembered as "no table"
+        return none;
+    }
+    std::vector<unsigned> order(n_ctas);
+    for (unsigned c = 0; c < n_ctas; ++c) order[c] = c;
+    std::stable_sort(order.begin(), order.end(), [&](unsigned a, unsigned b) { return load[a] > load[b]; });
+    e.tab.per_cta = (int)longest;
+    for (unsigned c = 0; c < n_ctas; ++c)
+        for (size_t n = 0; n < longest; ++n)
+            e.tab.ids[c * longest + n] = n < lists[order[c]].size() ? lists[order[c]][n] : kItemTableEnd;
+    return e.tab;
 }
 
 // SM count of the current device (cached per device).
@@ -169,7 +236,8 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
     pl.div_bh = fastdiv_make((unsigned)(p.B * p.Hq));
     pl.div_h = fastdiv_make((unsigned)p.Hq);
     pl.div_group = fastdiv_make((unsigned)p.group);
-    if (launch_pdl(attn_fwd_kernel<D>, grid, 256, Cfg::kSmemBytes, st, tq, tk, tv, pl) != cudaSuccess) {
+    const ItemTable& tab = item_table_for(pl.sched ? -1 : items, grid, p.B * p.Hq, p.n_qtiles, p.T, 1);
+    if (launch_pdl(attn_fwd_kernel<D>, grid, 256, Cfg::kSmemBytes, st, tq, tk, tv, pl, tab) != cudaSuccess) {
         cudaGetLastError();
         return B200ATTN_ERR_CUDA;
     }
@@ -282,7 +350,9 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk64, const CUtensorMap
     const cudaError_t e = kWide ? launch_pdl(attn_bwd_dq_wide_kernel<D>, dq_grid, 320, DqWideCfg<D>::kSmemBytes, st, tq, tk,
                                              tv, tdo, tdq, p)
                                 : launch_pdl(attn_bwd_dq_kernel<D>, dq_grid, DqCfg<D>::kThreads, DqCfg<D>::kSmemBytes, st, tq, tk64, tv64,
-                                             tdo, to, pq);
+                                             tdo, to, pq,
+                                             item_table_for(pq.sched ? -1 : (long long)dq_items, dq_grid, p.B * p.Hq,
+                                                            p.n_tiles, p.T, 4));
     if (e != cudaSuccess) {
         cudaGetLastError();
         return B200ATTN_ERR_CUDA;

@@ -277,6 +277,28 @@ __device__ __forceinline__ int sched_fetch(int* sched, int n, int cta, int n_cta
     if (sched == nullptr) return n * n_ctas + ((n & 1) ? n_ctas - 1 - cta : cta);
     return n_ctas + atomicAdd(&sched[0], 1);
 }
+// A static deal prepared on the host (a kernel parameter): CTA c takes ids[c * per_cta + n] as its n-th item,
+// kItemTableEnd ends its list.  The host balances the lists by their work (longest processing time first) and
+// hands the heavier lists to the lower block indices: with two CTAs per SM the hardware places block i and block
+// i + n_SMs on the same SM (measured: every SM got one block of each half in every launch), so an SM's two lists
+// are one heavy and one light one and all SMs finish together; the formula above leaves some SMs with two heavy
+// lists.  per_cta == 0: no table, use the formula (or the counter).
+constexpr int kItemTableCtas = 296, kItemTableMaxPerCta = 8;
+constexpr unsigned short kItemTableEnd = 0xffffu;
+struct ItemTable {
+    int per_cta;
+    unsigned short ids[kItemTableCtas * kItemTableMaxPerCta];
+};
+__device__ __forceinline__ int sched_fetch(const ItemTable& tab, int* sched, int n, int cta, int n_ctas) {
+    if (sched != nullptr || tab.per_cta == 0) return sched_fetch(sched, n, cta, n_ctas);
+    if (n >= tab.per_cta) return 0x7fffffff;
+    const unsigned short id = tab.ids[cta * tab.per_cta + n];
+    return id == kItemTableEnd ? 0x7fffffff : int(id);
+}
+// the CTA's first item: its block index, unless a table says otherwise
+__device__ __forceinline__ int sched_first(const ItemTable& tab, int* sched, int cta) {
+    return (sched != nullptr || tab.per_cta == 0) ? cta : int(tab.ids[cta * tab.per_cta]);
+}
 // Producer, lane 0 only, after its last sched_fetch: count this CTA; the last one resets the counters.
 __device__ __forceinline__ void sched_finish(int* sched, int n_ctas) {
     if (sched == nullptr) return;

@@ -228,6 +228,15 @@ int b200attn_rope_norm_bwd_qk(const void* dyq, const void* dyk, int y_layout, co
 int b200attn_set_bwd_profile_events(void* ev_start, void* ev_after_dq, void* ev_after_dkdv);
 
 /*
+ * The static deal of work items the forward and the dQ pass use when a problem has fewer than four items per
+ * CTA (host arithmetic only, no device needed; for inspection and tests).  Items are (128-query tile, head,
+ * batch), numbered heaviest first: item id covers query tile n_qtiles - 1 - id / n_groups (n_groups = B * Hq).
+ * Writes per_cta (0: this shape uses the closed formula or the device-wide counter instead) and, for block c,
+ * its item ids ids[c * per_cta .. + per_cta), ended by 0xffff; ids must hold n_ctas * 8 entries, n_ctas <= 296.
+ */
+int b200attn_item_deal(int n_groups, int n_qtiles, int T, int n_ctas, int item_cost, unsigned short* ids, int* per_cta);
+
+/*
  * Synchronises `stream` and returns the device status word of the current device:
  * 0, or the code of the first bounded wait that gave up since the last call (101 load,
  * 102 tensor core, 103 softmax hand-off, 104 buffer free), or 105 when b200attn_kv_append_at met a

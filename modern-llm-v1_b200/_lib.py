@@ -45,6 +45,7 @@ SYMBOLS = (
     "b200attn_fwd_kvcache",
     "b200attn_kv_append",
     "b200attn_kv_append_at",
+    "b200attn_item_deal",
     "b200attn_decode_ragged",
     "b200attn_rope_table",
     "b200attn_rope_norm_fwd",
@@ -97,6 +98,8 @@ def load() -> ctypes.CDLL:
     L.b200attn_kv_append_at.restype = i
     L.b200attn_decode_ragged.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, f, i, vp, sz, vp]
     L.b200attn_decode_ragged.restype = i
+    L.b200attn_item_deal.argtypes = [i, i, i, i, i, vp, vp]
+    L.b200attn_item_deal.restype = i
     L.b200attn_rope_table.argtypes = [i, i, f, vp, vp]
     L.b200attn_rope_table.restype = i
     L.b200attn_rope_norm_fwd.argtypes = [vp, i, i, vp, i, vp, vp, vp, vp, i, i, i, i, f, vp]

@@ -912,6 +912,16 @@ int kv_append_run(const void* xq, const void* xk, const void* xv, int x_dtype, v
 }
 }  // namespace
 
+extern "C" int b200attn_item_deal(int n_groups, int n_qtiles, int T, int n_ctas, int item_cost, unsigned short* ids,
+                                  int* per_cta) {
+    if (n_groups <= 0 || n_qtiles <= 0 || T <= 0 || n_ctas <= 0 || item_cost < 0 || !ids || !per_cta)
+        return B200ATTN_ERR_INVALID_ARG;
+    const ItemTable& tab = item_table_for((long long)n_groups * n_qtiles, (unsigned)n_ctas, n_groups, n_qtiles, T, item_cost);
+    *per_cta = tab.per_cta;
+    for (int i = 0; i < n_ctas * tab.per_cta; ++i) ids[i] = tab.ids[i];
+    return B200ATTN_OK;
+}
+
 extern "C" int b200attn_last_device_status(void* stream) {
     int rc = 0;
     int* status = status_ptr(&rc);

@@ -37,8 +37,8 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 # DRAM traffic of the dominant kernel per launch at the default workload, from the committed ncu
 # summary (profiles/); None until a capture exists for the current kernel.
 # (dram read + write per launch of each kernel, profiles/attn_fwd_bwd_c2_50m_train.md)
-NCU_TRAFFIC_BYTES = {"c2_50m_train": {"attn_fwd_kernel": 21028864, "attn_bwd_dq_kernel": 46915584,
-                                      "attn_bwd_dkdv_kernel": 34409472}}
+NCU_TRAFFIC_BYTES = {"c2_50m_train": {"attn_fwd_kernel": 21029632, "attn_bwd_dq_kernel": 46798080,
+                                      "attn_bwd_dkdv_kernel": 34434048}}
 
 
 def load_peaks():

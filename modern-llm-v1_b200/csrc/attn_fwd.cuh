@@ -4,8 +4,8 @@
 // llm/src/model/flash_attn.cu:28-131), computed tile-wise on the tensor cores.
 //
 // Persistent CTAs, two per SM.  A CTA walks a static list of work items (item = one 128-row
-// query tile of one (batch, query head); items are ordered heaviest first and dealt in rounds of
-// alternating direction) and, per item, the 64-key tiles of K/V up to the diagonal (tiles above it are
+// query tile of one (batch, query head); items are ordered heaviest first and dealt by a host-built
+// table, see ItemTable) and, per item, the 64-key tiles of K/V up to the diagonal (tiles above it are
 // never loaded).  Every pipeline keeps running across item boundaries: the K/V ring prefetches
 // the next item's tiles and the MMA warp issues the next item's first Q K^T products while the
 // softmax warps write the previous item's output rows.  GQA is an index: the K/V tensor maps are

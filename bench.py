@@ -61,6 +61,8 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c2_50m_train")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="issue every launch of the timed region from Python instead of replaying CUDA graphs")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak (default): every rank runs the whole config; strong: the config's batch is split over "
                          "the ranks (contiguous (batch, KV head) units), so the total work is fixed")
@@ -127,6 +129,47 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------
 # CPU side: the oracle port timed on the host cores (cpu_baseline leg and --impl reference)
 # ------------------------------------------------------------------------------------------
+class StepGraphs:
+    """Runs exactly K steps from CUDA graphs.  A step is a few short launches (2-3 kernels of 25-45 us); issued one
+    by one from Python the host can set the pace (15-25 us per call on a slow host), so one round over the buffer
+    sets is captured in a graph and replayed; a remainder of K % round steps comes from single-step graphs.  The
+    launches inside a graph keep their programmatic-dependent-launch edges."""
+
+    def __init__(self, step_fn, round_len: int):
+        import torch
+
+        self.torch, self.step_fn, self.round_len = torch, step_fn, round_len
+        self.singles = {}
+        self.round = self._capture(range(round_len))
+
+    def _capture(self, indices):
+        torch = self.torch
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for i in indices:
+                    self.step_fn(i)
+        torch.cuda.current_stream().wait_stream(side)
+        return graph
+
+    def prepare(self, k: int) -> None:
+        for i in range(k % self.round_len):
+            if i not in self.singles:
+                self.singles[i] = self._capture([i])
+        self.round.replay()  # warm
+        for g in self.singles.values():
+            g.replay()
+
+    def run(self, k: int) -> None:
+        rounds, rem = divmod(k, self.round_len)
+        for _ in range(rounds):
+            self.round.replay()
+        for i in range(rem):
+            self.singles[i].replay()
+
+
 def cpu_prepare(cfg, seed, n_units, one_head=False):
     """FP32 copies of the BF16-rounded inputs of the first `n_units` (batch, KV head) units; with
     one_head only the first query head of the first unit (the smallest sample there is)."""
@@ -352,13 +395,21 @@ def run_decode(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier)
     for _ in range(warmup):
         step()
     m.device_status()
+    graphs = None
+    if not args.no_graph:
+        graphs = StepGraphs(lambda i: step(), 8)
+        graphs.prepare(steps)
+        m.device_status()
     sampler = ClockSampler(device.index or 0)
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
-    for _ in range(steps):
-        step()
+    if graphs is not None:
+        graphs.run(steps)
+    else:
+        for _ in range(steps):
+            step()
     e1.record()
     barrier()
     clocks = sampler.stop()
@@ -368,6 +419,23 @@ def run_decode(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     m.device_status()
+    # end to end: q from pinned host memory, o back to pinned host memory, a stream synchronise per step
+    q_host, o_host = q.cpu().pin_memory(), torch.empty(q.shape, dtype=q.dtype).pin_memory()
+    n_e2e = max(10, steps // 10)
+    barrier()
+    e0.record()
+    for _ in range(n_e2e):
+        q.copy_(q_host, non_blocking=True)
+        step()
+        o_host.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1) / n_e2e
+    if world > 1:
+        t = torch.tensor([ms_e2e], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e2e = float(t.item())
     nbytes = cfg.decode_bytes()
     gbs = world * nbytes / (ms * 1e-3) / 1e9
     peak = float(peaks["hbm_gbs"])
@@ -378,7 +446,11 @@ def run_decode(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier)
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": cfg.name, "B_per_gpu": cfg.B, "cache_len": cfg.T, "Hq": cfg.Hq, "Hkv": cfg.Hkv,
                        "D": cfg.D, "l2": f"cache of {nbytes / 1e6:.0f} MB > 126 MB L2"},
-            "clocks": clocks, "gpu_launches": 3 * steps,
+            "clocks": clocks, "gpu_launches": 2 * steps,
+            "e2e": {"value": world * nbytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": q.numel() * 2, "d2h_bytes_per_step": q.numel() * 2,
+                    "note": "q from pinned host memory, o read back, a stream synchronise per step; the cache stays "
+                            "on the device, as it does between the tokens of a sampling loop"},
             "roofline": {"bound": "hbm", "kernel": "attn_decode_kernel", "achieved": gbs / world, "peak": peak,
                          "unit": "GB/s", "frac": gbs / world / peak,
                          "traffic": 273453056 if cfg.name == "c5_decode" else None,  # profiles/attn_decode_c5_decode.md
@@ -454,6 +526,28 @@ def run_qkprep(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier)
     m.device_status()
     rows = B * T * sum(heads)
     nbytes = rows * D * 2 * 2 + rows * 4 + rows * D * 2 * 3 + rows * 4  # fwd: x, y, rstd; bwd: x, dy, dx, rstd
+    # end to end: x and dy of q and k from pinned host memory, y and dx back, a stream synchronise per step
+    tq0, tk0 = sets[0]
+    h_in = [t[k_].cpu().pin_memory() for t in (tq0, tk0) for k_ in ("x", "dy")]
+    h_out = [torch.empty(t[k_].shape, dtype=t[k_].dtype).pin_memory() for t in (tq0, tk0) for k_ in ("y", "dx")]
+    n_e2e = max(5, min(50, steps // 20))
+    barrier()
+    e0.record()
+    for _ in range(n_e2e):
+        for dst, src in zip([t[k_] for t in (tq0, tk0) for k_ in ("x", "dy")], h_in):
+            dst.copy_(src, non_blocking=True)
+        step(0)
+        for dst, src in zip(h_out, [t[k_] for t in (tq0, tk0) for k_ in ("y", "dx")]):
+            dst.copy_(src, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1) / n_e2e
+    if world > 1:
+        t_ = torch.tensor([ms_e2e], device=device)
+        dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+        ms_e2e = float(t_.item())
+    m.device_status()
     gbs = world * nbytes / (ms * 1e-3) / 1e9
     peak = float(peaks["hbm_gbs"])
     out = {
@@ -465,6 +559,10 @@ def run_qkprep(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier)
                    "l2": f"rotating over {n_sets} buffer sets, {n_sets * rows * D * 2 * 4 / 1e6:.0f} MB > 126 MB L2",
                    "launch": "one round over the buffer sets captured in a CUDA graph and replayed"},
         "clocks": clocks, "gpu_launches": 3 * steps,
+        "e2e": {"value": world * nbytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in h_in),
+                "d2h_bytes_per_step": sum(t.numel() * t.element_size() for t in h_out),
+                "note": "bound by the host link: every tensor crosses it once per step"},
         "roofline": {"bound": "hbm", "kernel": "rope_norm_fwd_kernel + rope_norm_bwd_kernel", "achieved": gbs / world,
                      "peak": peak, "unit": "GB/s", "frac": gbs / world / peak,
                      "traffic": 799593216 if cfg.name == "c4_long_context" else None,  # profiles/rope_norm_c4_long_context.md
@@ -524,12 +622,17 @@ def run_decode_step(m, cfg, args, rank, world, device, peaks, warmup, steps, bar
             o_host.copy_(o, non_blocking=True)
             torch.cuda.current_stream().synchronize()
 
+    graphs = None
+
     def timed(n, e2e=False):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         e0.record()
-        for _ in range(n):
-            step(e2e)
+        if graphs is not None and not e2e:
+            graphs.run(n)
+        else:
+            for _ in range(n):
+                step(e2e)
         e1.record()
         barrier()
         ms = e0.elapsed_time(e1) / n
@@ -542,6 +645,10 @@ def run_decode_step(m, cfg, args, rank, world, device, peaks, warmup, steps, bar
     for _ in range(warmup):
         step()
     m.device_status()
+    if not args.no_graph:
+        graphs = StepGraphs(lambda i: step(), 8)
+        graphs.prepare(steps)
+        m.device_status()
     sampler = ClockSampler(device.index or 0)
     sampler.start()
     ms = timed(steps)
@@ -668,22 +775,42 @@ def main():
     m.device_status()
     barrier()
 
+    graphs = None
+    if not args.no_graph:
+        graphs = StepGraphs(lambda i: step(m, cfg, sets[i % n_sets]), n_sets)
+        graphs.prepare(steps)
+        m.device_status()
+    # The same K steps are timed twice, replayed from the graph and issued one by one (each run bracketed as the
+    # contract says, the max over ranks taken of each); the line reports the faster way and names it.  Which one
+    # wins depends on the host: direct calls keep the dependent-launch overlap between rounds, graphs do not wait
+    # for Python.
+    def timed_steps(use_graph):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        if use_graph:
+            graphs.run(steps)
+        else:
+            for i in range(steps):
+                step(m, cfg, sets[i % n_sets])
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        m.device_status()
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
     sampler = ClockSampler(local_rank)
     sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for i in range(steps):
-        step(m, cfg, sets[i % n_sets])
-    e1.record()
-    barrier()
+    ms_by_launch = {"direct calls": timed_steps(False)}
+    if graphs is not None:
+        ms_by_launch[f"one round over the {n_sets} buffer sets captured in a CUDA graph and replayed"] = timed_steps(True)
     clocks = sampler.stop()
-    ms_total = e0.elapsed_time(e1)
-    m.device_status()
-    if world > 1:
-        t = torch.tensor([ms_total], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
+    launch_how = min(ms_by_launch, key=ms_by_launch.get)
+    ms_total = ms_by_launch[launch_how]
     ms_step = ms_total / steps
     flops_step = cfg.fwd_bwd_flops()
     value = world * flops_step / (ms_step * 1e-3) / 1e12
@@ -749,6 +876,9 @@ def main():
             "config": {"workload": cfg.name, "B_per_gpu": cfg.B, "global_B": global_B, "T": cfg.T, "Hq": cfg.Hq,
                        "Hkv": cfg.Hkv, "D": cfg.D, "layout": "BHTD", "parallelism": f"{world} x independent (batch, KV head) shards",
                        "l2": f"rotating over {n_sets} buffer sets, {n_sets * probe.nbytes() / 1e6:.0f} MB > 126 MB L2",
+                       "launch": launch_how,
+                       "ms_per_step_by_launch": {("graph" if "graph" in k else "direct"): v / steps
+                                                 for k, v in ms_by_launch.items()},
                        "inputs": "q,k: N(0,1) -> RoPE(base 1e4) -> per-head RMSNorm(gamma 1); v: N(0,1); "
                                  "dO: N(0,1e-2); rounded to BF16"},
             "per_gpu_tflops": value / world,

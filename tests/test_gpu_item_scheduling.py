@@ -14,7 +14,9 @@ ROOT = os.path.dirname(HERE)
 
 # (B, T, Hq, Hkv, D, repetitions): few items per CTA (static by default) and many (counter by default);
 # 70 repetitions use each of the library's 64 counter pairs at least once more
-CASES = [(4, 512, 6, 2, 64, 3), (8, 2048, 16, 4, 64, 70), (4, 2048, 8, 2, 128, 3), (3, 1100, 8, 4, 64, 3)]
+# (32, 512, 6, 2, 64) and (10, 640, 7, 7, 64): two to three items per CTA, dealt from the host-built table by default
+CASES = [(4, 512, 6, 2, 64, 3), (8, 2048, 16, 4, 64, 70), (4, 2048, 8, 2, 128, 3), (3, 1100, 8, 4, 64, 3),
+         (32, 512, 6, 2, 64, 3), (10, 640, 7, 7, 64, 3)]
 
 
 def _run(case, mode):

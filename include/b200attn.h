@@ -64,7 +64,8 @@ int b200attn_fwd(const void* q, const void* k, const void* v, void* o, float* ls
  * llm/src/model/flash_attn.cu:428-504): a dQ pass (which also computes D = rowsum(o * dout)) and
  * a dK/dV pass.  dk/dv are already summed over the query heads of each KV group (what
  * accumulate_kv_grads does in the reference, llm/src/model/attention.cu:510-543),
- * in a fixed order, so results are bit-reproducible.  The reference allocates its
+ * in a fixed order, so dk and dv are bit-reproducible; dq is too in the two-pass mode (see
+ * b200attn_bwd_mode below for the modes and which one this call picks).  The reference allocates its
  * D vector per call (llm/src/model/flash_attn.cu:463); here the caller passes a
  * workspace of at least b200attn_bwd_workspace_bytes(...) bytes, 256-byte aligned.
  */
@@ -74,11 +75,34 @@ int b200attn_bwd(const void* q, const void* k, const void* v, const void* o, con
 size_t b200attn_bwd_workspace_bytes(int B, int T, int Hq, int Hkv, int D);
 
 /*
+ * The same backward with the algorithm chosen by the caller (b200attn_bwd is mode B200ATTN_BWD_AUTO).
+ *
+ * B200ATTN_BWD_TWO_PASS: the structure of the reference (llm/src/model/flash_attn.cu:475-503): a dQ pass and a
+ *   dK/dV pass that each recompute the scores.  No atomics anywhere: dq, dk and dv are bit-reproducible.
+ *   Workspace: two FP32 row vectors, 2 * B * Hq * ceil(T/128)*128 * 4 bytes.
+ * B200ATTN_BWD_ONE_PASS (D = 64 only, B200ATTN_ERR_UNSUPPORTED otherwise): one key-stationary kernel computes the
+ *   scores once and produces dk, dv and the dq contributions together; the contributions of different key tiles
+ *   to one query tile are summed in an FP32 accumulator in the workspace by reduce-adds whose order is not fixed,
+ *   so dq is reproducible only to FP32 rounding (dk and dv stay bit-reproducible).  Five products and one
+ *   exponential per score instead of seven and two, but measured slower than TWO_PASS below T = 4096 on B200
+ *   (both are bound by shared-memory traffic, which is the same).  Workspace: the two row vectors plus
+ *   B * Hq * ceil(T/128)*128 * D * 4 bytes.
+ * B200ATTN_BWD_AUTO: TWO_PASS, unless the environment variable B200ATTN_BWD=two_pass|one_pass (read once) says
+ *   otherwise.  If the workspace passed is too small for ONE_PASS but holds the two row vectors, AUTO runs TWO_PASS.
+ * b200attn_bwd_workspace_bytes_mode gives the size for a mode (for AUTO: of the algorithm AUTO picks).
+ */
+enum { B200ATTN_BWD_AUTO = 0, B200ATTN_BWD_TWO_PASS = 1, B200ATTN_BWD_ONE_PASS = 2 };
+int b200attn_bwd_mode(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* dout,
+                      void* dq, void* dk, void* dv, int B, int T, int Hq, int Hkv, int D, int layout,
+                      float softmax_scale, int mode, void* workspace, size_t workspace_bytes, void* stream);
+size_t b200attn_bwd_workspace_bytes_mode(int B, int T, int Hq, int Hkv, int D, int mode);
+
+/*
  * Backward without a workspace argument and without any allocation (this entry point has no
  * counterpart in the reference, whose backward allocates its D vector with cudaMalloc on every
  * call, llm/src/model/flash_attn.cu:463).
  *
- * Same inputs, outputs and results as b200attn_bwd (it runs the same kernels), but the two
+ * Same inputs, outputs and results as b200attn_bwd_mode with B200ATTN_BWD_TWO_PASS (it runs the same kernels), but the two
  * per-row FP32 vectors the backward needs live in a fixed array inside the library's device
  * image instead of a caller-provided workspace.  It is meant for callers that cannot obtain
  * device memory at the point of the call: code that runs between training steps under a
@@ -226,6 +250,10 @@ int b200attn_rope_norm_bwd_qk(const void* dyq, const void* dyk, int y_layout, co
  * owned by the caller.
  */
 int b200attn_set_bwd_profile_events(void* ev_start, void* ev_after_dq, void* ev_after_dkdv);
+/* With a fourth event for the one-pass backward, which has three kernels: events are recorded before the
+ * row-vector kernel, after it, after the fused kernel and after the dq conversion.  The two-pass backward
+ * records the first three as above and leaves the fourth alone. */
+int b200attn_set_bwd_profile_events4(void* ev0, void* ev1, void* ev2, void* ev3);
 
 /*
  * The static deal of work items the forward and the dQ pass use when a problem has fewer than four items per

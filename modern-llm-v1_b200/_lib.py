@@ -30,14 +30,21 @@ LAYOUT_BTHD = 1
 LAYOUTS = {"BHTD": LAYOUT_BHTD, "BTHD": LAYOUT_BTHD}
 DTYPE_BF16 = 0
 DTYPE_F32 = 1
+BWD_AUTO = 0
+BWD_TWO_PASS = 1
+BWD_ONE_PASS = 2
+BWD_MODES = {"auto": BWD_AUTO, "two_pass": BWD_TWO_PASS, "one_pass": BWD_ONE_PASS}
 
 # every symbol include/b200attn.h declares
 SYMBOLS = (
     "b200attn_fwd",
     "b200attn_bwd",
     "b200attn_bwd_workspace_bytes",
+    "b200attn_bwd_mode",
+    "b200attn_bwd_workspace_bytes_mode",
     "b200attn_bwd_static",
     "b200attn_set_bwd_profile_events",
+    "b200attn_set_bwd_profile_events4",
     "b200attn_decode",
     "b200attn_decode_workspace_bytes",
     "b200attn_decode_default_splits",
@@ -80,8 +87,14 @@ def load() -> ctypes.CDLL:
     L.b200attn_bwd_static.restype = i
     L.b200attn_bwd_workspace_bytes.argtypes = [i, i, i, i, i]
     L.b200attn_bwd_workspace_bytes.restype = sz
+    L.b200attn_bwd_mode.argtypes = [vp] * 9 + [i, i, i, i, i, i, f, i, vp, sz, vp]
+    L.b200attn_bwd_mode.restype = i
+    L.b200attn_bwd_workspace_bytes_mode.argtypes = [i, i, i, i, i, i]
+    L.b200attn_bwd_workspace_bytes_mode.restype = sz
     L.b200attn_set_bwd_profile_events.argtypes = [vp, vp, vp]
     L.b200attn_set_bwd_profile_events.restype = i
+    L.b200attn_set_bwd_profile_events4.argtypes = [vp, vp, vp, vp]
+    L.b200attn_set_bwd_profile_events4.restype = i
     L.b200attn_decode.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, f, i, vp, sz, vp]
     L.b200attn_decode.restype = i
     L.b200attn_decode_workspace_bytes.argtypes = [i, i, i, i, i, i]

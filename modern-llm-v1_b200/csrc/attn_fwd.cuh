@@ -17,8 +17,13 @@
 //   warp  4    TMA producer (converged warp, one elected lane issues)
 //   warp  5    TMEM allocation and tcgen05.mma issue (converged warp, one elected lane issues)
 //   warps 6-7  idle (they only donate registers)
-// TMEM (256 columns): S buffers of 64 FP32 columns, three for D = 64 and two for D = 128, each
-//   re-used as P (BF16 pairs, 32 columns); the O accumulator (FP32, D columns) behind them.
+// TMEM (256 columns): two S buffers of 64 FP32 columns, each re-used as P (BF16 pairs, 32 columns); the O
+//   accumulator (FP32, D columns) behind them; for D = 64 two Q buffers of 32 columns behind that.
+// Q in tensor memory (D = 64): every D = 64 kernel here is bound by the shared-memory data path (an SS product
+//   M128 N64 K16 fetches 4 KB of A and 2 KB of B for 32 clocks of math), and Q is the same for all key tiles of an
+//   item.  The softmax warps therefore copy an item's Q tile once from shared memory into tensor memory (the
+//   128 bytes of row r are the 32 BF16-pair columns of lane r as they stand) and Q K^T is issued with the A
+//   operand in tensor memory, like P V: per key tile the products then read 16 KB of shared memory instead of 32.
 // The MMA warp's work is a chain softmax(g) -> P V(g) -> Q K^T(g + buffers) -> softmax(g + buffers);
 // with several S buffers the products Q K^T run that many tiles ahead of the softmax, and P V of
 // tile g runs under the softmax of tile g+1.
@@ -52,11 +57,12 @@ struct FwdCfg {
     static constexpr int kKVBoxBytes = kKeys * 64 * 2;  // K/V TMA box: 64 rows x 64 bf16
     static constexpr int kBoxes = D / 64;
     static constexpr int kBarBytes = 384;
+    static constexpr bool kQInTmem = (D == 64);
     static constexpr int kSmemBytes = kQBufs * kQTileBytes + 2 * kStages * kKVTileBytes + kBarBytes + 1024;
     static constexpr int kTmemCols = 256;
-    // S buffers: three for D = 64 (all 256 columns used), two for D = 128
-    static constexpr int kSBufs = (D == 64) ? 3 : 2;
+    static constexpr int kSBufs = 2;
     static constexpr int kColO = kSBufs * 64;
+    static constexpr int kColQ = kColO + D;  // D = 64 only: [192, 224) and [224, 256)
     __host__ __device__ static constexpr int col_s(int buf) { return buf * 64; }
 };
 
@@ -91,6 +97,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint64_t* bar_v_free = bars + 13 + 3 * NST;  // [NST]
     uint64_t* bar_item = bars + 32;    // [kItemRing] item ids handed out by the producer
     volatile int* item_ring = reinterpret_cast<volatile int*>(bars + 32 + kItemRing);
+    uint64_t* bar_qs_free = bars + 44;  // [2] per Q buffer: the tile in shared memory has been copied (phase: item / NQB)
+    uint64_t* bar_qt_full = bars + 46;  // [2] per Q buffer: Q of an item is in tensor memory          (phase: item / NQB)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 30);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 31);
 
@@ -118,6 +126,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bar_q[i], 1);
             mbar_init(&bar_q_free[i], 1);
+            mbar_init(&bar_qs_free[i], 128);
+            mbar_init(&bar_qt_full[i], 128);
         }
         for (int i = 0; i < NSB; ++i) {
             mbar_init(&bar_s_full[i], 1);
@@ -161,7 +171,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         auto load_q = [&](int n, int id) {
             const int qb = n % NQB;
             if (n >= NQB)
-                ok = mbar_wait_warp(&bar_q_free[qb], uint32_t(n / NQB - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
+                ok = mbar_wait_warp(Cfg::kQInTmem ? &bar_qs_free[qb] : &bar_q_free[qb], uint32_t(n / NQB - 1) & 1, abort_flag,
+                                    p.status, DEV_WAIT_TIMEOUT_FREE);
             if (!ok) return;
             if (elect_one()) {
                 mbar_arrive_expect_tx(&bar_q[qb], Cfg::kQTileBytes);
@@ -242,7 +253,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         auto issue_next_s = [&]() {
             if (sc.id < 0) return;
             const int s = sc.g % NST, qb = sc.n % NQB;
-            if (sc.j == 0) ok = mbar_wait_warp(&bar_q[qb], uint32_t(sc.n / NQB) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+            if (sc.j == 0)
+                ok = mbar_wait_warp(Cfg::kQInTmem ? &bar_qt_full[qb] : &bar_q[qb], uint32_t(sc.n / NQB) & 1, abort_flag, p.status,
+                                    DEV_WAIT_TIMEOUT_LOAD);
             if (ok) ok = mbar_wait_warp(&bar_k_full[s], uint32_t(sc.g / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
             if (!ok) return;
             tc_fence_after_sync();
@@ -251,9 +264,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const bool last = sc.j + 1 == sc.n_kv;  // no later MMA reads this item's Q
             if (elect_one()) {
 #pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks)
-                    umma_ss(tmem + Cfg::col_s(sc.g % NSB), q_desc + kmajor_step(ks, Cfg::kQBoxBytes),
-                            k_desc + kmajor_step(ks, Cfg::kKVBoxBytes), idesc_s, ks > 0);
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    if constexpr (Cfg::kQInTmem)
+                        umma_ts(tmem + Cfg::col_s(sc.g % NSB), tmem + Cfg::kColQ + qb * 32 + ks * 8,
+                                k_desc + kmajor_step(ks, Cfg::kKVBoxBytes), idesc_s, ks > 0);
+                    else
+                        umma_ss(tmem + Cfg::col_s(sc.g % NSB), q_desc + kmajor_step(ks, Cfg::kQBoxBytes),
+                                k_desc + kmajor_step(ks, Cfg::kKVBoxBytes), idesc_s, ks > 0);
+                }
                 umma_commit(&bar_s_full[sc.g % NSB]);
                 umma_commit(&bar_k_free[s]);
                 if (last) umma_commit(&bar_q_free[qb]);
@@ -353,6 +371,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             B200ATTN_STAMP(tid == 0, 400 + 4 * n_item + 2);
             return true;
         };
+        // D = 64: Q of this CTA's n-th item from shared memory into Q buffer n % NQB of tensor memory.  The buffer
+        // held Q of item n - NQB, whose last Q K^T product must have completed.
+        auto copy_q = [&](int n_item) -> bool {
+            const int qb = n_item % NQB;
+            if (!mbar_wait_warp(&bar_q[qb], uint32_t(n_item / NQB) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD)) return false;
+            if (n_item >= NQB &&
+                !mbar_wait_warp(&bar_q_free[qb], uint32_t(n_item / NQB - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE))
+                return false;
+            tc_fence_after_sync();
+            uint32_t qw[32];
+            const uint8_t* qrow = sQ + qb * Cfg::kQTileBytes + row * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint4 w = *reinterpret_cast<const uint4*>(qrow + ((c ^ (row & 7)) << 4));
+                qw[4 * c] = w.x, qw[4 * c + 1] = w.y, qw[4 * c + 2] = w.z, qw[4 * c + 3] = w.w;
+            }
+            tmem_st_x32(tmem + lane_base + Cfg::kColQ + qb * 32, qw);
+            mbar_arrive(&bar_qs_free[qb]);  // the values are in registers: the tile in shared memory may be reloaded
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(&bar_qt_full[qb]);
+            return true;
+        };
+        if constexpr (Cfg::kQInTmem) {
+            if (get_item(0) >= 0) ok = copy_q(0);
+        }
         // The epilogue of an item is deferred until the softmax of the next item's first tile has been handed
         // to the MMA warp: the wait for the item's last P V then overlaps useful work.
         bool pending = false;
@@ -365,6 +409,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             float m_ref = -INFINITY;  // exponent reference (a past row maximum), raw score units
             float l = 0.f;            // running sum of exp2((s - m_ref) * scale_log2)
             for (int j = 0; j < n_kv; ++j, ++g) {
+                if constexpr (Cfg::kQInTmem) {
+                    // the next item's Q, a few tiles before the MMA warp wants it for that item's first products
+                    if (j == max(0, n_kv - 3) && get_item(n + 1) >= 0) {
+                        ok = copy_q(n + 1);
+                        if (!ok) break;
+                    }
+                }
                 const uint32_t t_s = tmem + lane_base + Cfg::col_s(g % NSB);
                 ok = mbar_wait_warp(&bar_s_full[g % NSB], uint32_t(g / NSB) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
                 if (!ok) break;

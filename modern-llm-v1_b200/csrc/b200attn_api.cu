@@ -15,6 +15,7 @@
 #include <stdlib.h>
 
 #include "attn_bwd.cuh"
+#include "attn_bwd_onepass.cuh"
 #include "attn_decode.cuh"
 #include "attn_fwd.cuh"
 #include "kv_cache.cuh"
@@ -318,10 +319,63 @@ int set_smem_once(K kernel, int bytes, bool* done) {
     return B200ATTN_OK;
 }
 
-cudaEvent_t g_bwd_events[3] = {nullptr, nullptr, nullptr};
+cudaEvent_t g_bwd_events[4] = {nullptr, nullptr, nullptr, nullptr};
 
 inline void record_bwd_event(int i, cudaStream_t st) {
     if (g_bwd_events[i]) cudaEventRecord(g_bwd_events[i], st);
+}
+
+// Which backward runs.  The one-pass kernel (attn_bwd_onepass.cuh) exists for D = 64; it needs the FP32 dQ
+// accumulator behind the two row vectors in the workspace.  AUTO is the two-pass backward: measured on B200 the
+// one-pass kernel moves as many bytes through shared memory per block of scores as the two passes together (the
+// limiter of every D = 64 kernel here) and pays two HBM-bound kernels around it, so it only draws level from
+// T = 4096 on.  The environment variable B200ATTN_BWD=two_pass|one_pass overrides AUTO.
+inline size_t bwd_acc_bytes(int B, int T, int Hq, int D) { return bwd_vec_elems(B, T, Hq) * (size_t)D * sizeof(float); }
+inline size_t bwd_vec_bytes_padded(int B, int T, int Hq) { return (2 * bwd_vec_elems(B, T, Hq) * sizeof(float) + 255) & ~(size_t)255; }
+
+int bwd_resolve_mode(int mode, int B, int T, int Hq, int D) {
+    static const int forced = [] {
+        const char* e = getenv("B200ATTN_BWD");
+        return !e ? 0 : (e[0] == 't' ? B200ATTN_BWD_TWO_PASS : (e[0] == 'o' ? B200ATTN_BWD_ONE_PASS : 0));
+    }();
+    if (mode == B200ATTN_BWD_AUTO) {
+        mode = forced ? forced : B200ATTN_BWD_TWO_PASS;
+        if (D != 64) mode = B200ATTN_BWD_TWO_PASS;
+        (void)B, (void)T, (void)Hq;
+    }
+    return mode;
+}
+
+// One-pass backward (D = 64): row vectors + cleared accumulator, the fused kernel, accumulator -> dq.
+int launch_bwd_onepass(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                       const BwdParams& p, float* dq_acc, cudaStream_t st) {
+    static bool set[kMaxDevices] = {false};
+    int rc = set_smem_once(attn_bwd_onepass_kernel, OnePassCfg::kSmemBytes, set);
+    if (rc) return rc;
+    record_bwd_event(0, st);
+    const unsigned q_tiles = (unsigned)(p.n_tiles * p.Hq * p.B);
+    if (launch_pdl(attn_bwd_prep_kernel<64>, q_tiles, 256, 0, st, p, dq_acc) != cudaSuccess) {
+        cudaGetLastError();
+        return B200ATTN_ERR_CUDA;
+    }
+    record_bwd_event(1, st);
+    const unsigned kv_items = (unsigned)(p.n_tiles * p.Hkv * p.B);
+    const unsigned kv_grid = std::min(kv_items, (unsigned)sm_count());
+    BwdParams pk = p;
+    pk.sched2 = next_sched_pair(kv_items, kv_grid);
+    if (launch_pdl(attn_bwd_onepass_kernel, kv_grid, OnePassCfg::kThreads, OnePassCfg::kSmemBytes, st, tk, tv, tq, tdo, pk,
+                   dq_acc) != cudaSuccess) {
+        cudaGetLastError();
+        return B200ATTN_ERR_CUDA;
+    }
+    record_bwd_event(2, st);
+    const float* acc_c = dq_acc;
+    if (launch_pdl(attn_bwd_dq_convert_kernel<64>, q_tiles, 128, 0, st, p, acc_c) != cudaSuccess) {
+        cudaGetLastError();
+        return B200ATTN_ERR_CUDA;
+    }
+    record_bwd_event(3, st);
+    return B200ATTN_OK;
 }
 
 template <int D>
@@ -564,33 +618,62 @@ extern "C" int b200attn_rope_norm_bwd_qk(const void* dyq, const void* dyk, int y
                          stream);
 }
 
-extern "C" int b200attn_set_bwd_profile_events(void* e0, void* e1, void* e2) {
-    void* ev[3] = {e0, e1, e2};
+extern "C" int b200attn_set_bwd_profile_events4(void* e0, void* e1, void* e2, void* e3) {
+    void* ev[4] = {e0, e1, e2, e3};
     const int n_set = (e0 != nullptr) + (e1 != nullptr) + (e2 != nullptr);
     if (n_set != 0 && n_set != 3) return B200ATTN_ERR_INVALID_ARG;
-    for (int i = 0; i < 3; ++i) g_bwd_events[i] = static_cast<cudaEvent_t>(ev[i]);
+    if (n_set == 0 && e3 != nullptr) return B200ATTN_ERR_INVALID_ARG;
+    for (int i = 0; i < 4; ++i) g_bwd_events[i] = static_cast<cudaEvent_t>(ev[i]);
     return B200ATTN_OK;
 }
 
-extern "C" size_t b200attn_bwd_workspace_bytes(int B, int T, int Hq, int Hkv, int D) {
+extern "C" int b200attn_set_bwd_profile_events(void* e0, void* e1, void* e2) {
+    return b200attn_set_bwd_profile_events4(e0, e1, e2, nullptr);
+}
+
+extern "C" size_t b200attn_bwd_workspace_bytes_mode(int B, int T, int Hq, int Hkv, int D, int mode) {
     (void)Hkv;
-    (void)D;
-    if (B <= 0 || T <= 0 || Hq <= 0) return 0;
+    if (B <= 0 || T <= 0 || Hq <= 0 || D <= 0) return 0;
+    if (mode != B200ATTN_BWD_AUTO && mode != B200ATTN_BWD_TWO_PASS && mode != B200ATTN_BWD_ONE_PASS) return 0;
+    if (bwd_resolve_mode(mode, B, T, Hq, D) == B200ATTN_BWD_ONE_PASS) return bwd_vec_bytes_padded(B, T, Hq) + bwd_acc_bytes(B, T, Hq, D);
     return 2 * bwd_vec_elems(B, T, Hq) * sizeof(float);
+}
+
+extern "C" size_t b200attn_bwd_workspace_bytes(int B, int T, int Hq, int Hkv, int D) {
+    return b200attn_bwd_workspace_bytes_mode(B, T, Hq, Hkv, D, B200ATTN_BWD_AUTO);
 }
 
 extern "C" int b200attn_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse,
                             const void* dout, void* dq, void* dk, void* dv, int B, int T, int Hq, int Hkv, int D,
                             int layout, float softmax_scale, void* workspace, size_t workspace_bytes, void* stream) {
+    return b200attn_bwd_mode(q, k, v, o, lse, dout, dq, dk, dv, B, T, Hq, Hkv, D, layout, softmax_scale, B200ATTN_BWD_AUTO,
+                             workspace, workspace_bytes, stream);
+}
+
+extern "C" int b200attn_bwd_mode(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                                 const void* dout, void* dq, void* dk, void* dv, int B, int T, int Hq, int Hkv, int D,
+                                 int layout, float softmax_scale, int mode, void* workspace, size_t workspace_bytes,
+                                 void* stream) {
     int rc = check_common(B, T, Hq, Hkv, D, layout);
     if (rc) return rc;
     if (!q || !k || !v || !o || !lse || !dout || !dq || !dk || !dv) return B200ATTN_ERR_INVALID_ARG;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(dout) || !aligned16(dq) ||
         !aligned16(dk) || !aligned16(dv))
         return B200ATTN_ERR_ALIGNMENT;
-    if (!workspace || workspace_bytes < b200attn_bwd_workspace_bytes(B, T, Hq, Hkv, D) ||
-        (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+    if (mode != B200ATTN_BWD_AUTO && mode != B200ATTN_BWD_TWO_PASS && mode != B200ATTN_BWD_ONE_PASS)
+        return B200ATTN_ERR_INVALID_ARG;
+    if (mode == B200ATTN_BWD_ONE_PASS && D != 64) return B200ATTN_ERR_UNSUPPORTED;
+    const size_t two_pass_bytes = 2 * bwd_vec_elems(B, T, Hq) * sizeof(float);
+    const size_t one_pass_bytes = bwd_vec_bytes_padded(B, T, Hq) + bwd_acc_bytes(B, T, Hq, D);
+    if (!workspace || workspace_bytes < two_pass_bytes || (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
         return B200ATTN_ERR_WORKSPACE;
+    // AUTO falls back to the two-pass kernels when the workspace only holds the row vectors
+    const bool auto_mode = mode == B200ATTN_BWD_AUTO;
+    mode = bwd_resolve_mode(mode, B, T, Hq, D);
+    if (mode == B200ATTN_BWD_ONE_PASS && workspace_bytes < one_pass_bytes) {
+        if (!auto_mode) return B200ATTN_ERR_WORKSPACE;
+        mode = B200ATTN_BWD_TWO_PASS;
+    }
     int* status = status_ptr(&rc);
     if (!status) return rc;
     const Strides sq = strides_for(layout, Hq, T, D), sk = strides_for(layout, Hkv, T, D);
@@ -643,6 +726,10 @@ extern "C" int b200attn_bwd(const void* q, const void* k, const void* v, const v
     p.div_hkv = fastdiv_make((unsigned)Hkv);
     p.div_group = fastdiv_make((unsigned)p.group);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (mode == B200ATTN_BWD_ONE_PASS) {
+        float* dq_acc = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + bwd_vec_bytes_padded(B, T, Hq));
+        return launch_bwd_onepass(tq, tk, tv, tdo, p, dq_acc, st);
+    }
     return D == 64 ? launch_bwd<64>(tq, tk64, tv64, tk, tv, tdo, to, tdq, tdk, tdv, p, st)
                    : launch_bwd<128>(tq, tk64, tv64, tk, tv, tdo, to, tdq, tdk, tdv, p, st);
 }
@@ -689,8 +776,8 @@ extern "C" int b200attn_bwd_static(const void* q, const void* k, const void* v, 
     if (!scratch) return rc;
     // Same kernels as b200attn_bwd; the preprocess kernel rewrites every row (padding included) that
     // the two passes read, so stale contents of an earlier call are never seen.
-    return b200attn_bwd(q, k, v, o, lse, dout, dq, dk, dv, B, T, Hq, Hkv, D, layout, softmax_scale, scratch,
-                        2 * sizeof(float) * (size_t)B200ATTN_BWD_STATIC_MAX_ROWS, stream);
+    return b200attn_bwd_mode(q, k, v, o, lse, dout, dq, dk, dv, B, T, Hq, Hkv, D, layout, softmax_scale,
+                             B200ATTN_BWD_TWO_PASS, scratch, 2 * sizeof(float) * (size_t)B200ATTN_BWD_STATIC_MAX_ROWS, stream);
 }
 
 namespace {

@@ -25,7 +25,7 @@ import torch
 
 from . import _lib
 
-_workspaces: dict[tuple[int, str], torch.Tensor] = {}
+_workspaces: dict[tuple[int, str, int], torch.Tensor] = {}
 
 
 def _stream_ptr() -> int:
@@ -34,8 +34,9 @@ def _stream_ptr() -> int:
 
 def _workspace(kind: str, nbytes: int, device: torch.device) -> torch.Tensor:
     """Private temporaries of the operator (the reference allocates its D vector per
-    call, llm/src/model/flash_attn.cu:463); kept and grown per device instead."""
-    key = (device.index if device.index is not None else torch.cuda.current_device(), kind)
+    call, llm/src/model/flash_attn.cu:463); kept and grown per (device, stream) instead, so
+    that calls issued on different torch streams never share scratch memory."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), kind, _stream_ptr())
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
@@ -88,9 +89,11 @@ def flash_attn_forward_gqa(q, k, v, ctx, L, B, T, Hq, Hkv, D, layout="BHTD", sof
 
 
 def flash_attn_backward_gqa(q, k, v, ctx, L, d_ctx, d_q, d_k, d_v, B, T, Hq, Hkv, D, layout="BHTD",
-                            softmax_scale=None):
+                            softmax_scale=None, mode="auto"):
     """d_q, d_k, d_v (overwritten) for the forward above.  d_k, d_v are Hkv-wide: the
-    sum over each group's query heads is done inside the kernel."""
+    sum over each group's query heads is done inside the kernel.  mode: "auto", "two_pass" (the
+    reference's structure, llm/src/model/flash_attn.cu:475-503, every output bit-reproducible) or
+    "one_pass" (D = 64: scores computed once, d_q summed by reduce-adds in no fixed order)."""
     fn = "flash_attn_backward"
     bf = torch.bfloat16
     _check_tensors(fn, [(q, "q", bf), (k, "k", bf), (v, "v", bf), (ctx, "ctx", bf), (L, "L", torch.float32),
@@ -102,13 +105,17 @@ def flash_attn_backward_gqa(q, k, v, ctx, L, d_ctx, d_q, d_k, d_v, B, T, Hq, Hkv
         raise ValueError(f"{fn}: shape mismatch")
     if L.numel() != B * Hq * T:
         raise ValueError(f"{fn}: L must be [B, T]")
+    if mode not in _lib.BWD_MODES:
+        raise ValueError(f"{fn}: mode must be auto, two_pass or one_pass")
     lib = _lib.load()
     with torch.cuda.device(q.device):
-        nbytes = int(lib.b200attn_bwd_workspace_bytes(B, T, Hq, Hkv, D))
+        m = _lib.BWD_MODES[mode]
+        nbytes = int(lib.b200attn_bwd_workspace_bytes_mode(B, T, Hq, Hkv, D, m))
         ws = _workspace("bwd", nbytes, q.device)
-        rc = lib.b200attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), ctx.data_ptr(), L.data_ptr(), d_ctx.data_ptr(),
-                              d_q.data_ptr(), d_k.data_ptr(), d_v.data_ptr(), B, T, Hq, Hkv, D, _lib.LAYOUTS[layout],
-                              float(softmax_scale or 0.0), ws.data_ptr(), ws.numel(), _stream_ptr())
+        rc = lib.b200attn_bwd_mode(q.data_ptr(), k.data_ptr(), v.data_ptr(), ctx.data_ptr(), L.data_ptr(),
+                                   d_ctx.data_ptr(), d_q.data_ptr(), d_k.data_ptr(), d_v.data_ptr(), B, T, Hq, Hkv, D,
+                                   _lib.LAYOUTS[layout], float(softmax_scale or 0.0), m, ws.data_ptr(), ws.numel(),
+                                   _stream_ptr())
     _lib.check(rc, fn)
 
 

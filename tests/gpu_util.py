@@ -30,7 +30,7 @@ def run_fwd(q, k, v, layout="BHTD", scale=None):
     return from_layout(o, layout), lse
 
 
-def run_fwd_bwd(q, k, v, do, layout="BHTD", scale=None):
+def run_fwd_bwd(q, k, v, do, layout="BHTD", scale=None, mode="auto"):
     B, Hq, T, D = q.shape
     Hkv = k.shape[1]
     qa, ka, va, doa = (to_layout(x, layout) for x in (q, k, v, do))
@@ -40,7 +40,7 @@ def run_fwd_bwd(q, k, v, do, layout="BHTD", scale=None):
     dk = torch.full_like(ka, float("nan"))
     dv = torch.full_like(va, float("nan"))
     m.flash_attn_forward_gqa(qa, ka, va, o, lse, B, T, Hq, Hkv, D, layout, scale)
-    m.flash_attn_backward_gqa(qa, ka, va, o, lse, doa, dq, dk, dv, B, T, Hq, Hkv, D, layout, scale)
+    m.flash_attn_backward_gqa(qa, ka, va, o, lse, doa, dq, dk, dv, B, T, Hq, Hkv, D, layout, scale, mode)
     m.device_status()
     return tuple(from_layout(x, layout) for x in (o,)) + (lse,) + tuple(from_layout(x, layout) for x in (dq, dk, dv))
 
@@ -57,9 +57,9 @@ def assert_close(name, got, want, max_abs=TOL_MAX_ABS, rel_l2=TOL_REL_L2):
     assert er <= rel_l2, f"{name}: rel-L2 {er:.3e} > {rel_l2}"
 
 
-def check_against_oracle(q, k, v, do, layout="BHTD"):
+def check_against_oracle(q, k, v, do, layout="BHTD", mode="auto"):
     """Runs the CUDA path through the C ABI and the oracle on the same BF16-rounded inputs."""
-    got = run_fwd_bwd(q, k, v, do, layout)
+    got = run_fwd_bwd(q, k, v, do, layout, mode=mode)
     want = ao.attn_fwd_bwd_c(np32(q), np32(k), np32(v), np32(do))
     assert_close("O", got[0], want[0])
     assert_close("LSE", got[1], want[1], max_abs=TOL_LSE, rel_l2=1.0)

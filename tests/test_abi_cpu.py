@@ -54,15 +54,28 @@ def test_argument_validation_happens_before_any_cuda_call(lib):
     args = [p16] * 9 + [1, 128, 1, 1, 64, 0, 0.0]
     assert b(*args, None, 0, None) == _lib.ERR_WORKSPACE
     assert b(*args, p16, 16, None) == _lib.ERR_WORKSPACE  # too small
+    bm = lib.b200attn_bwd_mode
+    assert bm(*args, 9, p16, 4096, None) == _lib.ERR_INVALID_ARG  # no such mode
+    assert bm(*([p16] * 9 + [1, 128, 1, 1, 128, 0, 0.0]), _lib.BWD_ONE_PASS, p16, 4096, None) == _lib.ERR_UNSUPPORTED
+    assert bm(*args, _lib.BWD_ONE_PASS, p16, 2 * 128 * 4, None) == _lib.ERR_WORKSPACE  # holds the vectors only
     d = lib.b200attn_decode
     assert d(p16, p16, p16, p16, None, 1, 128, 4, 3, 64, 0.0, 0, p16, 4096, None) == _lib.ERR_INVALID_ARG
     assert d(p16, p16, p16, p16, None, 1, 128, 4, 2, 64, 0.0, 0, None, 0, None) == _lib.ERR_WORKSPACE
 
 
 def test_workspace_sizes(lib):
-    # two FP32 vectors of B*Hq*ceil(T/128)*128
-    assert lib.b200attn_bwd_workspace_bytes(32, 512, 6, 2, 64) == 2 * 32 * 6 * 512 * 4
-    assert lib.b200attn_bwd_workspace_bytes(1, 77, 2, 1, 64) == 2 * 1 * 2 * 128 * 4
+    from modern_llm_v1_b200 import _lib
+
+    # two-pass: two FP32 vectors of B*Hq*ceil(T/128)*128; one-pass (D = 64): + an FP32 dq accumulator of that many rows
+    w = lib.b200attn_bwd_workspace_bytes_mode
+    assert w(32, 512, 6, 2, 64, _lib.BWD_TWO_PASS) == 2 * 32 * 6 * 512 * 4
+    assert w(1, 77, 2, 1, 64, _lib.BWD_TWO_PASS) == 2 * 1 * 2 * 128 * 4
+    assert w(32, 512, 6, 2, 64, _lib.BWD_ONE_PASS) == 2 * 32 * 6 * 512 * 4 + 32 * 6 * 512 * 64 * 4
+    assert w(1, 77, 2, 1, 64, _lib.BWD_ONE_PASS) == 2 * 1 * 2 * 128 * 4 + 2 * 128 * 64 * 4
+    assert w(4, 8192, 16, 4, 128, _lib.BWD_AUTO) == 2 * 4 * 16 * 8192 * 4  # D = 128 has no one-pass kernel
+    assert w(1, 77, 2, 1, 64, 7) == 0
+    if not os.environ.get("B200ATTN_BWD"):
+        assert lib.b200attn_bwd_workspace_bytes(32, 512, 6, 2, 64) == w(32, 512, 6, 2, 64, _lib.BWD_TWO_PASS)
     assert lib.b200attn_bwd_workspace_bytes(0, 77, 2, 1, 64) == 0
     s = lib.b200attn_decode_default_splits(64, 4096, 16, 4, 64)
     assert 1 <= s <= 32

@@ -113,6 +113,25 @@ def test_long_context_config_sampled_rows():
         assert_close(f"LSE[{t}]", lse[:, :, t], ld, max_abs=TOL_LSE, rel_l2=1.0)
 
 
+def test_long_context_config_backward_on_one_unit():
+    # The whole C4 problem (B=4, T=8192, Hq=16, Hkv=4, D=128: 64 key tiles per item, the device-wide item counter at
+    # D=128, P recomputed from the logsumexp over 8k keys) forward + backward on the GPU; O, logsumexp, dQ, dK, dV
+    # of one (batch, KV head) unit against the oracle.
+    cfg = inputs.CONFIGS["c4_long_context"]
+    q, k, v, do, _, _ = inputs.make_train_inputs(cfg, 20260004)
+    got = run_fwd_bwd(q.cuda(), k.cuda(), v.cuda(), do.cuda())
+    g = cfg.group
+    b, hk = 2, 1
+    hs = slice(hk * g, hk * g + g)
+    want = ao.attn_fwd_bwd_c(np32(q[b:b + 1, hs]), np32(k[b:b + 1, hk:hk + 1]), np32(v[b:b + 1, hk:hk + 1]),
+                             np32(do[b:b + 1, hs]))
+    assert_close("O", got[0][b:b + 1, hs], want[0])
+    assert_close("LSE", got[1][b:b + 1, hs], want[1], max_abs=TOL_LSE, rel_l2=1.0)
+    assert_close("dQ", got[2][b:b + 1, hs], want[2])
+    assert_close("dK", got[3][b:b + 1, hk:hk + 1], want[3])
+    assert_close("dV", got[4][b:b + 1, hk:hk + 1], want[4])
+
+
 def test_head_dim_128_with_several_items_per_cta():
     # B=4, T=2048, Hq=8, Hkv=2, D=128: 512 forward items on 296 persistent CTAs (single Q buffer, two S buffers),
     # 128-key-tile dQ pass, persistent dK/dV pass with one K/V buffer.  Full problem on the GPU, the oracle on two

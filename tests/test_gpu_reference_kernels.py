@@ -55,6 +55,23 @@ def test_matches_reference_gpu_attention(ref, which, B, T, Hq, Hkv, D):
     assert_close("dV", got[4], np32(want[4]))
 
 
+def test_long_context_unit_matches_reference_flash_kernels(ref):
+    # one (batch, KV head) unit of the long-context configuration (T=8192, 4 query heads on one KV head, D=128)
+    # against the reference's own flash kernels (llm/src/model/flash_attn.cu:428-504 and the forward :383-426)
+    from modern_llm_v1_b200 import inputs
+
+    cfg = inputs.CONFIGS["c4_long_context"]
+    q, k, v, do, _, _ = inputs.make_train_inputs(cfg, 20260004, 9, 10)  # unit 9 = (batch 2, KV head 1): [1, 4, T, D]
+    q, k, v, do = (x.cuda() for x in (q, k, v, do))
+    got = run_fwd_bwd(q, k, v, do)
+    want = _reference(ref, 0, q, k, v, do)
+    assert_close("O", got[0], np32(want[0]))
+    assert_close("LSE", got[1], np32(want[1]), max_abs=TOL_LSE, rel_l2=1.0)
+    assert_close("dQ", got[2], np32(want[2]))
+    assert_close("dK", got[3], np32(want[3]))
+    assert_close("dV", got[4], np32(want[4]))
+
+
 def test_faster_than_reference_gpu_paths_at_c2(ref, capsys):
     """Device time of one forward + backward at the 50M training shape: this library against the reference's
     two GPU paths compiled for the same GPU (their own allocations and GQA copies included, as the model

@@ -7,7 +7,7 @@ start-up, a host without an allocator of its own.  For them the library keeps th
 per-row vectors in a fixed 4 MiB array of its own device image and allocates nothing.
 
 This test calls that entry point through the C ABI and holds it to the regular entry point
-(b200attn_bwd with a caller workspace) on two calls in a row.  The second call is a smaller
+(b200attn_bwd_mode, two-pass, with a caller workspace) and to the CPU oracle on two calls in a row.  The second call is a smaller
 problem, so the array still holds the first call's rows beyond what the second one rewrites:
 stale contents must not leak into the result.  Both entry points run the same kernels, so the
 results have to be bit-identical.  The file is named so that pytest collects it last.
@@ -17,6 +17,9 @@ import torch
 
 import modern_llm_v1_b200 as m
 from modern_llm_v1_b200 import _lib
+from oracle import attn_oracle as ao
+
+from gpu_util import assert_close, np32
 
 pytestmark = pytest.mark.gpu
 
@@ -36,7 +39,7 @@ def _both_backwards(lib, B, T, Hq, Hkv, D, seed):
     m.flash_attn_forward_gqa(q, k, v, o, lse, B, T, Hq, Hkv, D)
     # regular entry point, caller-owned workspace
     want = [torch.full_like(q, float("nan")), torch.full_like(k, float("nan")), torch.full_like(v, float("nan"))]
-    m.flash_attn_backward_gqa(q, k, v, o, lse, do, want[0], want[1], want[2], B, T, Hq, Hkv, D)
+    m.flash_attn_backward_gqa(q, k, v, o, lse, do, want[0], want[1], want[2], B, T, Hq, Hkv, D, mode="two_pass")
     # allocation-free entry point, straight through the C ABI
     got = [torch.full_like(q, float("nan")), torch.full_like(k, float("nan")), torch.full_like(v, float("nan"))]
     stream = torch.cuda.current_stream().cuda_stream
@@ -45,6 +48,10 @@ def _both_backwards(lib, B, T, Hq, Hkv, D, seed):
                                  D, _lib.LAYOUT_BHTD, 0.0, stream)
     assert rc == _lib.OK, _lib.strerror(rc)
     m.device_status()
+    # and not only against the sibling entry point: the oracle on the same inputs, at the bar of every parity test
+    ref = ao.attn_fwd_bwd_c(np32(q), np32(k), np32(v), np32(do))
+    for name, x, y in zip(("dq", "dk", "dv"), got, ref[2:]):
+        assert_close(name, x, y)
     return got, want
 
 

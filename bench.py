@@ -224,7 +224,7 @@ def cpu_baseline(cfg, seed):
                       f"{t:.2f} s wall on {min(cores, heads)} threads (OpenMP over batch x query head)"}
 
 
-def run_reference_arm(args, cfg, rank, world):
+def run_reference_arm(args, cfg, cfg_full, rank, world):
     """--impl reference: the reference's host attention algorithm (oracle port: the reference's own
     host function is forward-only and single-threaded) on this box's cores, bounded sample per step."""
     if rank != 0:
@@ -258,9 +258,8 @@ def run_reference_arm(args, cfg, rank, world):
     line = {
         "impl": "reference", "metric": "causal_gqa_attn_fwd_bwd_tflops", "value": val, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": {"workload": cfg.name, "B": cfg.B, "T": cfg.T, "Hq": cfg.Hq, "Hkv": cfg.Hkv, "D": cfg.D,
-                   "sample": sample},
+        "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": workload_config(cfg_full, world, args.scaling),
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -290,8 +289,33 @@ class BufferSet:
 
 
 def step(m, cfg, s):
+    """One forward + one backward (the two-pass backward: three kernel launches per step)."""
     m.flash_attn_forward_gqa(s.q, s.k, s.v, s.o, s.lse, cfg.B, cfg.T, cfg.Hq, cfg.Hkv, cfg.D)
-    m.flash_attn_backward_gqa(s.q, s.k, s.v, s.o, s.lse, s.do, s.dq, s.dk, s.dv, cfg.B, cfg.T, cfg.Hq, cfg.Hkv, cfg.D)
+    m.flash_attn_backward_gqa(s.q, s.k, s.v, s.o, s.lse, s.do, s.dq, s.dk, s.dv, cfg.B, cfg.T, cfg.Hq, cfg.Hkv, cfg.D,
+                              mode="two_pass")
+
+
+def set_bytes(cfg):
+    """Bytes of one step's device tensors: q, dO, O, dQ (Hq heads), k, v, dK, dV (Hkv heads), BF16, and the logsumexp."""
+    return 2 * cfg.B * cfg.T * cfg.D * (4 * cfg.Hq + 4 * cfg.Hkv) + 4 * cfg.B * cfg.Hq * cfg.T
+
+
+def n_buffer_sets(cfg):
+    return max(2, int(2 * 126e6 // set_bytes(cfg)) + 1)
+
+
+def workload_config(cfg_full, world, scaling):
+    """What both arms print under "config": the workload, identical for the two arms (how an arm ran it is in "run")."""
+    per_gpu = cfg_full if scaling == "weak" else dataclasses.replace(cfg_full, B=cfg_full.B // world)
+    n = n_buffer_sets(per_gpu)
+    return {"workload": cfg_full.name, "B_per_gpu": per_gpu.B,
+            "global_B": cfg_full.B * world if scaling == "weak" else cfg_full.B, "T": cfg_full.T, "Hq": cfg_full.Hq,
+            "Hkv": cfg_full.Hkv, "D": cfg_full.D, "layout": "BHTD",
+            "parallelism": f"{world} x independent (batch, KV head) shards",
+            "l2": f"on a GPU consecutive steps rotate over {n} distinct buffer sets, {n * set_bytes(per_gpu) / 1e6:.0f} MB "
+                  "> 126 MB L2",
+            "inputs": "q,k: N(0,1) -> RoPE(base 1e4) -> per-head RMSNorm(gamma 1); v: N(0,1); dO: N(0,1e-2) "
+                      "(sigma 0.1; the kernels' time does not depend on the scale of dO); rounded to BF16"}
 
 
 def kernel_breakdown(m, cfg, sets, steps):
@@ -314,7 +338,7 @@ def kernel_breakdown(m, cfg, sets, steps):
         m.flash_attn_forward_gqa(s.q, s.k, s.v, s.o, s.lse, cfg.B, cfg.T, cfg.Hq, cfg.Hkv, cfg.D)
         e[1].record()
         m.flash_attn_backward_gqa(s.q, s.k, s.v, s.o, s.lse, s.do, s.dq, s.dk, s.dv, cfg.B, cfg.T, cfg.Hq, cfg.Hkv,
-                                  cfg.D)
+                                  cfg.D, mode="two_pass")
     lib.b200attn_set_bwd_profile_events(None, None, None)
     torch.cuda.synchronize()
     names = ["attn_fwd_kernel", "attn_bwd_dq_kernel", "attn_bwd_dkdv_kernel"]
@@ -325,56 +349,102 @@ def kernel_breakdown(m, cfg, sets, steps):
     return out
 
 
+def bind_near_gpu(index):
+    """Binds this process to the host cores NVML names as close to GPU `index` (those of them the process may
+    run on), so that the pinned buffers allocated afterwards are first touched on that side of the host.  A host
+    setting of this process only; nothing on the GPU changes.  Returns the number of cores bound, or None."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        allowed = os.sched_getaffinity(0)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (max(allowed) // 64) + 1)
+        near = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+        pick = near & allowed
+        if pick and pick != allowed:
+            os.sched_setaffinity(0, pick)
+            return len(pick)
+        return len(allowed) if pick else None
+    except Exception:
+        return None
+
+
+class PackedStep:
+    """Device tensors of one step carved out of two allocations (inputs q|k|v|dO and outputs O|dQ|dK|dV), so that
+    a step's inputs cross the host link in ONE copy and its results in one."""
+
+    def __init__(self, cfg, device):
+        import torch
+
+        nq, nk = cfg.B * cfg.Hq * cfg.T * cfg.D, cfg.B * cfg.Hkv * cfg.T * cfg.D
+        self.inp = torch.empty(2 * nq + 2 * nk, dtype=torch.bfloat16, device=device)
+        self.out = torch.empty(2 * nq + 2 * nk, dtype=torch.bfloat16, device=device)
+        qs, ks = (cfg.B, cfg.Hq, cfg.T, cfg.D), (cfg.B, cfg.Hkv, cfg.T, cfg.D)
+        self.q, self.k = self.inp[:nq].view(qs), self.inp[nq:nq + nk].view(ks)
+        self.v, self.do = self.inp[nq + nk:nq + 2 * nk].view(ks), self.inp[nq + 2 * nk:].view(qs)
+        self.o, self.dq = self.out[:nq].view(qs), self.out[nq:2 * nq].view(qs)
+        self.dk, self.dv = self.out[2 * nq:2 * nq + nk].view(ks), self.out[2 * nq + nk:].view(ks)
+        self.lse = torch.empty(cfg.B, cfg.Hq, cfg.T, dtype=torch.float32, device=device)
+
+
 def e2e_measure(m, cfg, host_sets, steps, warmup, device):
-    """Steps/s through the operator API with HOST buffers: H2D of q,k,v,dO from pinned memory, forward,
-    backward, D2H of O,dQ,dK,dV into pinned memory; three streams, two device buffer sets in flight."""
+    """ms per step through the operator API with HOST buffers: one H2D copy of q|k|v|dO from pinned memory, forward,
+    backward, one D2H copy of O|dQ|dK|dV into pinned memory; three streams, two device buffer sets in flight.  Also
+    the same copies with no kernels in between (what the host link alone allows)."""
     import torch
 
     n_buf = 2
-    dev = [BufferSet(cfg, host_sets[0], device) for _ in range(n_buf)]
-    outs = [[torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in (d.o, d.dq, d.dk, d.dv)] for d in dev]
+    dev = [PackedStep(cfg, device) for _ in range(n_buf)]
+    packed_in = []
+    for h in host_sets:
+        buf = torch.empty(dev[0].inp.numel(), dtype=torch.bfloat16, pin_memory=True)
+        torch.cat([t.reshape(-1) for t in (h[0], h[1], h[2], h[3])], out=buf)
+        packed_in.append(buf)
+    outs = [torch.empty(dev[0].out.numel(), dtype=torch.bfloat16, pin_memory=True) for _ in range(n_buf)]
     s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
     ev_in = [torch.cuda.Event() for _ in range(n_buf)]
     ev_cmp = [torch.cuda.Event() for _ in range(n_buf)]
     ev_out = [torch.cuda.Event() for _ in range(n_buf)]
     torch.cuda.synchronize()
 
-    def one(i):
+    def one(i, compute=True):
         b = i % n_buf
-        h = host_sets[i % len(host_sets)]
         d = dev[b]
         with torch.cuda.stream(s_in):
             s_in.wait_event(ev_cmp[b])  # the previous use of these device inputs has been consumed
-            for dst, src in zip((d.q, d.k, d.v, d.do), h):
-                dst.copy_(src, non_blocking=True)
+            d.inp.copy_(packed_in[i % len(packed_in)], non_blocking=True)
             ev_in[b].record()
         with torch.cuda.stream(s_cmp):
             s_cmp.wait_event(ev_in[b])
             s_cmp.wait_event(ev_out[b])  # the previous outputs of this set have left the device
-            step(m, cfg, d)
+            if compute:
+                step(m, cfg, d)
             ev_cmp[b].record()
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_cmp[b])
-            for dst, src in zip(outs[b], (d.o, d.dq, d.dk, d.dv)):
-                dst.copy_(src, non_blocking=True)
+            outs[b].copy_(d.out, non_blocking=True)
             ev_out[b].record()
 
-    for i in range(warmup):
-        one(i)
-    torch.cuda.synchronize()
-    t0 = torch.cuda.Event(enable_timing=True)
-    t1 = torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for i in range(steps):
-        one(i)
-    for st in (s_in, s_cmp, s_out):
-        torch.cuda.current_stream().wait_stream(st)
-    t1.record()
-    torch.cuda.synchronize()
-    ms = t0.elapsed_time(t1)
-    h2d = sum(t.numel() * t.element_size() for t in host_sets[0])
-    d2h = sum(t.numel() * t.element_size() for t in outs[0])
-    return ms / steps, h2d, d2h
+    def timed(compute):
+        for i in range(warmup):
+            one(i, compute)
+        torch.cuda.synchronize()
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for i in range(steps):
+            one(i, compute)
+        for st in (s_in, s_cmp, s_out):
+            torch.cuda.current_stream().wait_stream(st)
+        t1.record()
+        torch.cuda.synchronize()
+        return t0.elapsed_time(t1) / steps
+
+    ms = timed(True)
+    ms_copy = timed(False)
+    nbytes = dev[0].inp.numel() * 2
+    return ms, ms_copy, nbytes, nbytes
 
 
 def run_decode(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier):
@@ -709,6 +779,7 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    cfg_full = cfg
     global_B = cfg.B * world
     if args.scaling == "strong" and world > 1:
         if cfg.B % world != 0:
@@ -717,7 +788,7 @@ def main():
         cfg = dataclasses.replace(cfg, B=cfg.B // world)  # this rank's contiguous block of (batch, KV head) units
 
     if args.impl == "reference":
-        run_reference_arm(args, cfg, rank, world)
+        run_reference_arm(args, cfg, cfg_full, rank, world)
         return
 
     import torch
@@ -764,7 +835,7 @@ def main():
     seed0 = 20260002 + 1000 * rank
     host0 = [t.pin_memory() for t in inputs.make_train_inputs(cfg, seed0)[:4]]
     probe = BufferSet(cfg, host0, device)
-    n_sets = max(2, int(2 * 126e6 // probe.nbytes()) + 1)
+    n_sets = n_buffer_sets(cfg)
     host_sets = [host0] + [[t.pin_memory() for t in inputs.make_train_inputs(cfg, seed0 + i)[:4]]
                            for i in range(1, min(n_sets, 4))]
     sets = [probe] + [BufferSet(cfg, host_sets[i % len(host_sets)], device) for i in range(1, n_sets)]
@@ -775,24 +846,20 @@ def main():
     m.device_status()
     barrier()
 
+    # ONE launch protocol gives `value`: a round over the buffer sets captured in a CUDA graph and replayed (it does
+    # not depend on how fast the host's Python issues three 25-30 us launches); --no-graph makes it direct calls.
+    # The other way is timed too, over the same K steps, and only reported in config.ms_per_step_by_launch.
     graphs = None
     if not args.no_graph:
         graphs = StepGraphs(lambda i: step(m, cfg, sets[i % n_sets]), n_sets)
         graphs.prepare(steps)
         m.device_status()
-    # The same K steps are timed twice, replayed from the graph and issued one by one (each run bracketed as the
-    # contract says, the max over ranks taken of each); the line reports the faster way and names it.  Which one
-    # wins depends on the host: direct calls keep the dependent-launch overlap between rounds, graphs do not wait
-    # for Python.
-    def timed_steps(use_graph):
+
+    def timed_steps(run, n):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         e0.record()
-        if use_graph:
-            graphs.run(steps)
-        else:
-            for i in range(steps):
-                step(m, cfg, sets[i % n_sets])
+        run(n)
         e1.record()
         barrier()
         ms = e0.elapsed_time(e1)
@@ -803,19 +870,30 @@ def main():
             ms = float(t.item())
         return ms
 
+    def run_direct(n):
+        for i in range(n):
+            step(m, cfg, sets[i % n_sets])
+
     sampler = ClockSampler(local_rank)
     sampler.start()
-    ms_by_launch = {"direct calls": timed_steps(False)}
+    ms_by_launch = {"direct": timed_steps(run_direct, steps)}
     if graphs is not None:
-        ms_by_launch[f"one round over the {n_sets} buffer sets captured in a CUDA graph and replayed"] = timed_steps(True)
+        ms_by_launch["graph"] = timed_steps(graphs.run, steps)
     clocks = sampler.stop()
-    launch_how = min(ms_by_launch, key=ms_by_launch.get)
-    ms_total = ms_by_launch[launch_how]
-    ms_step = ms_total / steps
+    launch_how = "direct" if graphs is None else "graph"
+    ms_step = ms_by_launch[launch_how] / steps
     flops_step = cfg.fwd_bwd_flops()
     value = world * flops_step / (ms_step * 1e-3) / 1e12
 
-    # checksum gather: the only collective, outside every timed region
+    # the same steps on ONE buffer set (inputs of 67 MB stay in the 126 MB L2 from step to step)
+    warm_graph = StepGraphs(lambda i: step(m, cfg, sets[0]), 4) if graphs is not None else None
+    if warm_graph is not None:
+        warm_graph.prepare(steps)
+        ms_warm = timed_steps(warm_graph.run, steps) / steps
+    else:
+        ms_warm = timed_steps(lambda n: [step(m, cfg, sets[0]) for _ in range(n)], steps) / steps
+
+    # checksum gather: outside every timed region
     checksum = float(sets[0].dq.float().abs().sum().item())
     if world > 1:
         t = torch.tensor([checksum], device=device)
@@ -825,21 +903,36 @@ def main():
 
     # per-kernel device times (same loop, events between the kernels)
     kt = kernel_breakdown(m, cfg, sets, steps)
-    # executed matmul FLOPs of each kernel over the causal half: forward 2 GEMMs, dK/dV pass 4, dQ pass 3
+    # FLOPs per launch.  Credited (the metric's convention: forward 2 products over the causal half, backward 5):
+    # the backward's 5 are split over its two kernels in the ratio of what they execute (dQ pass 3 products,
+    # dK/dV pass 4: both recompute the scores), so the credited shares add up to the metric's FLOPs.
     gemm = cfg.fwd_flops() / 2.0
-    kflops = {"attn_fwd_kernel": 2 * gemm, "attn_bwd_dkdv_kernel": 4 * gemm, "attn_bwd_dq_kernel": 3 * gemm}
-    dom = max(kflops, key=lambda n: kt[n])
-    peak = float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]))
-    achieved = kflops[dom] / (kt[dom] * 1e-3) / 1e12
+    executed = {"attn_fwd_kernel": 2 * gemm, "attn_bwd_dq_kernel": 3 * gemm, "attn_bwd_dkdv_kernel": 4 * gemm}
+    credited = {"attn_fwd_kernel": 2 * gemm, "attn_bwd_dq_kernel": 5 * gemm * 3 / 7, "attn_bwd_dkdv_kernel": 5 * gemm * 4 / 7}
+    dom = max(kt, key=kt.get)
+    burst, sustained = float(peaks["bf16_tflops"]), float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]))
+    achieved = credited[dom] / (kt[dom] * 1e-3) / 1e12
+    bwd_ms = kt["attn_bwd_dq_kernel"] + kt["attn_bwd_dkdv_kernel"]
     roofline = {
-        "bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-        "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(cfg.name, {}).get(dom) if cfg.B == inputs.CONFIGS[args.config].B else None,
-        "peak_source": f"bf16_tflops_sustained of {peaks['_source']} (kernel timed inside a long loop); burst "
-                       f"{peaks['bf16_tflops']}",
-        "flops_per_launch": kflops[dom], "ms_per_launch": kt[dom],
+        "bound": "tensor", "kernel": dom, "achieved": achieved, "peak": burst, "unit": "TFLOP/s", "frac": achieved / burst,
+        "traffic": NCU_TRAFFIC_BYTES.get(cfg.name, {}).get(dom) if cfg.B == inputs.CONFIGS[args.config].B else None,
+        "peak_source": f"bf16_tflops (burst) of {peaks['_source']}: the timed region lasts milliseconds at full clocks; "
+                       f"sustained {sustained}",
+        "flops_per_launch": credited[dom], "ms_per_launch": kt[dom],
+        "flops_convention": "credited: forward 2 products per score block, backward 5, the backward's split 3:4 over "
+                            "the dQ and dK/dV passes",
+        "executed": {"flops_per_launch": executed[dom], "achieved": executed[dom] / (kt[dom] * 1e-3) / 1e12,
+                     "frac_of_burst": executed[dom] / (kt[dom] * 1e-3) / 1e12 / burst,
+                     "frac_of_sustained": executed[dom] / (kt[dom] * 1e-3) / 1e12 / sustained},
         "kernels_ms": kt,
-        "whole_step": {"achieved": value / world, "frac": value / world / peak,
-                       "frac_of_burst": value / world / float(peaks["bf16_tflops"])},
+        "fwd": {"ms": kt["attn_fwd_kernel"], "tflops": cfg.fwd_flops() / (kt["attn_fwd_kernel"] * 1e-3) / 1e12,
+                "frac_of_burst": cfg.fwd_flops() / (kt["attn_fwd_kernel"] * 1e-3) / 1e12 / burst},
+        "bwd": {"ms": bwd_ms, "tflops": 2.5 * cfg.fwd_flops() / (bwd_ms * 1e-3) / 1e12,
+                "frac_of_burst": 2.5 * cfg.fwd_flops() / (bwd_ms * 1e-3) / 1e12 / burst,
+                "note": "kernels timed one by one with events between them; back to back they overlap a little"},
+        "whole_step": {"achieved": value / world, "frac": value / world / burst, "frac_of_sustained": value / world / sustained,
+                       "l2_warm_ms_per_step": ms_warm,
+                       "l2_warm_tflops": flops_step / (ms_warm * 1e-3) / 1e12},
     }
     # the HBM roof beside the tensor roof: with L2-cold inputs a step cannot move fewer bytes than
     # forward q,k,v,o,lse and backward q,k,v,o,lse,dO,dq,dk,dv (BF16, FP32 lse)
@@ -851,48 +944,216 @@ def main():
                             "tflops_ceiling": cfg.fwd_bwd_flops() / (hbm_ms * 1e-3) / 1e12,
                             "frac_of_ceiling": (value / world) / (cfg.fwd_bwd_flops() / (hbm_ms * 1e-3) / 1e12)}
 
+    # strong scaling and the (batch, KV head) partition on hardware: every N > 1 run carries it
+    strong = None
+    if world > 1 and args.scaling == "weak":
+        strong = {}
+        for name in dict.fromkeys([cfg_full.name, "c3_300m_class"]):
+            full = inputs.CONFIGS[name] if name != cfg_full.name else cfg_full
+            t_full = ms_step if name == cfg_full.name else None
+            strong[name] = measure_strong(m, full, rank, world, device, min(steps, 400), barrier, t_full,
+                                          sets[0] if (name == cfg_full.name and rank == 0) else None)
+
     # end to end with host buffers
+    near = bind_near_gpu(local_rank)
     e2e_steps = max(20, min(steps, 200))
-    e2e_ms, h2d, d2h = e2e_measure(m, cfg, host_sets, e2e_steps, 5, device)
+    e2e_ms, copy_ms, h2d, d2h = e2e_measure(m, cfg, host_sets, e2e_steps, 5, device)
     if world > 1:
-        t = torch.tensor([e2e_ms], device=device)
+        t = torch.tensor([e2e_ms, copy_ms], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+        e2e_ms, copy_ms = float(t[0].item()), float(t[1].item())
     e2e = {"value": world * flops_step / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
-           "what": "pinned host q,k,v,dO -> device, forward, backward, O,dQ,dK,dV -> pinned host; copies and "
-                   "compute of consecutive steps overlap on three streams"}
+           "copy_only_ms_per_step": copy_ms,
+           "host_link_gbs_per_direction": h2d / (copy_ms * 1e-3) / 1e9,
+           "host_cores_bound_near_gpu": near,
+           "what": "pinned host q|k|v|dO -> device in one copy, forward, backward, O|dQ|dK|dV -> pinned host in one copy; "
+                   "copies and compute of consecutive steps overlap on three streams; copy_only is the same loop "
+                   "without the kernels (what the host link allows)"}
     m.device_status()
 
-    cpu = None
+    cpu = ref_gpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline(cfg, seed0)
+        ref_gpu = reference_gpu_paths(m, cfg, sets[0])
 
     if rank == 0:
+        config = workload_config(cfg_full, world, args.scaling)
+        run = {
+            "launch": ("one round over the buffer sets captured in a CUDA graph and replayed" if launch_how == "graph"
+                       else "every launch issued from Python"),
+            "ms_per_step_by_launch": {k: v / steps for k, v in ms_by_launch.items()},
+            "backward": "two-pass (dQ pass, dK/dV pass): bit-reproducible", "buffer_sets": n_sets}
         line = {
             "metric": "causal_gqa_attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
             "steps": steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling,
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": cfg.name, "B_per_gpu": cfg.B, "global_B": global_B, "T": cfg.T, "Hq": cfg.Hq,
-                       "Hkv": cfg.Hkv, "D": cfg.D, "layout": "BHTD", "parallelism": f"{world} x independent (batch, KV head) shards",
-                       "l2": f"rotating over {n_sets} buffer sets, {n_sets * probe.nbytes() / 1e6:.0f} MB > 126 MB L2",
-                       "launch": launch_how,
-                       "ms_per_step_by_launch": {("graph" if "graph" in k else "direct"): v / steps
-                                                 for k, v in ms_by_launch.items()},
-                       "inputs": "q,k: N(0,1) -> RoPE(base 1e4) -> per-head RMSNorm(gamma 1); v: N(0,1); "
-                                 "dO: N(0,1e-2); rounded to BF16"},
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config, "run": run,
             "per_gpu_tflops": value / world,
-            "pct_of_bf16_peak": {"burst": 100 * value / world / float(peaks["bf16_tflops"]),
-                                 "sustained": 100 * value / world / peak, "source": peaks["_source"]},
+            "pct_of_bf16_peak": {"burst": 100 * value / world / burst, "sustained": 100 * value / world / sustained,
+                                 "source": peaks["_source"]},
             "clocks": clocks, "e2e": e2e, "gpu_launches": 3 * steps, "roofline": roofline,
             "checksum_dq_abs_sum": checksum,
         }
+        if strong is not None:
+            line["strong"] = strong
         if cpu is not None:
             line["cpu_baseline"] = cpu
+        if ref_gpu is not None:
+            line["reference_gpu"] = ref_gpu
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def measure_strong(m, full, rank, world, device, steps, barrier, t_full_ms, full_result):
+    """The whole configuration `full` split over the ranks by (batch, KV head) units (sharding.unit_range): every
+    rank runs its contiguous block, nothing is exchanged.  Device time of a step is the max over ranks; efficiency is
+    against the time of the whole configuration on one GPU (t_full_ms, measured in this run when the configuration
+    is the bench's own, else taken by rank 0 here).  Outside the timed region every rank's O, dQ, dK, dV are gathered
+    over NCCL (sharding.gather_units) and rank 0 compares them, bit for bit, with its own run of the whole
+    configuration."""
+    import torch
+    import torch.distributed as dist
+    from modern_llm_v1_b200 import inputs, sharding
+
+    seed = 20260002
+    lo, hi = sharding.unit_range(full.units, rank, world)
+    if (hi - lo) % full.Hkv or lo % full.Hkv:
+        return {"skipped": f"{full.units} units do not split into whole batches over {world} ranks"}
+    mine = dataclasses.replace(full, B=(hi - lo) // full.Hkv)
+    host = [t.pin_memory() for t in inputs.make_train_inputs(full, seed, lo, hi)[:4]]
+    one = BufferSet(mine, host, device)
+    n_sets = max(2, int(2 * 126e6 // one.nbytes()) + 1)
+    sets = [one] + [BufferSet(mine, host, device) for _ in range(n_sets - 1)]
+    for i in range(3):
+        step(m, mine, sets[i % n_sets])
+    graphs = StepGraphs(lambda i: step(m, mine, sets[i % n_sets]), n_sets)
+    graphs.prepare(steps)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    graphs.run(steps)
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    m.device_status()
+    # the whole configuration on one GPU, for the efficiency and for the comparison
+    ref = None
+    if rank == 0:
+        if full_result is None:
+            hf = inputs.make_train_inputs(full, seed)[:4]
+            fs = [BufferSet(full, hf, device) for _ in range(max(2, int(2 * 126e6 // (one.nbytes() * world)) + 1))]
+            for s_ in fs[:2]:
+                step(m, full, s_)
+            gf = StepGraphs(lambda i: step(m, full, fs[i % len(fs)]), len(fs))
+            gf.prepare(steps)
+            torch.cuda.synchronize()
+            e0.record()
+            gf.run(steps)
+            e1.record()
+            torch.cuda.synchronize()
+            t_full_ms = e0.elapsed_time(e1) / steps
+            full_result = fs[0]
+        ref = full_result
+    tt = torch.tensor([t_full_ms if rank == 0 else 0.0], device=device)
+    dist.broadcast(tt, 0)
+    t_full_ms = float(tt.item())
+    # verification gather (the only collective; not timed)
+    g, T, D, Hkv = full.group, full.T, full.D, full.Hkv
+    per_unit = lambda x, h: x.reshape(-1, Hkv, h, T, D).reshape(-1, h, T, D)
+    ok, worst = True, 0.0
+    for name, local, h in (("o", one.o, g), ("dq", one.dq, g), ("dk", one.dk, 1), ("dv", one.dv, 1)):
+        got = sharding.gather_units(per_unit(local, h).contiguous(), full.units, rank, world)
+        if rank == 0:
+            want = per_unit(getattr(ref, name), h)
+            same = torch.equal(got, want)
+            ok = ok and same
+            if not same:
+                worst = max(worst, float((got.float() - want.float()).abs().max().item()))
+    flops = full.fwd_bwd_flops()
+    return {"ms_per_step": ms, "tflops_total": flops / (ms * 1e-3) / 1e12,
+            "tflops_per_gpu": flops / (ms * 1e-3) / 1e12 / world, "one_gpu_ms_per_step": t_full_ms,
+            "speedup": t_full_ms / ms, "efficiency": t_full_ms / ms / world,
+            "units_per_gpu": hi - lo, "query_tiles_per_gpu": (hi - lo) * g * ((T + 127) // 128),
+            "limiter": ("per-kernel start-up and tail (about 6 us each of three kernels) do not shrink with the work, and "
+                        f"{(hi - lo) * g * ((T + 127) // 128)} forward items do not fill the 296 CTA slots of a GPU"
+                        if (hi - lo) * g * ((T + 127) // 128) < 296 * 2 else
+                        "per-kernel start-up and tail (about 6 us each of three kernels) do not shrink with the work"),
+            "parity_ok": bool(ok) if rank == 0 else None, "parity_max_abs_diff": worst,
+            "parity": "O, dQ, dK, dV of every unit gathered over NCCL == the whole configuration run on rank 0, bit for bit"}
+
+
+def reference_gpu_paths(m, cfg, s):
+    """The reference's own two GPU attention paths (its per-row flash kernels and its cuBLAS path with
+    repeat_kv_heads / accumulate_kv_grads, compiled unchanged for sm_100a into oracle/_ref/libref_gpu.so where the
+    reference tree was present at build time) timed beside this library: forward + backward at the configuration, and
+    forward / backward at the shapes of the reference's own benchmark (llm/tests/bench_flash_attn.cu:98-101:
+    B' = 8 heads, D = 64, T = 128..512; B' = 4 at T = 1024).  Part of the CPU/reference baseline leg: never on the
+    product path, never in a timed region of the arm."""
+    import ctypes
+
+    import torch
+
+    path = os.path.join(ROOT, "oracle", "_ref", "libref_gpu.so")
+    if not os.path.exists(path):
+        return {"unavailable": "oracle/_ref/libref_gpu.so was not built (it needs the reference tree at build time)"}
+    L = ctypes.CDLL(path)
+    L.ref_gpu_attention.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 9 + [ctypes.c_int] * 5
+    L.ref_gpu_attention.restype = ctypes.c_int
+
+    def ms_of(fn, reps):
+        fn()
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    def ref_call(which, q, k, v, do, B, T, Hq, Hkv, D):
+        qf, kf, vf = q.float().contiguous(), k.float().contiguous(), v.float().contiguous()
+        dof = do.float().contiguous() if do is not None else None
+        o, dq, dk, dv = torch.empty_like(qf), torch.empty_like(qf), torch.empty_like(kf), torch.empty_like(vf)
+        lse = torch.zeros(B, Hq, T, device=q.device)
+
+        def run():
+            rc = L.ref_gpu_attention(which, qf.data_ptr(), kf.data_ptr(), vf.data_ptr(),
+                                     dof.data_ptr() if dof is not None else None, o.data_ptr(), lse.data_ptr(), dq.data_ptr(),
+                                     dk.data_ptr(), dv.data_ptr(), B, T, Hq, Hkv, D)
+            if rc != 0:
+                raise RuntimeError("the reference's GPU attention threw")
+        return run
+
+    out = {"what": "the reference's GPU paths compiled unchanged for sm_100a (FP32), its own GQA copies and allocations "
+                   "included, on this GPU"}
+    B, T, Hq, Hkv, D = cfg.B, cfg.T, cfg.Hq, cfg.Hkv, cfg.D
+    flash = ms_of(ref_call(0, s.q, s.k, s.v, s.do, B, T, Hq, Hkv, D), 2)
+    cublas = ms_of(ref_call(1, s.q, s.k, s.v, s.do, B, T, Hq, Hkv, D), 2)
+    ours = ms_of(lambda: step(m, cfg, s), 20)
+    out[cfg.name] = {"flash_ms": flash, "cublas_ms": cublas, "this_library_ms": ours}
+    table = []
+    for Bh, Tb in ((8, 128), (8, 256), (8, 512), (4, 1024)):
+        g = torch.Generator().manual_seed(Tb)
+        q, k, v, do = ((torch.rand(Bh, 1, Tb, 64, generator=g) * 2 - 1).bfloat16().to(s.q.device) for _ in range(4))
+        o, lse = torch.empty_like(q), torch.empty(Bh, 1, Tb, device=q.device)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+        row = {"B_heads": Bh, "T": Tb, "D": 64}
+        for which, nm in ((0, "flash"), (1, "naive")):
+            row[f"{nm}_fwd_ms"] = ms_of(ref_call(which, q, k, v, None, Bh, Tb, 1, 1, 64), 8)
+            row[f"{nm}_fwd_bwd_ms"] = ms_of(ref_call(which, q, k, v, do, Bh, Tb, 1, 1, 64), 8)
+        row["this_library_fwd_ms"] = ms_of(lambda: m.flash_attn_forward_gqa(q, k, v, o, lse, Bh, Tb, 1, 1, 64), 20)
+        row["this_library_bwd_ms"] = ms_of(
+            lambda: m.flash_attn_backward_gqa(q, k, v, o, lse, do, dq, dk, dv, Bh, Tb, 1, 1, 64, mode="two_pass"), 20)
+        table.append(row)
+    out["reference_bench_shapes"] = table
+    m.device_status()
+    return out
 
 
 if __name__ == "__main__":

@@ -43,7 +43,8 @@ enum {
     B200ATTN_ERR_TENSOR_MAP = 6,   /* the driver refused a TMA tensor map */
     B200ATTN_ERR_DEVICE_WAIT = 7,  /* a kernel gave up on a bounded wait (see b200attn_last_device_status) */
     B200ATTN_ERR_NO_DEVICE = 8,    /* no sm_100 device is current */
-    B200ATTN_ERR_TOO_LARGE = 9     /* problem exceeds the fixed scratch of b200attn_bwd_static */
+    B200ATTN_ERR_TOO_LARGE = 9     /* problem too large: beyond the fixed scratch of b200attn_bwd_static (524288 rows), or
+                                      2^31 or more rows in a RoPE / QK-Norm / KV-append call */
 };
 
 enum { B200ATTN_LAYOUT_BHTD = 0, B200ATTN_LAYOUT_BTHD = 1 };
@@ -184,8 +185,10 @@ int b200attn_decode_cached(const void* q, const void* kcache, const void* vcache
 /*
  * The same two calls for sequences of different lengths (a batch that does not advance in lock step).
  * b200attn_kv_append_at: pos [B] (device, int32) is the first position of each sequence's n_new tokens.  A
- * sequence whose pos[b] + n_new exceeds L_cap is skipped and sets the device status word to 105
- * (b200attn_last_device_status reports and clears it).
+ * sequence whose pos[b] + n_new exceeds L_cap is skipped and sets the device status word to 105 (unless the word
+ * already holds an earlier code).  While the status word is non-zero every kernel of this library on that device
+ * returns at once without writing anything, although its launching call still returns B200ATTN_OK: check
+ * b200attn_last_device_status (which reports the code and clears the word) before trusting later results.
  * b200attn_decode_ragged: lens [B] (device, int32), 1 <= lens[b] <= L, is each sequence's cache length
  * (the newest token included); L is the host's upper bound on them: it sizes the grid, the splits and the
  * workspace (b200attn_decode_workspace_bytes with this L).  Rows lens[b] .. L-1 of a sequence's caches are

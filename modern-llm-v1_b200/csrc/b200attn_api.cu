@@ -1045,7 +1045,8 @@ extern "C" const char* b200attn_strerror(int status) {
         case B200ATTN_ERR_DEVICE_WAIT: return "a kernel gave up on a bounded wait";
         case B200ATTN_ERR_NO_DEVICE: return "no usable CUDA device is current";
         case B200ATTN_ERR_TOO_LARGE:
-            return "problem exceeds the fixed scratch of b200attn_bwd_static (B*Hq*ceil(T/128)*128 > 524288)";
+            return "problem too large: beyond the fixed scratch of b200attn_bwd_static (B*Hq*ceil(T/128)*128 > 524288), or "
+                   "2^31 or more rows in a RoPE / QK-Norm / KV-append call";
         case DEV_WAIT_TIMEOUT_LOAD: return "device: a TMA load barrier never completed";
         case DEV_WAIT_TIMEOUT_MMA: return "device: a tensor-core completion barrier never completed";
         case DEV_WAIT_TIMEOUT_SOFTMAX: return "device: a softmax hand-off barrier never completed";

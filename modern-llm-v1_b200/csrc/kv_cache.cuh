@@ -102,7 +102,7 @@ kv_append_kernel(const __grid_constant__ KvAppendParams p) {
         ss = rn_row_sum<LPR>(ss);  // every lane takes part in the shuffles
         if (!live) continue;
         if (!fits) {
-            if (li == 0) atomicExch(p.status, int(DEV_KV_CACHE_OVERFLOW));
+            if (li == 0) atomicCAS(p.status, 0, int(DEV_KV_CACHE_OVERFLOW));  // the first error recorded stays
             continue;
         }
         if (which == 2) {

@@ -1,8 +1,12 @@
 // See modernllm_shim.h.  Compiled inside the reference tree; links libb200attn.so.
 #include "modernllm_shim.h"
 
+#include <cuda_runtime.h>
+
+#include <mutex>
 #include <stdexcept>
 #include <string>
+#include <vector>
 
 #include "b200attn.h"
 
@@ -23,15 +27,40 @@ void raise(int status, const char* fn) {
     if (status == B200ATTN_OK) return;
     std::string msg = std::string(fn) + ": " + b200attn_strerror(status);
     if (status == B200ATTN_ERR_INVALID_ARG || status == B200ATTN_ERR_UNSUPPORTED ||
-        status == B200ATTN_ERR_ALIGNMENT || status == B200ATTN_ERR_WORKSPACE)
+        status == B200ATTN_ERR_ALIGNMENT || status == B200ATTN_ERR_WORKSPACE || status == B200ATTN_ERR_TOO_LARGE)
         throw std::invalid_argument(msg);
     throw std::runtime_error(msg);
+}
+
+// A private temporary that is kept between calls: one per (device, stream, operator), grown when a larger problem
+// comes and never shrunk.  Growing frees the old buffer, and cudaFree waits for the work that still reads it.
+enum WsKind { kWsBackward = 0, kWsDecode = 1, kWsRopeNorm = 2 };
+struct WsEntry {
+    int device;
+    void* stream;
+    int kind;
+    Tensor buf;
+};
+void* cached_workspace(int kind, size_t bytes, void* stream) {
+    static std::mutex mu;
+    static std::vector<WsEntry> cache;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) throw std::runtime_error("cached_workspace: no current CUDA device");
+    std::lock_guard<std::mutex> lock(mu);
+    for (WsEntry& e : cache) {
+        if (e.device == dev && e.stream == stream && e.kind == kind) {
+            if (e.buf.bytes() < bytes) e.buf = Tensor({static_cast<std::int64_t>((bytes + 3) / 4)}, DType::FP32, Device::Cuda);
+            return e.buf.data();
+        }
+    }
+    cache.push_back(WsEntry{dev, stream, kind, Tensor({static_cast<std::int64_t>((bytes + 1023) / 4)}, DType::FP32, Device::Cuda)});
+    return cache.back().buf.data();
 }
 
 }  // namespace
 
 void flash_attn_forward_gqa(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& ctx, Tensor& L, int B, int T,
-                            int Hq, int Hkv, int D, Layout layout) {
+                            int Hq, int Hkv, int D, Layout layout, void* stream) {
     const char* fn = "flash_attn_forward";
     check(q, DType::BF16, fn, "q"); check(k, DType::BF16, fn, "k"); check(v, DType::BF16, fn, "v");
     check(ctx, DType::BF16, fn, "ctx"); check(L, DType::FP32, fn, "L");
@@ -42,13 +71,13 @@ void flash_attn_forward_gqa(const Tensor& q, const Tensor& k, const Tensor& v, T
         throw std::invalid_argument("flash_attn_forward: shape mismatch (qkv/ctx)");
     if (L.numel() != 1LL * B * Hq * T) throw std::invalid_argument("flash_attn_forward: L must be [B, T]");
     raise(b200attn_fwd(q.data(), k.data(), v.data(), ctx.data(), L.data_as<float>(), B, T, Hq, Hkv, D,
-                       static_cast<int>(layout), 0.f, nullptr),
+                       static_cast<int>(layout), 0.f, stream),
           fn);
 }
 
 void flash_attn_backward_gqa(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& ctx, const Tensor& L,
                              const Tensor& d_ctx, Tensor& d_q, Tensor& d_k, Tensor& d_v, int B, int T, int Hq,
-                             int Hkv, int D, Layout layout) {
+                             int Hkv, int D, Layout layout, void* stream) {
     const char* fn = "flash_attn_backward";
     const Tensor* bf[] = {&q, &k, &v, &ctx, &d_ctx, &d_q, &d_k, &d_v};
     const char* names[] = {"q", "k", "v", "ctx", "d_ctx", "d_q", "d_k", "d_v"};
@@ -63,31 +92,38 @@ void flash_attn_backward_gqa(const Tensor& q, const Tensor& k, const Tensor& v, 
         v.numel() != nkv || d_k.numel() != nkv || d_v.numel() != nkv)
         throw std::invalid_argument("flash_attn_backward: shape mismatch");
     if (L.numel() != 1LL * B * Hq * T) throw std::invalid_argument("flash_attn_backward: L must be [B, T]");
-    // private temporary, like the reference's Dh (llm/src/model/flash_attn.cu:463)
-    const long long ws_bytes = static_cast<long long>(b200attn_bwd_workspace_bytes(B, T, Hq, Hkv, D));
-    Tensor ws({ws_bytes / 4}, DType::FP32, Device::Cuda);
-    raise(b200attn_bwd(q.data(), k.data(), v.data(), ctx.data(), L.data_as<float>(), d_ctx.data(), d_q.data(),
-                       d_k.data(), d_v.data(), B, T, Hq, Hkv, D, static_cast<int>(layout), 0.f, ws.data(),
-                       static_cast<size_t>(ws_bytes), nullptr),
+    // Private temporary (the reference's Dh, llm/src/model/flash_attn.cu:463, is a cudaMalloc per call).  On the
+    // legacy default stream - where the reference launches and where calls cannot overlap - the library's fixed
+    // scratch serves every problem that fits it; otherwise a workspace kept for this (device, stream).
+    const long long rows = 1LL * B * Hq * ((T + 127) / 128 * 128);
+    if (stream == nullptr && rows <= B200ATTN_BWD_STATIC_MAX_ROWS) {
+        raise(b200attn_bwd_static(q.data(), k.data(), v.data(), ctx.data(), L.data_as<float>(), d_ctx.data(), d_q.data(),
+                                  d_k.data(), d_v.data(), B, T, Hq, Hkv, D, static_cast<int>(layout), 0.f, stream),
+              fn);
+        return;
+    }
+    const size_t ws_bytes = b200attn_bwd_workspace_bytes_mode(B, T, Hq, Hkv, D, B200ATTN_BWD_TWO_PASS);
+    raise(b200attn_bwd_mode(q.data(), k.data(), v.data(), ctx.data(), L.data_as<float>(), d_ctx.data(), d_q.data(),
+                            d_k.data(), d_v.data(), B, T, Hq, Hkv, D, static_cast<int>(layout), 0.f, B200ATTN_BWD_TWO_PASS,
+                            cached_workspace(kWsBackward, ws_bytes, stream), ws_bytes, stream),
           fn);
-    // the workspace is freed at scope exit: wait for the kernels that read it
-    raise(b200attn_last_device_status(nullptr), fn);
 }
 
 void flash_attn_forward(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& ctx, Tensor& L, int B, int T, int D,
-                        int tile_kv) {
+                        int tile_kv, void* stream) {
     if (tile_kv <= 0) throw std::invalid_argument("flash_attn_forward: tile_kv must be > 0");
-    flash_attn_forward_gqa(q, k, v, ctx, L, B, T, 1, 1, D, Layout::BHTD);
+    flash_attn_forward_gqa(q, k, v, ctx, L, B, T, 1, 1, D, Layout::BHTD, stream);
 }
 
 void flash_attn_backward(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& ctx, const Tensor& L,
-                         const Tensor& d_ctx, Tensor& d_q, Tensor& d_k, Tensor& d_v, int B, int T, int D, int tile) {
+                         const Tensor& d_ctx, Tensor& d_q, Tensor& d_k, Tensor& d_v, int B, int T, int D, int tile,
+                         void* stream) {
     if (tile <= 0) throw std::invalid_argument("flash_attn_backward: tile must be > 0");
-    flash_attn_backward_gqa(q, k, v, ctx, L, d_ctx, d_q, d_k, d_v, B, T, 1, 1, D, Layout::BHTD);
+    flash_attn_backward_gqa(q, k, v, ctx, L, d_ctx, d_q, d_k, d_v, B, T, 1, 1, D, Layout::BHTD, stream);
 }
 
 void flash_attn_decode(const Tensor& q, const Tensor& kcache, const Tensor& vcache, Tensor& o, int B, int Lcache,
-                       int Hq, int Hkv, int D) {
+                       int Hq, int Hkv, int D, void* stream) {
     const char* fn = "flash_attn_decode";
     check(q, DType::BF16, fn, "q"); check(kcache, DType::BF16, fn, "kcache"); check(vcache, DType::BF16, fn, "vcache");
     check(o, DType::BF16, fn, "o");
@@ -95,12 +131,10 @@ void flash_attn_decode(const Tensor& q, const Tensor& kcache, const Tensor& vcac
     if (q.numel() != 1LL * B * Hq * D || o.numel() != q.numel() || kcache.numel() != 1LL * B * Hkv * Lcache * D ||
         vcache.numel() != kcache.numel())
         throw std::invalid_argument("flash_attn_decode: shape mismatch");
-    const long long ws_bytes = static_cast<long long>(b200attn_decode_workspace_bytes(B, Lcache, Hq, Hkv, D, 0));
-    Tensor ws({(ws_bytes + 3) / 4}, DType::FP32, Device::Cuda);
+    const size_t ws_bytes = b200attn_decode_workspace_bytes(B, Lcache, Hq, Hkv, D, 0);
     raise(b200attn_decode(q.data(), kcache.data(), vcache.data(), o.data(), nullptr, B, Lcache, Hq, Hkv, D, 0.f, 0,
-                          ws.data(), static_cast<size_t>(ws_bytes), nullptr),
+                          cached_workspace(kWsDecode, ws_bytes, stream), ws_bytes, stream),
           fn);
-    raise(b200attn_last_device_status(nullptr), fn);
 }
 
 namespace {
@@ -112,7 +146,7 @@ int x_dtype_of(const Tensor& x, const char* fn) {
 }  // namespace
 
 void rope_qknorm_forward(const Tensor& x, const Tensor& cos, const Tensor& sin, const Tensor& gamma, float eps, Tensor& y,
-                         Tensor& rstd, int B, int T, int H, int d_h, Layout x_layout, Layout y_layout) {
+                         Tensor& rstd, int B, int T, int H, int d_h, Layout x_layout, Layout y_layout, void* stream) {
     const char* fn = "rope_qknorm_forward";
     const int xd = x_dtype_of(x, fn);
     check(y, DType::BF16, fn, "y"); check(cos, DType::FP32, fn, "cos"); check(sin, DType::FP32, fn, "sin");
@@ -127,13 +161,13 @@ void rope_qknorm_forward(const Tensor& x, const Tensor& cos, const Tensor& sin, 
     raise(b200attn_rope_norm_fwd(x.data(), xd, static_cast<int>(x_layout), y.data(), static_cast<int>(y_layout),
                                  static_cast<float*>(rstd.data()), static_cast<const float*>(gamma.data()),
                                  static_cast<const float*>(cos.data()), static_cast<const float*>(sin.data()), B, T, H, d_h,
-                                 eps, nullptr),
+                                 eps, stream),
           fn);
 }
 
 void rope_qknorm_backward(const Tensor& d_y, const Tensor& x, const Tensor& cos, const Tensor& sin, const Tensor& gamma,
                           const Tensor& rstd, Tensor& d_x, Tensor& d_gamma, int B, int T, int H, int d_h, Layout x_layout,
-                          Layout y_layout) {
+                          Layout y_layout, void* stream) {
     const char* fn = "rope_qknorm_backward";
     const int xd = x_dtype_of(x, fn);
     check(d_y, DType::BF16, fn, "d_y"); check(d_x, x.dtype(), fn, "d_x"); check(cos, DType::FP32, fn, "cos");
@@ -146,20 +180,18 @@ void rope_qknorm_backward(const Tensor& d_y, const Tensor& x, const Tensor& cos,
         throw std::invalid_argument("rope: x numel mismatch");
     if (gamma.numel() != d_h || d_gamma.numel() != d_h || rstd.numel() != 1LL * B * H * T)
         throw std::invalid_argument("rope_qknorm_backward: shape mismatch (gamma/d_gamma/rstd)");
-    const long long ws_bytes = static_cast<long long>(b200attn_rope_norm_bwd_workspace_bytes(d_h));
-    Tensor ws({(ws_bytes + 3) / 4}, DType::FP32, Device::Cuda);  // private temporary, like the reference's Dh
+    const size_t ws_bytes = b200attn_rope_norm_bwd_workspace_bytes(d_h);
     raise(b200attn_rope_norm_bwd(d_y.data(), static_cast<int>(y_layout), x.data(), xd, static_cast<int>(x_layout),
                                  static_cast<const float*>(rstd.data()), static_cast<const float*>(gamma.data()),
                                  static_cast<const float*>(cos.data()), static_cast<const float*>(sin.data()), d_x.data(),
-                                 static_cast<float*>(d_gamma.data()), B, T, H, d_h, ws.data(), static_cast<size_t>(ws_bytes),
-                                 nullptr),
+                                 static_cast<float*>(d_gamma.data()), B, T, H, d_h,
+                                 cached_workspace(kWsRopeNorm, ws_bytes, stream), ws_bytes, stream),
           fn);
-    raise(b200attn_last_device_status(nullptr), fn);  // the workspace is freed on return: the kernels must be done
 }
 
 void kv_cache_append(const Tensor& q_proj, const Tensor& k_proj, const Tensor& v_proj, const Tensor& cos, const Tensor& sin,
                      const Tensor& gamma_q, const Tensor& gamma_k, float eps, Tensor& q_out, Tensor& kcache, Tensor& vcache,
-                     int B, int n_new, int pos0, int L_cap, int Hq, int Hkv, int d_h) {
+                     int B, int n_new, int pos0, int L_cap, int Hq, int Hkv, int d_h, void* stream) {
     const char* fn = "kv_cache_append";
     const int xd = x_dtype_of(q_proj, fn);
     check(k_proj, q_proj.dtype(), fn, "k_proj"); check(v_proj, q_proj.dtype(), fn, "v_proj");
@@ -180,12 +212,12 @@ void kv_cache_append(const Tensor& q_proj, const Tensor& k_proj, const Tensor& v
     raise(b200attn_kv_append(q_proj.data(), k_proj.data(), v_proj.data(), xd, q_out.data(), kcache.data(), vcache.data(),
                              static_cast<const float*>(gamma_q.data()), static_cast<const float*>(gamma_k.data()),
                              static_cast<const float*>(cos.data()), static_cast<const float*>(sin.data()), B, n_new, pos0,
-                             L_cap, Hq, Hkv, d_h, eps, nullptr),
+                             L_cap, Hq, Hkv, d_h, eps, stream),
           fn);
 }
 
 void flash_attn_decode_cached(const Tensor& q, const Tensor& kcache, const Tensor& vcache, Tensor& o, int B, int L, int L_cap,
-                              int Hq, int Hkv, int D) {
+                              int Hq, int Hkv, int D, void* stream) {
     const char* fn = "flash_attn_decode_cached";
     check(q, DType::BF16, fn, "q"); check(kcache, DType::BF16, fn, "kcache"); check(vcache, DType::BF16, fn, "vcache");
     check(o, DType::BF16, fn, "o");
@@ -193,16 +225,14 @@ void flash_attn_decode_cached(const Tensor& q, const Tensor& kcache, const Tenso
     if (q.numel() != 1LL * B * Hq * D || o.numel() != q.numel() || kcache.numel() != 1LL * B * Hkv * L_cap * D ||
         vcache.numel() != kcache.numel())
         throw std::invalid_argument("flash_attn_decode_cached: shape mismatch");
-    const long long ws_bytes = static_cast<long long>(b200attn_decode_workspace_bytes(B, L, Hq, Hkv, D, 0));
-    Tensor ws({(ws_bytes + 3) / 4}, DType::FP32, Device::Cuda);
+    const size_t ws_bytes = b200attn_decode_workspace_bytes(B, L, Hq, Hkv, D, 0);
     raise(b200attn_decode_cached(q.data(), kcache.data(), vcache.data(), o.data(), nullptr, B, L, L_cap, Hq, Hkv, D, 0.f, 0,
-                                 ws.data(), static_cast<size_t>(ws_bytes), nullptr),
+                                 cached_workspace(kWsDecode, ws_bytes, stream), ws_bytes, stream),
           fn);
-    raise(b200attn_last_device_status(nullptr), fn);  // the workspace is freed on return
 }
 
 void flash_attn_forward_kvcache(const Tensor& q, const Tensor& kcache, const Tensor& vcache, Tensor& ctx, Tensor& L, int B,
-                                int T, int L_cap, int Hq, int Hkv, int D) {
+                                int T, int L_cap, int Hq, int Hkv, int D, void* stream) {
     const char* fn = "flash_attn_forward_kvcache";
     check(q, DType::BF16, fn, "q"); check(kcache, DType::BF16, fn, "kcache"); check(vcache, DType::BF16, fn, "vcache");
     check(ctx, DType::BF16, fn, "ctx"); check(L, DType::FP32, fn, "L");
@@ -212,7 +242,7 @@ void flash_attn_forward_kvcache(const Tensor& q, const Tensor& kcache, const Ten
         kcache.numel() != 1LL * B * Hkv * L_cap * D || vcache.numel() != kcache.numel())
         throw std::invalid_argument("flash_attn_forward_kvcache: shape mismatch");
     raise(b200attn_fwd_kvcache(q.data(), kcache.data(), vcache.data(), ctx.data(), static_cast<float*>(L.data()), B, T, L_cap,
-                               Hq, Hkv, D, B200ATTN_LAYOUT_BHTD, 0.f, nullptr),
+                               Hq, Hkv, D, B200ATTN_LAYOUT_BHTD, 0.f, stream),
           fn);
 }
 

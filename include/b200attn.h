@@ -181,6 +181,16 @@ int b200attn_fwd_kvcache(const void* q, const void* kcache, const void* vcache, 
 int b200attn_decode_cached(const void* q, const void* kcache, const void* vcache, void* o, float* lse, int B, int L,
                            int L_cap, int Hq, int Hkv, int D, float softmax_scale, int n_splits, void* workspace,
                            size_t workspace_bytes, void* stream);
+/*
+ * Chunked prefill: T new tokens at positions pos0 .. pos0 + T - 1 attend over the pos0 tokens already cached and,
+ * causally, over themselves (append them with b200attn_kv_append at pos0 first).  q, o: [.., T, ..] in q_layout;
+ * lse [B, Hq, T].  Row t equals row pos0 + t of b200attn_fwd over pos0 + T tokens.  pos0 == 0 is
+ * b200attn_fwd_kvcache; pos0 + T > L_cap is B200ATTN_ERR_INVALID_ARG.  (The sampler it serves re-runs the whole
+ * window per token, llm/apps/infer_modern_gpt.cu:253-255.)
+ */
+int b200attn_fwd_kvcache_at(const void* q, const void* kcache, const void* vcache, void* o, float* lse, int B, int T,
+                            int pos0, int L_cap, int Hq, int Hkv, int D, int q_layout, float softmax_scale,
+                            void* stream);
 
 /*
  * The same two calls for sequences of different lengths (a batch that does not advance in lock step).

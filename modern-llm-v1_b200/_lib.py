@@ -50,6 +50,7 @@ SYMBOLS = (
     "b200attn_decode_default_splits",
     "b200attn_decode_cached",
     "b200attn_fwd_kvcache",
+    "b200attn_fwd_kvcache_at",
     "b200attn_kv_append",
     "b200attn_kv_append_at",
     "b200attn_item_deal",
@@ -105,6 +106,8 @@ def load() -> ctypes.CDLL:
     L.b200attn_decode_cached.restype = i
     L.b200attn_fwd_kvcache.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, i, f, vp]
     L.b200attn_fwd_kvcache.restype = i
+    L.b200attn_fwd_kvcache_at.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, i, i, f, vp]
+    L.b200attn_fwd_kvcache_at.restype = i
     L.b200attn_kv_append.argtypes = [vp, vp, vp, i, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, f, vp]
     L.b200attn_kv_append.restype = i
     L.b200attn_kv_append_at.argtypes = [vp, vp, vp, i, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, f, vp]

@@ -36,6 +36,8 @@ namespace b200attn {
 struct FwdParams {
     int B, T, Hq, Hkv, group;
     int n_qtiles;
+    int kv_off;        // keys in front of the first query row: query row t sees keys 0 .. kv_off + t (0 when q and k
+                       // cover the same tokens; the cached tokens' count when a chunk of new tokens attends over a KV cache)
     float scale;       // softmax scale
     float scale_log2;  // scale * log2(e)
     float* lse;        // [B, Hq, T]
@@ -114,7 +116,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     auto item_qt = [&](int id) { return p.n_qtiles - 1 - int(fastdiv(unsigned(id), p.div_bh)); };
     auto item_b = [&](int id) { return int(fastdiv(unsigned(item_rest(id)), p.div_h)); };
     auto item_h = [&](int id) { return item_rest(id) - item_b(id) * p.Hq; };
-    auto item_nkv = [&](int id) { return (min(p.T, item_qt(id) * 128 + 128) + Cfg::kKeys - 1) / Cfg::kKeys; };
+    auto item_nkv = [&](int id) { return (p.kv_off + min(p.T, item_qt(id) * 128 + 128) + Cfg::kKeys - 1) / Cfg::kKeys; };
 
     B200ATTN_TRACE_BEGIN(0);
     // Set-up with one CTA-wide barrier: one lane of the producer warp initialises every mbarrier while
@@ -426,9 +428,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 tmem_ld_x32(t_s + 32, &sr[32]);
                 tmem_wait_ld();
                 const int kbase = j * Cfg::kKeys;  // first key of this tile
-                if (kbase + Cfg::kKeys - 1 > q0) {
-                    // tile touches the diagonal: key kbase + c is visible to query q0 + row iff it is <= the query
-                    const int lim = q0 + row - kbase;  // columns c <= lim are visible
+                if (kbase + Cfg::kKeys - 1 > q0 + p.kv_off) {
+                    // tile touches the diagonal: key kbase + c is visible to query q0 + row iff it is <= the query's
+                    // own position kv_off + q0 + row
+                    const int lim = p.kv_off + q0 + row - kbase;  // columns c <= lim are visible
 #pragma unroll
                     for (int c = 0; c < 64; ++c)
                         if (c > lim) sr[c] = 0xff800000u;  // -inf

@@ -251,7 +251,7 @@ namespace {
 
 // The forward with K and V at their own strides (sk): the training call passes the strides of `layout`, the
 // prefill over a KV cache those of the cache.
-int fwd_run(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T, int Hq, int Hkv, int D,
+int fwd_run(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T, int kv_off, int Hq, int Hkv, int D,
             int layout, const Strides& sk, float softmax_scale, void* stream) {
     int rc = check_common(B, T, Hq, Hkv, D, layout);
     if (rc) return rc;
@@ -262,8 +262,8 @@ int fwd_run(const void* q, const void* k, const void* v, void* o, float* lse, in
     const Strides sq = strides_for(layout, Hq, T, D);
     CUtensorMap tq, tk, tv;
     if (!make_tmap_bf16_4d(&tq, q, D, T, Hq, B, sq.t, sq.h, sq.b, 128) ||
-        !make_tmap_bf16_4d(&tk, k, D, T, Hkv, B, sk.t, sk.h, sk.b, 64) ||
-        !make_tmap_bf16_4d(&tv, v, D, T, Hkv, B, sk.t, sk.h, sk.b, 64))
+        !make_tmap_bf16_4d(&tk, k, D, kv_off + T, Hkv, B, sk.t, sk.h, sk.b, 64) ||
+        !make_tmap_bf16_4d(&tv, v, D, kv_off + T, Hkv, B, sk.t, sk.h, sk.b, 64))
         return B200ATTN_ERR_TENSOR_MAP;
     FwdParams p;
     p.B = B;
@@ -272,6 +272,7 @@ int fwd_run(const void* q, const void* k, const void* v, void* o, float* lse, in
     p.Hkv = Hkv;
     p.group = Hq / Hkv;
     p.n_qtiles = (T + 127) / 128;
+    p.kv_off = kv_off;
     p.scale = softmax_scale > 0.f ? softmax_scale : 1.f / sqrtf((float)D);
     p.scale_log2 = p.scale * 1.4426950408889634f;
     p.lse = lse;
@@ -290,15 +291,21 @@ int fwd_run(const void* q, const void* k, const void* v, void* o, float* lse, in
 extern "C" int b200attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T, int Hq,
                             int Hkv, int D, int layout, float softmax_scale, void* stream) {
     if (T <= 0 || Hkv <= 0 || D <= 0) return B200ATTN_ERR_INVALID_ARG;
-    return fwd_run(q, k, v, o, lse, B, T, Hq, Hkv, D, layout, strides_for(layout, Hkv, T, D), softmax_scale, stream);
+    return fwd_run(q, k, v, o, lse, B, T, 0, Hq, Hkv, D, layout, strides_for(layout, Hkv, T, D), softmax_scale, stream);
 }
 
 extern "C" int b200attn_fwd_kvcache(const void* q, const void* kcache, const void* vcache, void* o, float* lse, int B,
                                     int T, int L_cap, int Hq, int Hkv, int D, int q_layout, float softmax_scale,
                                     void* stream) {
-    if (T <= 0 || Hkv <= 0 || D <= 0 || L_cap < T) return B200ATTN_ERR_INVALID_ARG;
-    return fwd_run(q, kcache, vcache, o, lse, B, T, Hq, Hkv, D, q_layout, strides_for(B200ATTN_LAYOUT_BHTD, Hkv, L_cap, D),
-                   softmax_scale, stream);
+    return b200attn_fwd_kvcache_at(q, kcache, vcache, o, lse, B, T, 0, L_cap, Hq, Hkv, D, q_layout, softmax_scale, stream);
+}
+
+extern "C" int b200attn_fwd_kvcache_at(const void* q, const void* kcache, const void* vcache, void* o, float* lse, int B,
+                                       int T, int pos0, int L_cap, int Hq, int Hkv, int D, int q_layout,
+                                       float softmax_scale, void* stream) {
+    if (T <= 0 || pos0 < 0 || Hkv <= 0 || D <= 0 || (long long)pos0 + T > L_cap) return B200ATTN_ERR_INVALID_ARG;
+    return fwd_run(q, kcache, vcache, o, lse, B, T, pos0, Hq, Hkv, D, q_layout,
+                   strides_for(B200ATTN_LAYOUT_BHTD, Hkv, L_cap, D), softmax_scale, stream);
 }
 
 namespace {

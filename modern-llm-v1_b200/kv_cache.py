@@ -111,7 +111,8 @@ class KVCache:
     def attend(self, layer: int, q, ctx, lse, n_new: int = 1, softmax_scale=None) -> None:
         """Attention of the n_new appended tokens over the length + n_new cached ones.  q, ctx: [B, Hq, n_new, D]
         BF16; lse: [B, Hq, n_new] FP32 (may be None for n_new == 1).  n_new == 1 is the split-KV decode kernel;
-        n_new > 1 is the causal forward over a prompt and needs an empty cache before it (length == 0)."""
+        n_new > 1 is the causal forward of the new tokens over the cache: a whole prompt into an empty cache, or a
+        further chunk of it behind the tokens already cached (chunked prefill; lock-step sequences only)."""
         fn = "KVCache.attend"
         self._layer(fn, layer)
         bf = torch.bfloat16
@@ -140,13 +141,13 @@ class KVCache:
                                                 self.L_cap, Hq, Hkv, D, scale, 0, ws.data_ptr(), ws.numel(),
                                                 _stream_ptr())
             else:
-                if self.length != 0:
-                    raise ValueError(f"{fn}: several tokens at once only into an empty cache (prompt)")
+                if self.lengths is not None:
+                    raise ValueError(f"{fn}: several tokens at once only while the sequences advance in lock step")
                 if lse is None:
                     raise ValueError(f"{fn}: lse is required for n_new > 1")
-                rc = lib.b200attn_fwd_kvcache(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), ctx.data_ptr(),
-                                              lse.data_ptr(), B, n_new, self.L_cap, Hq, Hkv, D, _lib.LAYOUTS["BHTD"],
-                                              scale, _stream_ptr())
+                rc = lib.b200attn_fwd_kvcache_at(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), ctx.data_ptr(),
+                                                 lse.data_ptr(), B, n_new, self.length, self.L_cap, Hq, Hkv, D,
+                                                 _lib.LAYOUTS["BHTD"], scale, _stream_ptr())
         _lib.check(rc, fn)
 
     def advance(self, n_new: int = 1) -> None:

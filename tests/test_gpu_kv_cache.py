@@ -98,6 +98,43 @@ def test_prefill_over_the_cache_equals_the_forward_on_dense_tensors(B, T, Hq, Hk
     assert_close("LSE", lse, wl, max_abs=TOL_LSE, rel_l2=1.0)
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,D,chunks,L_cap", [
+    (2, 6, 2, 64, (200, 1, 130, 57, 300), 700),     # prompt in chunks of uneven size, one of a single token
+    (1, 8, 2, 128, (129, 128, 64), 400),
+    (3, 4, 4, 64, (64, 64, 64, 64), 256),           # chunk boundaries on the 64-key tile boundaries
+])
+def test_chunked_prefill_equals_the_rows_of_the_whole_forward(B, Hq, Hkv, D, chunks, L_cap):
+    # several new tokens against a non-empty cache: every chunk's rows must be the rows of one causal forward over
+    # the whole prompt (oracle on the cached, BF16-rounded q, k, v)
+    T = sum(chunks)
+    xq, xk, xv, gq, gk = _inputs(B, T, Hq, Hkv, D, torch.float32, 21)
+    cache = m.KVCache(1, B, Hq, Hkv, D, L_cap)
+    cache.k.fill_(float("nan"))  # rows that are not cached yet must never reach a result
+    cache.v.fill_(float("nan"))
+    qs, ctxs, lses = [], [], []
+    pos = 0
+    for n in chunks:
+        sl = slice(pos, pos + n)
+        q = _append(cache, 0, xq[:, sl], xk[:, sl], xv[:, sl], gq, gk)
+        ctx = torch.full_like(q, float("nan"))
+        lse = torch.full((B, Hq, n), float("nan"), device="cuda")
+        cache.attend(0, q, ctx, lse, n_new=n)
+        cache.advance(n)
+        qs.append(q), ctxs.append(ctx), lses.append(lse)
+        pos += n
+    m.device_status()
+    q, ctx, lse = torch.cat(qs, 2), torch.cat(ctxs, 2), torch.cat(lses, 2)
+    k, v = cache.k[0, :, :, :T].contiguous(), cache.v[0, :, :, :T].contiguous()
+    wo, wl = ao.attn_fwd_c(np32(q), np32(k), np32(v))
+    assert_close("O", ctx, wo)
+    assert_close("LSE", lse, wl, max_abs=TOL_LSE, rel_l2=1.0)
+    # and close to the one-shot forward of this library (the tiles fall differently, so not bit for bit)
+    ctx2, lse2 = torch.empty_like(ctx), torch.empty_like(lse)
+    m.flash_attn_forward_gqa(q.contiguous(), k, v, ctx2, lse2, B, T, Hq, Hkv, D)
+    m.device_status()
+    assert_close("O vs one-shot", ctx, np32(ctx2), max_abs=1e-2, rel_l2=3e-3)
+
+
 def test_generation_loop_matches_the_full_forward_per_token():
     """Prompt of 70 tokens, then 30 single-token steps: every step's output equals the last row of a full
     causal forward over the tokens so far (what the reference's sampler computes each step), inside the bar."""
@@ -164,9 +201,10 @@ def test_capacity_and_argument_errors():
     cache.advance(3)
     with pytest.raises(ValueError, match="exceed the capacity"):
         cache.append(0, xq, xk, xk, g, g, q)
-    with pytest.raises(ValueError, match="empty cache"):
-        cache.length = 1
-        cache.attend(0, q, q, torch.zeros((1, 2, 3), device="cuda"), n_new=3)
+    with pytest.raises(ValueError, match="n_new out of range"):
+        cache.length = 2
+        cache.attend(0, q, q, torch.zeros((1, 2, 3), device="cuda"), n_new=3)  # 2 + 3 tokens > capacity 4
+    cache.length = 3
     lib = m._lib.load()
     rc = lib.b200attn_kv_append(xq.data_ptr(), xk.data_ptr(), xk.data_ptr(), 0, q.data_ptr(), cache.k.data_ptr(),
                                 cache.v.data_ptr(), g.data_ptr(), g.data_ptr(), cache.cos.data_ptr(),

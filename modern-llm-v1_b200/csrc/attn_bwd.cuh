@@ -132,20 +132,27 @@ __device__ __forceinline__ void stage_row_chunk(uint8_t* tile, int row, int col,
 }
 
 // ---------------------------------------------------------------------------------------
-// dQ pass (D = 64): persistent CTAs, two per SM.  A CTA walks a static list of work items
-// (item = one 128-row query tile of one (batch, query head); items are ordered heaviest first and
-// dealt round-robin), and every pipeline keeps running across item boundaries: the K/V ring
-// prefetches the next item's tiles, the MMA warp issues the next item's first products while the
-// compute warps write the previous item's dQ rows.  The O tile travels with Q and dO, so the
-// preprocess D = rowsum(O * dO) (flash_attn_compute_D_kernel, llm/src/model/flash_attn.cu:150-172)
-// is shared-memory work at the head of each item; D and L * log2(e) are also left in the workspace
-// for the dK/dV pass, which therefore has to run after this kernel.
+// dQ pass (D = 64): persistent CTAs, two per SM.  A CTA walks a list of work items (item = one 128-row query tile
+// of one (batch, query head); items are ordered heaviest first), and every pipeline keeps running across item
+// boundaries.  The O tile travels with Q and dO, so the preprocess D = rowsum(O * dO)
+// (flash_attn_compute_D_kernel, llm/src/model/flash_attn.cu:150-172) is shared-memory work at the head of each
+// item; D and L * log2(e) are also left in the workspace for the dK/dV pass, which therefore has to run after this
+// kernel.
 //
-// Roles (320 threads): warps 0-7 compute (thread owns query row (warp % 4) * 32 + lane == TMEM lane
-// and the 32 key columns of its part warp / 4), warp 8 TMA producer, warp 9 TMEM allocation + MMA
-// issue (converged warps, one elected lane issues).
-// TMEM (256 columns): S buffer 0 [0,64), S buffer 1 [64,128) (dS as BF16 over the first 16 columns
-// of each part's range), dP [128,192), dQ accumulator [192,256).
+// Q and dO in tensor memory.  Every D = 64 kernel here is bound by the shared-memory data path (a product M128 N64
+// K16 with both operands in shared memory fetches 4 KB of A and 2 KB of B for 32 clocks of math), and Q and dO are
+// the A operands of every S = Q K^T and dP = dO V^T product of an item.  The compute warps therefore copy the two
+// tiles once per item from shared memory into tensor memory (the 128 bytes of row r are the 32 BF16-pair columns
+// of lane r as they stand), all three products of a key tile take their A operand from tensor memory, and the
+// shared-memory tiles are free for the NEXT item's loads while this item is still being worked on.
+//
+// Roles (320 threads): warps 0-7 compute (thread owns query row (warp % 4) * 32 + lane == TMEM lane and the 32 key
+// columns of its part warp / 4), warp 8 TMA producer, warp 9 TMEM allocation + MMA issue (converged warps, one
+// elected lane issues).
+// TMEM (256 columns): S [0,64), dP [64,128) (dS as BF16 over the first 16 columns of each part's range), dQ
+// accumulator [128,192), Q [192,224), dO [224,256).  There is one S buffer: the compute warps read a tile's scores
+// into registers in one go and hand the buffer back at once, so the next tile's Q K^T runs under this tile's
+// exponentials; dS overwrites dP, so the next dP product follows the dQ product that consumes it.
 // ---------------------------------------------------------------------------------------
 template <int D>
 struct DqCfg {
@@ -159,7 +166,7 @@ struct DqCfg {
     static constexpr int kSmemBytes = 3 * kQTileBytes + 2 * kStages * kKVTileBytes + 512 + 1024;  // Q, dO, O + ring + barriers
     static constexpr int kTmemCols = 256;
     static constexpr int kCtasPerSm = 2;
-    static constexpr int kColS0 = 0, kColS1 = 64, kColDP = 128, kColAcc = 192;
+    static constexpr int kColS = 0, kColDP = 64, kColAcc = 128, kColQ = 192, kColDO = 224;
     static constexpr int kParts = 2;
     static constexpr int kPartCols = kKeys / kParts;  // 32
     static constexpr int kComputeThreads = 128 * kParts;
@@ -172,6 +179,7 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, DqCfg<D>::kCtasPerSm)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                    const __grid_constant__ CUtensorMap tmO, const BwdParams p, const __grid_constant__ ItemTable tab) {
+    static_assert(D == 64, "the persistent dQ pass keeps Q and dO in 64 tensor-memory columns: D = 64 only");
     using Cfg = DqCfg<D>;
     constexpr int NST = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -182,15 +190,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     uint8_t* sK = sO + Cfg::kQTileBytes;         // [NST]
     uint8_t* sV = sK + NST * Cfg::kKVTileBytes;  // [NST]
     uint64_t* bars = reinterpret_cast<uint64_t*>(sV + NST * Cfg::kKVTileBytes);
-    uint64_t* bar_q = bars + 0;         // Q, dO, O of an item have landed            (phase: item)
-    uint64_t* bar_q_free = bars + 1;    // every MMA reading Q, dO of an item is done (phase: item)
-    uint64_t* bar_s_full = bars + 2;    // [2] per S buffer                            (phase: tile / 2)
-    uint64_t* bar_ds_full = bars + 4;   // [2] per S buffer: dS written               (phase: tile / 2)
-    uint64_t* bar_dp_full = bars + 6;   //                                             (phase: tile)
-    uint64_t* bar_dp_free = bars + 7;   // dP read into registers                      (phase: tile)
-    uint64_t* bar_acc = bars + 8;       // dQ accumulator of an item complete          (phase: item)
-    uint64_t* bar_acc_free = bars + 9;  // dQ accumulator read by the epilogue         (phase: item)
-    uint64_t* bar_o_free = bars + 10;   // the O tile has been read by the preprocess  (phase: item)
+    uint64_t* bar_q = bars + 0;         // Q, dO, O of an item have landed in shared memory      (phase: item)
+    uint64_t* bar_qs_free = bars + 1;   // the compute warps have read those three tiles          (phase: item)
+    uint64_t* bar_qt_full = bars + 2;   // Q and dO of an item are in tensor memory               (phase: item)
+    uint64_t* bar_s_full = bars + 3;    //                                                         (phase: tile)
+    uint64_t* bar_s_loaded = bars + 4;  // S is in registers: the buffer may be overwritten       (phase: tile)
+    uint64_t* bar_dp_full = bars + 5;   //                                                         (phase: tile)
+    uint64_t* bar_ds_full = bars + 6;   // dS written over dP                                      (phase: tile)
+    uint64_t* bar_acc = bars + 8;       // dQ accumulator of an item complete                      (phase: item)
+    uint64_t* bar_acc_free = bars + 9;  // dQ accumulator read by the epilogue                     (phase: item)
     uint64_t* bar_kv_full = bars + 14;        // [NST]
     uint64_t* bar_kv_free = bars + 14 + NST;  // [NST]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14 + 2 * NST);
@@ -217,16 +225,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tma_prefetch_desc(&tmdO);
         tma_prefetch_desc(&tmO);
         mbar_init(bar_q, 1);
-        mbar_init(bar_q_free, 1);
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&bar_s_full[i], 1);
-            mbar_init(&bar_ds_full[i], Cfg::kComputeThreads);
-        }
+        mbar_init(bar_qs_free, Cfg::kComputeThreads);
+        mbar_init(bar_qt_full, Cfg::kComputeThreads);
+        mbar_init(bar_s_full, 1);
+        mbar_init(bar_s_loaded, Cfg::kComputeThreads);
         mbar_init(bar_dp_full, 1);
-        mbar_init(bar_dp_free, Cfg::kComputeThreads);
+        mbar_init(bar_ds_full, Cfg::kComputeThreads);
         mbar_init(bar_acc, 1);
         mbar_init(bar_acc_free, Cfg::kComputeThreads);
-        mbar_init(bar_o_free, Cfg::kComputeThreads);
         for (int s = 0; s < NST; ++s) {
             mbar_init(&bar_kv_full[s], 1);
             mbar_init(&bar_kv_free[s], 1);
@@ -265,17 +271,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             // ring has been filled for this item
             const int j_next = max(min(n_kv, NST) - 1, n_kv - 2);
             int id_new = n_items;
-            if (n > 0) ok = mbar_wait_warp(bar_q_free, (n - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
-            if (ok && n > 0) ok = mbar_wait_warp(bar_o_free, (n - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
+            // the three tiles in shared memory are free as soon as the previous item has been copied out of them
+            if (n > 0) ok = mbar_wait_warp(bar_qs_free, (n - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE);
             if (!ok) break;
             if (elect_one()) {
                 mbar_arrive_expect_tx(bar_q, 3 * Cfg::kQTileBytes);
-#pragma unroll
-                for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
-                    tma_load_4d(sQ + bx * Cfg::kQBoxBytes, &tmQ, bar_q, bx * 64, qt * 128, h, b);
-                    tma_load_4d(sdO + bx * Cfg::kQBoxBytes, &tmdO, bar_q, bx * 64, qt * 128, h, b);
-                    tma_load_4d(sO + bx * Cfg::kQBoxBytes, &tmO, bar_q, bx * 64, qt * 128, h, b);
-                }
+                tma_load_4d(sQ, &tmQ, bar_q, 0, qt * 128, h, b);
+                tma_load_4d(sdO, &tmdO, bar_q, 0, qt * 128, h, b);
+                tma_load_4d(sO, &tmO, bar_q, 0, qt * 128, h, b);
             }
             __syncwarp();
             for (int j = 0; j < n_kv; ++j, ++g) {
@@ -284,13 +287,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 if (!ok) break;
                 if (elect_one()) {
                     mbar_arrive_expect_tx(&bar_kv_full[s], 2 * Cfg::kKVTileBytes);
-#pragma unroll
-                    for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
-                        tma_load_4d(sK + s * Cfg::kKVTileBytes + bx * Cfg::kKVBoxBytes, &tmK, &bar_kv_full[s], bx * 64,
-                                    j * Cfg::kKeys, hk, b);
-                        tma_load_4d(sV + s * Cfg::kKVTileBytes + bx * Cfg::kKVBoxBytes, &tmV, &bar_kv_full[s], bx * 64,
-                                    j * Cfg::kKeys, hk, b);
-                    }
+                    tma_load_4d(sK + s * Cfg::kKVTileBytes, &tmK, &bar_kv_full[s], 0, j * Cfg::kKeys, hk, b);
+                    tma_load_4d(sV + s * Cfg::kKVTileBytes, &tmV, &bar_kv_full[s], 0, j * Cfg::kKeys, hk, b);
                 }
                 __syncwarp();
                 if (j == j_next) {
@@ -308,39 +306,35 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (ok && lane == 0) sched_finish(p.sched, int(gridDim.x));
     } else if (warp == Cfg::kMmaWarp) {
         // ------------------------------------------------------------------ MMA issuer
-        constexpr uint32_t idesc_s = make_idesc_bf16(128, Cfg::kKeys, 0, 0);
-        constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
-        const uint64_t q_desc = make_sdesc_sw128(smem_u32(sQ), 16, 1024);
-        const uint64_t do_desc = make_sdesc_sw128(smem_u32(sdO), 16, 1024);
-        // g numbers this CTA's key tiles across all its items: ring stage g % NST, S buffer g & 1
-        auto issue_s = [&](int g) -> bool {  // S(g) = Q K^T
+        constexpr uint32_t idesc_s = make_idesc_bf16(128, Cfg::kKeys, 0, 0);  // A in TMEM, B (K or V tile) K-major
+        constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);         // A in TMEM, B (K tile) MN-major
+        // g numbers this CTA's key tiles across all its items: ring stage g % NST
+        auto issue_s = [&](int g) -> bool {  // S(g) = Q K^T; the buffer still holds S(g - 1) until it has been read
             const int s = g % NST;
-            if (!mbar_wait_warp(&bar_kv_full[s], (g / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD))
+            if (g > 0 && !mbar_wait_warp(bar_s_loaded, uint32_t(g - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX))
                 return false;
+            if (!mbar_wait_warp(&bar_kv_full[s], (g / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD)) return false;
             tc_fence_after_sync();
             const uint64_t k_desc = make_sdesc_sw128(smem_u32(sK + s * Cfg::kKVTileBytes), 16, 1024);
             if (elect_one()) {
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks)
-                    umma_ss(tmem + ((g & 1) ? Cfg::kColS1 : Cfg::kColS0), q_desc + kmajor_step(ks, Cfg::kQBoxBytes),
-                            k_desc + kmajor_step(ks, Cfg::kKVBoxBytes), idesc_s, ks > 0);
-                umma_commit(&bar_s_full[g & 1]);
+                    umma_ts(tmem + Cfg::kColS, tmem + Cfg::kColQ + ks * 8, k_desc + kmajor_step(ks, Cfg::kKVBoxBytes), idesc_s, ks > 0);
+                umma_commit(bar_s_full);
             }
             __syncwarp();
             return true;
         };
-        // dP(g) = dO V^T; tile g's loads have landed (S(g) was issued).  `last` = last tile of the item:
-        // after it no MMA reads Q or dO of the item any more.
-        auto issue_dp = [&](int g, bool last) {
+        // dP(g) = dO V^T; tile g's loads have landed (S(g) was issued), and the product that read dS(g - 1) out of
+        // this block was issued before (the products execute in order)
+        auto issue_dp = [&](int g) {
             const int s = g % NST;
             const uint64_t v_desc = make_sdesc_sw128(smem_u32(sV + s * Cfg::kKVTileBytes), 16, 1024);
             if (elect_one()) {
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks)
-                    umma_ss(tmem + Cfg::kColDP, do_desc + kmajor_step(ks, Cfg::kQBoxBytes),
-                            v_desc + kmajor_step(ks, Cfg::kKVBoxBytes), idesc_s, ks > 0);
+                    umma_ts(tmem + Cfg::kColDP, tmem + Cfg::kColDO + ks * 8, v_desc + kmajor_step(ks, Cfg::kKVBoxBytes), idesc_s, ks > 0);
                 umma_commit(bar_dp_full);
-                if (last) umma_commit(bar_q_free);
             }
             __syncwarp();
         };
@@ -349,27 +343,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int id; ok && (id = get_item(n)) >= 0; ++n) {
             const int n_kv = item_nkv(id);
             B200ATTN_STAMP(lane == 0, 440 + 2 * n);
-            ok = mbar_wait_warp(bar_q, n & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+            ok = mbar_wait_warp(bar_qt_full, n & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
             B200ATTN_STAMP(lane == 0, 441 + 2 * n);
             if (ok) ok = issue_s(g0);
-            // the dP block still holds the previous item's last dP until the compute warps have read it
-            if (ok && g0 > 0) ok = mbar_wait_warp(bar_dp_free, (g0 - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
             if (!ok) break;
-            tc_fence_after_sync();
-            issue_dp(g0, n_kv == 1);
-            if (n_kv > 1) ok = issue_s(g0 + 1);
+            issue_dp(g0);
             for (int j = 0; j < n_kv && ok; ++j) {
                 const int g = g0 + j;
                 const int s = g % NST;
                 if (j + 1 < n_kv) {
-                    // next dP as soon as this one has been read into registers
-                    ok = mbar_wait_warp(bar_dp_free, g & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+                    ok = issue_s(g + 1);  // as soon as S(g) is in registers
                     if (!ok) break;
-                    B200ATTN_STAMP(lane == 0, 240 + 8 * g + 4);
-                    tc_fence_after_sync();
-                    issue_dp(g + 1, j + 2 == n_kv);
                 }
-                ok = mbar_wait_warp(&bar_ds_full[g & 1], uint32_t(g >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+                ok = mbar_wait_warp(bar_ds_full, uint32_t(g) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
                 if (!ok) break;
                 B200ATTN_STAMP(lane == 0, 240 + 8 * g + 5);
                 // the accumulator still belongs to the previous item's epilogue until it has been read
@@ -384,18 +370,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
                     for (int ks = 0; ks < Cfg::kKeys / 16; ++ks) {
                         constexpr int kStepsPerPart = Cfg::kPartCols / 16;
-                        const uint32_t a_col = ((g & 1) ? Cfg::kColS1 : Cfg::kColS0) + (ks / kStepsPerPart) * Cfg::kPartCols +
-                                               (ks % kStepsPerPart) * 8;
-                        umma_ts(tmem + Cfg::kColAcc, tmem + a_col, kmn_desc + uint64_t(ks * 128), idesc_acc,
-                                (j > 0) || (ks > 0));
+                        const uint32_t a_col = Cfg::kColDP + (ks / kStepsPerPart) * Cfg::kPartCols + (ks % kStepsPerPart) * 8;
+                        umma_ts(tmem + Cfg::kColAcc, tmem + a_col, kmn_desc + uint64_t(ks * 128), idesc_acc, (j > 0) || (ks > 0));
                     }
                     umma_commit(&bar_kv_free[s]);
                     if (j + 1 == n_kv) umma_commit(bar_acc);
                 }
                 __syncwarp();
                 B200ATTN_STAMP(lane == 0, 240 + 8 * g + 6);
-                if (j + 2 < n_kv) ok = issue_s(g + 2);
-                B200ATTN_STAMP(lane == 0, 240 + 8 * g + 7);
+                if (j + 1 < n_kv) issue_dp(g + 1);
             }
             g0 += n_kv;
         }
@@ -407,55 +390,76 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const int row = w4 * 32 + lane;  // query row in the tile == TMEM lane
         const uint32_t lane_base = uint32_t(w4 * 32) << 16;
         const int c0 = part * Cfg::kPartCols;  // first key column of this thread's part
-        int g0 = 0, n = 0;
         bool ok = true;
-        for (int id; ok && (id = get_item(n)) >= 0; ++n) {
-            const int qt = item_qt(id), h = item_h(id), b = item_b(id), n_kv = item_nkv(id);
-            const int q0 = qt * 128;
-            // preprocess of this row from the tiles in shared memory: D = rowsum(O * dO); L * log2(e)
+        float dv = 0.f, lse2 = INFINITY;  // of the item whose Q and dO are in tensor memory
+        // Head of this CTA's n-th item: the preprocess of this row from the tiles in shared memory
+        // (D = rowsum(O * dO); L * log2(e)), and Q (part 0) / dO (part 1) into tensor memory.  All S and dP products
+        // of the previous item have completed when this runs (their results were waited for).
+        auto item_head = [&](int n_item, int id) -> bool {
+            const int q0 = item_qt(id) * 128, h = item_h(id), b = item_b(id);
             const bool in_range = q0 + row < p.T;
-            // (the load is issued here and first used after the preprocess below, so that its latency
-            // overlaps the wait for the item's tiles)
+            // (issued here and first used after the wait below, so that its latency overlaps the wait)
             const float lse_raw = in_range ? p.lse[(size_t(b) * p.Hq + h) * p.T + q0 + row] : 0.f;
-            B200ATTN_STAMP(tid == 0, 400 + 4 * n + 0);
-            ok = mbar_wait_warp(bar_q, n & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-            if (!ok) break;
-            B200ATTN_STAMP(tid == 0, 400 + 4 * n + 1);
-            float dv = 0.f;
+            B200ATTN_STAMP(tid == 0, 400 + 4 * n_item + 0);
+            if (!mbar_wait_warp(bar_q, n_item & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD)) return false;
+            B200ATTN_STAMP(tid == 0, 400 + 4 * n_item + 1);
+            tc_fence_after_sync();
+            float acc = 0.f;
+            uint32_t tw[32];  // this row of Q (part 0) or dO (part 1) as it goes into tensor memory
 #pragma unroll
             for (int c = 0; c < D / 8; ++c) {
-                const uint32_t off = (c >> 3) * Cfg::kQBoxBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4);
+                const uint32_t off = row * 128 + ((c ^ (row & 7)) << 4);
                 const uint4 a = *reinterpret_cast<const uint4*>(sO + off);
                 const uint4 gq = *reinterpret_cast<const uint4*>(sdO + off);
                 const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
                 const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    dv = fmaf(__uint_as_float(aw[e] << 16), __uint_as_float(gw[e] << 16), dv);
-                    dv = fmaf(__uint_as_float(aw[e] & 0xffff0000u), __uint_as_float(gw[e] & 0xffff0000u), dv);
+                    acc = fmaf(__uint_as_float(aw[e] << 16), __uint_as_float(gw[e] << 16), acc);
+                    acc = fmaf(__uint_as_float(aw[e] & 0xffff0000u), __uint_as_float(gw[e] & 0xffff0000u), acc);
+                }
+                if (part == 0) {
+                    const uint4 qv = *reinterpret_cast<const uint4*>(sQ + off);
+                    tw[4 * c] = qv.x, tw[4 * c + 1] = qv.y, tw[4 * c + 2] = qv.z, tw[4 * c + 3] = qv.w;
+                } else {
+                    tw[4 * c] = gq.x, tw[4 * c + 1] = gq.y, tw[4 * c + 2] = gq.z, tw[4 * c + 3] = gq.w;
                 }
             }
-            mbar_arrive(bar_o_free);  // the O tile may be overwritten by the next item's load
+            mbar_arrive(bar_qs_free);  // the three tiles may be overwritten by the next item's loads
+            tmem_st_x32(tmem + lane_base + (part == 0 ? Cfg::kColQ : Cfg::kColDO), tw);
             // exp2(x - inf) = 0: padding query rows contribute nothing
-            const float lse2 = in_range ? lse_raw * 1.4426950408889634f : INFINITY;
+            lse2 = in_range ? lse_raw * 1.4426950408889634f : INFINITY;
+            dv = in_range ? acc : 0.f;
             if (part == 0) {
                 const size_t vrow = (size_t(b) * p.Hq + h) * p.Tpad + q0 + row;
                 p.lse2_w[vrow] = lse2;
-                p.dvec_w[vrow] = in_range ? dv : 0.f;
+                p.dvec_w[vrow] = dv;
             }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(bar_qt_full);
+            return true;
+        };
+        int g0 = 0, n = 0;
+        int id = get_item(0);
+        if (id >= 0) ok = item_head(0, id);
+        while (ok && id >= 0) {
+            const int qt = item_qt(id), h = item_h(id), b = item_b(id), n_kv = item_nkv(id);
+            const int q0 = qt * 128;
             for (int j = 0; j < n_kv; ++j) {
                 const int g = g0 + j;
-                const uint32_t t_s = tmem + lane_base + ((g & 1) ? Cfg::kColS1 : Cfg::kColS0) + c0;
-                ok = mbar_wait_warp(&bar_s_full[g & 1], uint32_t(g >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+                ok = mbar_wait_warp(bar_s_full, uint32_t(g) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
                 if (!ok) break;
                 B200ATTN_STAMP(tid == 0, 240 + 8 * g + 0);
                 tc_fence_after_sync();
-                // phase A: P from S
+                // phase A: P from S (the scores leave tensor memory in one go)
                 float pr[32];
                 {
                     uint32_t sv[32];
-                    tmem_ld_x32(t_s, sv);
+                    tmem_ld_x32(tmem + lane_base + Cfg::kColS + c0, sv);
                     tmem_wait_ld();
+                    tc_fence_before_sync();
+                    mbar_arrive(bar_s_loaded);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) pr[i] = ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse2));
                 }
@@ -467,30 +471,36 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                         if (i > lim) pr[i] = 0.f;
                 }
                 B200ATTN_STAMP(tid == 0, 240 + 8 * g + 1);
-                ok = mbar_wait_warp(bar_dp_full, g & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+                ok = mbar_wait_warp(bar_dp_full, uint32_t(g) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
                 if (!ok) break;
                 B200ATTN_STAMP(tid == 0, 240 + 8 * g + 2);
                 tc_fence_after_sync();
-                // phase B: dS = P (dP - D), written as BF16 over the part's first 16 columns of the S buffer
+                // phase B: dS = P (dP - D), written as BF16 over the part's first 16 columns of the dP block
                 {
                     uint32_t dp[32], pk[16];
-                    tmem_ld_x32(tmem + lane_base + Cfg::kColDP + c0, dp);
+                    const uint32_t t_dp = tmem + lane_base + Cfg::kColDP + c0;
+                    tmem_ld_x32(t_dp, dp);
                     tmem_wait_ld();
-                    tc_fence_before_sync();
-                    mbar_arrive(bar_dp_free);  // dP is in registers: the next dP may overwrite the block
 #pragma unroll
                     for (int i = 0; i < 16; ++i)
                         pk[i] = pack_bf16x2(pr[2 * i] * (__uint_as_float(dp[2 * i]) - dv),
                                             pr[2 * i + 1] * (__uint_as_float(dp[2 * i + 1]) - dv));
-                    tmem_st_x16(t_s, pk);
+                    tmem_st_x16(t_dp, pk);
                 }
                 tmem_wait_st();
                 tc_fence_before_sync();
-                mbar_arrive(&bar_ds_full[g & 1]);
+                mbar_arrive(bar_ds_full);
                 B200ATTN_STAMP(tid == 0, 240 + 8 * g + 3);
             }
             if (!ok) break;
             g0 += n_kv;
+            // The next item's head before this item's epilogue: its first products then run while the dQ rows are
+            // written.  (dv and lse2 change here; the epilogue below needs neither.)
+            const int id_next = get_item(n + 1);
+            if (id_next >= 0) {
+                ok = item_head(n + 1, id_next);
+                if (!ok) break;
+            }
             // epilogue of the item: dQ rows (times scale) -> BF16 -> global memory; each part writes D / 2 columns
             ok = mbar_wait_warp(bar_acc, n & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
             if (!ok) break;
@@ -498,8 +508,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             tc_fence_after_sync();
             constexpr int kCols = D / Cfg::kParts;
             uint32_t v[kCols];
-#pragma unroll
-            for (int c = 0; c < kCols / 32; ++c) tmem_ld_x32(tmem + lane_base + Cfg::kColAcc + part * kCols + c * 32, &v[c * 32]);
+            tmem_ld_x32(tmem + lane_base + Cfg::kColAcc + part * kCols, v);
             tmem_wait_ld();
             tc_fence_before_sync();
             mbar_arrive(bar_acc_free);  // the MMA warp may start the next item's accumulation
@@ -516,6 +525,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 }
             }
             B200ATTN_STAMP(tid == 0, 400 + 4 * n + 3);
+            id = id_next;
+            ++n;
         }
     }
 

@@ -392,28 +392,26 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk64, const CUtensorMap
     static bool dq_set[kMaxDevices] = {false}, dkdv_set[kMaxDevices] = {false};
     // D = 64: 64-key tiles, two CTAs per SM.  D = 128: 128-key tiles, one CTA per SM (tensor-pipe bound).
     constexpr bool kWide = (D == 128);
-    int rc = kWide ? set_smem_once(attn_bwd_dq_wide_kernel<D>, DqWideCfg<D>::kSmemBytes, dq_set)
-                   : set_smem_once(attn_bwd_dq_kernel<D>, DqCfg<D>::kSmemBytes, dq_set);
+    int rc;
+    if constexpr (kWide) rc = set_smem_once(attn_bwd_dq_wide_kernel<D>, DqWideCfg<D>::kSmemBytes, dq_set);
+    else rc = set_smem_once(attn_bwd_dq_kernel<D>, DqCfg<D>::kSmemBytes, dq_set);
     if (rc) return rc;
     rc = set_smem_once(attn_bwd_dkdv_kernel<D>, BwdCfg<D>::kSmemBytes, dkdv_set);
     if (rc) return rc;
     record_bwd_event(0, st);
     // the dQ pass also writes the two per-row vectors the dK/dV pass reads
     const unsigned dq_items = (unsigned)(p.n_tiles * p.Hq * p.B);
-    // the D = 64 kernel is persistent: two CTAs per SM walk the item list
-    unsigned dq_grid = dq_items;
-    if (!kWide) {
-        const unsigned resident = 2u * (unsigned)sm_count();
-        if (dq_grid > resident) dq_grid = resident;
+    cudaError_t e;
+    if constexpr (kWide) {
+        e = launch_pdl(attn_bwd_dq_wide_kernel<D>, dq_items, 320, DqWideCfg<D>::kSmemBytes, st, tq, tk, tv, tdo, tdq, p);
+    } else {
+        // the D = 64 kernel is persistent: two CTAs per SM walk the item list
+        const unsigned dq_grid = std::min(dq_items, 2u * (unsigned)sm_count());
+        BwdParams pq = p;
+        pq.sched = next_sched_pair(dq_items, dq_grid);
+        e = launch_pdl(attn_bwd_dq_kernel<D>, dq_grid, DqCfg<D>::kThreads, DqCfg<D>::kSmemBytes, st, tq, tk64, tv64, tdo, to, pq,
+                       item_table_for(pq.sched ? -1 : (long long)dq_items, dq_grid, p.B * p.Hq, p.n_tiles, p.T, 4));
     }
-    BwdParams pq = p;
-    if (!kWide) pq.sched = next_sched_pair(dq_items, dq_grid);
-    const cudaError_t e = kWide ? launch_pdl(attn_bwd_dq_wide_kernel<D>, dq_grid, 320, DqWideCfg<D>::kSmemBytes, st, tq, tk,
-                                             tv, tdo, tdq, p)
-                                : launch_pdl(attn_bwd_dq_kernel<D>, dq_grid, DqCfg<D>::kThreads, DqCfg<D>::kSmemBytes, st, tq, tk64, tv64,
-                                             tdo, to, pq,
-                                             item_table_for(pq.sched ? -1 : (long long)dq_items, dq_grid, p.B * p.Hq,
-                                                            p.n_tiles, p.T, 4));
     if (e != cudaSuccess) {
         cudaGetLastError();
         return B200ATTN_ERR_CUDA;

@@ -66,6 +66,9 @@ def parse_args():
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak (default): every rank runs the whole config; strong: the config's batch is split over "
                          "the ranks (contiguous (batch, KV head) units), so the total work is fixed")
+    ap.add_argument("--backward", default="two_pass", choices=["two_pass", "one_pass"],
+                    help="two_pass (default, bit-reproducible): dQ pass + dK/dV pass; one_pass (D = 64): scores computed "
+                         "once, dQ summed by reduce-adds (row-vector kernel, fused kernel, dQ conversion)")
     ap.add_argument("--op", default="attention", choices=["attention", "qkprep", "decode_step"],
                     help="qkprep: the fused RoPE + QK-Norm operator on the config's q and k (HBM GB/s); "
                          "decode_step (with --config c5_decode): one cached sampling step of a layer, KV-cache "
@@ -288,11 +291,14 @@ class BufferSet:
                    (self.q, self.k, self.v, self.do, self.o, self.lse, self.dq, self.dk, self.dv))
 
 
+BWD_MODE = "two_pass"  # set from --backward
+
+
 def step(m, cfg, s):
-    """One forward + one backward (the two-pass backward: three kernel launches per step)."""
+    """One forward + one backward (two-pass backward: three kernel launches per step; one-pass: four)."""
     m.flash_attn_forward_gqa(s.q, s.k, s.v, s.o, s.lse, cfg.B, cfg.T, cfg.Hq, cfg.Hkv, cfg.D)
     m.flash_attn_backward_gqa(s.q, s.k, s.v, s.o, s.lse, s.do, s.dq, s.dk, s.dv, cfg.B, cfg.T, cfg.Hq, cfg.Hkv, cfg.D,
-                              mode="two_pass")
+                              mode=BWD_MODE)
 
 
 def set_bytes(cfg):
@@ -324,7 +330,7 @@ def kernel_breakdown(m, cfg, sets, steps):
 
     lib = m._lib.load()
     n = min(steps, 200)
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(n)]
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(n)]
     for row in evs:  # events get their CUDA handle on first record
         for e in row:
             e.record()
@@ -332,17 +338,21 @@ def kernel_breakdown(m, cfg, sets, steps):
     for i in range(n):
         s = sets[i % len(sets)]
         e = evs[i]
-        m._lib.check(lib.b200attn_set_bwd_profile_events(e[2].cuda_event, e[3].cuda_event, e[4].cuda_event),
-                     "set_bwd_profile_events")
+        m._lib.check(lib.b200attn_set_bwd_profile_events4(e[2].cuda_event, e[3].cuda_event, e[4].cuda_event,
+                                                           e[5].cuda_event), "set_bwd_profile_events4")
         e[0].record()
         m.flash_attn_forward_gqa(s.q, s.k, s.v, s.o, s.lse, cfg.B, cfg.T, cfg.Hq, cfg.Hkv, cfg.D)
         e[1].record()
         m.flash_attn_backward_gqa(s.q, s.k, s.v, s.o, s.lse, s.do, s.dq, s.dk, s.dv, cfg.B, cfg.T, cfg.Hq, cfg.Hkv,
-                                  cfg.D, mode="two_pass")
-    lib.b200attn_set_bwd_profile_events(None, None, None)
+                                  cfg.D, mode=BWD_MODE)
+    lib.b200attn_set_bwd_profile_events4(None, None, None, None)
     torch.cuda.synchronize()
-    names = ["attn_fwd_kernel", "attn_bwd_dq_kernel", "attn_bwd_dkdv_kernel"]
-    pairs = [(0, 1), (2, 3), (3, 4)]
+    if BWD_MODE == "one_pass":
+        names = ["attn_fwd_kernel", "attn_bwd_prep_kernel", "attn_bwd_onepass_kernel", "attn_bwd_dq_convert_kernel"]
+        pairs = [(0, 1), (2, 3), (3, 4), (4, 5)]
+    else:
+        names = ["attn_fwd_kernel", "attn_bwd_dq_kernel", "attn_bwd_dkdv_kernel"]
+        pairs = [(0, 1), (2, 3), (3, 4)]
     out = {}
     for name, (a, b) in zip(names, pairs):
         out[name] = sum(e[a].elapsed_time(e[b]) for e in evs) / n  # ms
@@ -776,6 +786,8 @@ def main():
     from modern_llm_v1_b200 import inputs
 
     cfg = inputs.CONFIGS[args.config]
+    global BWD_MODE
+    BWD_MODE = args.backward
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -907,12 +919,14 @@ def main():
     # the backward's 5 are split over its two kernels in the ratio of what they execute (dQ pass 3 products,
     # dK/dV pass 4: both recompute the scores), so the credited shares add up to the metric's FLOPs.
     gemm = cfg.fwd_flops() / 2.0
-    executed = {"attn_fwd_kernel": 2 * gemm, "attn_bwd_dq_kernel": 3 * gemm, "attn_bwd_dkdv_kernel": 4 * gemm}
-    credited = {"attn_fwd_kernel": 2 * gemm, "attn_bwd_dq_kernel": 5 * gemm * 3 / 7, "attn_bwd_dkdv_kernel": 5 * gemm * 4 / 7}
+    executed = {"attn_fwd_kernel": 2 * gemm, "attn_bwd_dq_kernel": 3 * gemm, "attn_bwd_dkdv_kernel": 4 * gemm,
+                "attn_bwd_onepass_kernel": 5 * gemm, "attn_bwd_prep_kernel": 0.0, "attn_bwd_dq_convert_kernel": 0.0}
+    credited = {"attn_fwd_kernel": 2 * gemm, "attn_bwd_dq_kernel": 5 * gemm * 3 / 7, "attn_bwd_dkdv_kernel": 5 * gemm * 4 / 7,
+                "attn_bwd_onepass_kernel": 5 * gemm, "attn_bwd_prep_kernel": 0.0, "attn_bwd_dq_convert_kernel": 0.0}
     dom = max(kt, key=kt.get)
     burst, sustained = float(peaks["bf16_tflops"]), float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]))
     achieved = credited[dom] / (kt[dom] * 1e-3) / 1e12
-    bwd_ms = kt["attn_bwd_dq_kernel"] + kt["attn_bwd_dkdv_kernel"]
+    bwd_ms = sum(v for k, v in kt.items() if k != "attn_fwd_kernel")
     roofline = {
         "bound": "tensor", "kernel": dom, "achieved": achieved, "peak": burst, "unit": "TFLOP/s", "frac": achieved / burst,
         "traffic": NCU_TRAFFIC_BYTES.get(cfg.name, {}).get(dom) if cfg.B == inputs.CONFIGS[args.config].B else None,
@@ -983,7 +997,9 @@ def main():
             "launch": ("one round over the buffer sets captured in a CUDA graph and replayed" if launch_how == "graph"
                        else "every launch issued from Python"),
             "ms_per_step_by_launch": {k: v / steps for k, v in ms_by_launch.items()},
-            "backward": "two-pass (dQ pass, dK/dV pass): bit-reproducible", "buffer_sets": n_sets}
+            "backward": ("two-pass (dQ pass, dK/dV pass): bit-reproducible" if BWD_MODE == "two_pass" else
+                         "one-pass (row-vector kernel, fused kernel, dQ conversion): dQ summed by reduce-adds"),
+            "buffer_sets": n_sets}
         line = {
             "metric": "causal_gqa_attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
             "steps": steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling,
@@ -991,7 +1007,7 @@ def main():
             "per_gpu_tflops": value / world,
             "pct_of_bf16_peak": {"burst": 100 * value / world / burst, "sustained": 100 * value / world / sustained,
                                  "source": peaks["_source"]},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": 3 * steps, "roofline": roofline,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": (3 if BWD_MODE == "two_pass" else 4) * steps, "roofline": roofline,
             "checksum_dq_abs_sum": checksum,
         }
         if strong is not None:

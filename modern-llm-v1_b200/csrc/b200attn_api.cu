@@ -453,13 +453,13 @@ int rope_norm_check(int B, int T, int H, int D, int x_dtype, int x_layout, int y
 // grid: as many CTAs as the device keeps resident at once (asked of the runtime once per kernel and device), never
 // more than the rows need
 template <typename K>
-unsigned rope_norm_grid(K kernel, long long rows, int rows_per_cta_iter, int* cached_occ) {
+unsigned rope_norm_grid(K kernel, long long rows, int rows_per_cta_iter, int* cached_occ, int dyn_smem = 0) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= kMaxDevices) dev = 0;
     if (cached_occ[dev] == 0) {
         int occ = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, kRopeNormThreads, 0) != cudaSuccess || occ <= 0) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, kRopeNormThreads, dyn_smem) != cudaSuccess || occ <= 0) {
             cudaGetLastError();
             occ = 1;
         }
@@ -481,11 +481,14 @@ template <int D, bool F32>
 void rope_norm_launch_bwd(RopeNormParams p0, RopeNormParams p1, int n_tensors, long long rows, float* workspace,
                           cudaStream_t st) {
     static int occ[kMaxDevices] = {0};
-    unsigned grid = rope_norm_grid(rope_norm_bwd_kernel<D, F32>, rows, (kRopeNormThreads / 32) * kBwdSteps * (256 / D), occ);
+    static bool smem_set[kMaxDevices] = {false};
+    constexpr int kSmem = kRopeNormBwdSmemBytes<F32>;
+    if (set_smem_once(rope_norm_bwd_kernel<D, F32>, kSmem, smem_set) != B200ATTN_OK) return;
+    unsigned grid = rope_norm_grid(rope_norm_bwd_kernel<D, F32>, rows, (kRopeNormThreads / 32) * kBwdSteps * (256 / D), occ, kSmem);
     grid = std::min(grid, (unsigned)(kRopeNormMaxCtasPerSm * sm_count()));  // the workspace holds that many partial sums
     p0.partial = workspace;
     p1.partial = workspace + (size_t)kRopeNormMaxCtasPerSm * sm_count() * D;
-    launch_pdl(rope_norm_bwd_kernel<D, F32>, dim3(grid, 1, 1), kRopeNormThreads, 0, st, p0, p1, n_tensors);
+    launch_pdl(rope_norm_bwd_kernel<D, F32>, dim3(grid, 1, 1), kRopeNormThreads, kSmem, st, p0, p1, n_tensors);
     const float* part0 = p0.partial;
     const float* part1 = p1.partial;
     launch_pdl(rope_norm_dgamma_kernel<D>, dim3(n_tensors * D, 1, 1), 32, 0, st, part0, p0.d_gamma, part1, p1.d_gamma,

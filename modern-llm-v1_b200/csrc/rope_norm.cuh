@@ -48,8 +48,14 @@ struct RopeNormParams {
 };
 
 constexpr int kRopeNormThreads = 256;  // 8 warps
-constexpr int kFwdSteps = 2;           // row groups per loop iteration (all their loads are issued first)
-constexpr int kBwdSteps = 2;
+#ifndef RN_FWD_STEPS
+#define RN_FWD_STEPS 1
+#define RN_FWD_BLOCKS 4
+#define RN_BWD_STEPS 1
+#define RN_BWD_BLOCKS 3
+#endif
+constexpr int kFwdSteps = RN_FWD_STEPS;  // row groups per loop iteration (all their loads are issued first)
+constexpr int kBwdSteps = RN_BWD_STEPS;
 
 __device__ __forceinline__ float rn_bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float rn_bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
@@ -136,68 +142,144 @@ __device__ __forceinline__ void rn_scale8(const float (&rot)[8], float rstd, con
     for (int e = 0; e < 8; ++e) out[e] = rot[e] * rstd * gm[e];
 }
 
+// 16-byte asynchronous copy global -> shared (LDGSTS): the data does not pass through registers, so a lane can keep
+// several iterations' worth of loads in flight at no register cost.
+__device__ __forceinline__ void rn_cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void rn_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void rn_cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// iterations in flight per lane in the forward (their loads are staged in shared memory: 48 KB per CTA either way)
+template <bool F32>
+constexpr int kFwdDepth = F32 ? 3 : 4;
+
+// Shared memory of one forward stage: per thread 16 bytes each of cos and sin and 16 (BF16 x) or 32 (FP32 x) bytes
+// of x, laid out [piece][thread] so that a warp's accesses are contiguous.
+template <bool F32>
+struct RnFwdStage {
+    uint4 cs[kRopeNormThreads], sn[kRopeNormThreads], x0[kRopeNormThreads], x1[kRopeNormThreads];
+};
+template <>
+struct RnFwdStage<false> {
+    uint4 cs[kRopeNormThreads], sn[kRopeNormThreads], x0[kRopeNormThreads];
+};
+
 // One tensor's forward.  (A function of its own, called once per tensor with the kernel parameter itself, so that
 // every field stays a constant-bank operand; selecting the struct at run time would move it to local memory.)
+// A lane works on one row piece per iteration; the loads of the next few iterations (x, cos, sin) are
+// already on their way into this lane's own slots of the stage ring, so no barrier is needed: a lane only ever
+// reads what it has copied itself, after cp.async.wait_group.
 template <int D, bool F32>
-__device__ __forceinline__ void rope_norm_fwd_tensor(const RopeNormParams& p) {
+__device__ __forceinline__ void rope_norm_fwd_tensor(const RopeNormParams& p, RnFwdStage<F32>* ring) {
     constexpr int LPR = D / 8;      // lanes per row
-    constexpr int RPS = 32 / LPR;   // rows per warp and step
+    constexpr int RPS = 32 / LPR;   // rows per warp and iteration
     const int lane = threadIdx.x & 31;
-    const int sub = lane / LPR, li = lane % LPR;  // row within the step, position within the row
+    const int sub = lane / LPR, li = lane % LPR;  // row within the iteration, position within the row
     const unsigned warp0 = (blockIdx.x * kRopeNormThreads + threadIdx.x) >> 5;
     const unsigned n_warps = (gridDim.x * kRopeNormThreads) >> 5;
     const unsigned n_rows = unsigned(p.B) * unsigned(p.T) * unsigned(p.H);
     float gm[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) gm[e] = p.gamma[li * 8 + e];
+    const unsigned long long stride = static_cast<unsigned long long>(n_warps) * RPS;
+    const unsigned long long first = static_cast<unsigned long long>(warp0) * RPS + sub;
 
-    for (unsigned long long r0 = static_cast<unsigned long long>(warp0) * (kFwdSteps * RPS); r0 < n_rows;
-         r0 += static_cast<unsigned long long>(n_warps) * (kFwdSteps * RPS)) {
-        float v[kFwdSteps][8];
-        float4 cs[kFwdSteps], sn[kFwdSteps];
-        int bb[kFwdSteps], tt[kFwdSteps], hh[kFwdSteps];
-        bool live[kFwdSteps];
-        // all loads of the iteration first
-#pragma unroll
-        for (int k = 0; k < kFwdSteps; ++k) {
-            const unsigned long long r = r0 + k * RPS + sub;
-            live[k] = r < n_rows;
-            if (live[k]) {
-                rn_decode_row(p, unsigned(r), bb[k], tt[k], hh[k]);
-                rn_load8<F32>(p.x, bb[k] * p.x_sb + tt[k] * p.x_st + hh[k] * p.x_sh + li * 8, v[k]);
-                cs[k] = *reinterpret_cast<const float4*>(p.cos_t + static_cast<long long>(tt[k]) * (D / 2) + li * 4);
-                sn[k] = *reinterpret_cast<const float4*>(p.sin_t + static_cast<long long>(tt[k]) * (D / 2) + li * 4);
+    // requests the loads of this lane's iteration `it` (row first + it * stride) into ring slot it % depth
+    auto request = [&](unsigned it) {
+        const unsigned long long r = first + it * stride;
+        if (r < n_rows) {
+            int b, t, h;
+            rn_decode_row(p, unsigned(r), b, t, h);
+            RnFwdStage<F32>& st = ring[it % kFwdDepth<F32>];
+            const long long off = b * p.x_sb + t * p.x_st + h * p.x_sh + li * 8;
+            if constexpr (F32) {
+                rn_cp_async16(&st.x0[threadIdx.x], static_cast<const float*>(p.x) + off);
+                rn_cp_async16(&st.x1[threadIdx.x], static_cast<const float*>(p.x) + off + 4);
+            } else {
+                rn_cp_async16(&st.x0[threadIdx.x], static_cast<const uint16_t*>(p.x) + off);
             }
+            rn_cp_async16(&st.cs[threadIdx.x], p.cos_t + static_cast<long long>(t) * (D / 2) + li * 4);
+            rn_cp_async16(&st.sn[threadIdx.x], p.sin_t + static_cast<long long>(t) * (D / 2) + li * 4);
         }
+        rn_cp_async_commit();  // one group per iteration, also when it is empty
+    };
 #pragma unroll
-        for (int k = 0; k < kFwdSteps; ++k) {
-            float rot[8];
-            float ss = 0.f;
-            if (live[k]) ss = rn_rotate8(v[k], cs[k], sn[k], rot);
-            ss = rn_row_sum<LPR>(ss);  // every lane takes part in the shuffles
-            if (live[k]) {
-                const float rstd = rn_rstd<D>(ss, p.eps);
-                float out[8];
-                rn_scale8(rot, rstd, gm, out);
-                rn_store8<false>(p.y, (static_cast<long long>(r0) + k * RPS + sub) * D + li * 8, out);  // y is dense in walk order
-                if (li == 0) p.rstd[(static_cast<long long>(bb[k]) * p.H + hh[k]) * p.T + tt[k]] = rstd;
+    for (int i = 0; i < kFwdDepth<F32> - 1; ++i) request(i);
+    for (unsigned it = 0; first + it * stride - sub < n_rows; ++it) {  // (all lanes of a warp run the same iterations)
+        request(it + kFwdDepth<F32> - 1);
+        rn_cp_async_wait<kFwdDepth<F32> - 1>();  // everything but the newest kFwdDepth - 1 groups has landed: iteration `it`
+        const unsigned long long r = first + it * stride;
+        const bool live = r < n_rows;
+        float rot[8];
+        float ss = 0.f;
+        int b = 0, t = 0, h = 0;
+        if (live) {
+            const RnFwdStage<F32>& st = ring[it % kFwdDepth<F32>];
+            float v[8];
+            if constexpr (F32) {
+                const uint4 a = st.x0[threadIdx.x], c = st.x1[threadIdx.x];
+                v[0] = __uint_as_float(a.x), v[1] = __uint_as_float(a.y), v[2] = __uint_as_float(a.z), v[3] = __uint_as_float(a.w);
+                v[4] = __uint_as_float(c.x), v[5] = __uint_as_float(c.y), v[6] = __uint_as_float(c.z), v[7] = __uint_as_float(c.w);
+            } else {
+                const uint4 a = st.x0[threadIdx.x];
+                v[0] = rn_bf16_lo(a.x), v[1] = rn_bf16_hi(a.x), v[2] = rn_bf16_lo(a.y), v[3] = rn_bf16_hi(a.y);
+                v[4] = rn_bf16_lo(a.z), v[5] = rn_bf16_hi(a.z), v[6] = rn_bf16_lo(a.w), v[7] = rn_bf16_hi(a.w);
             }
+            const uint4 cw = st.cs[threadIdx.x], sw = st.sn[threadIdx.x];
+            const float4 cs = make_float4(__uint_as_float(cw.x), __uint_as_float(cw.y), __uint_as_float(cw.z), __uint_as_float(cw.w));
+            const float4 sn = make_float4(__uint_as_float(sw.x), __uint_as_float(sw.y), __uint_as_float(sw.z), __uint_as_float(sw.w));
+            ss = rn_rotate8(v, cs, sn, rot);
+            rn_decode_row(p, unsigned(r), b, t, h);
+        }
+        ss = rn_row_sum<LPR>(ss);  // every lane takes part in the shuffles
+        if (live) {
+            const float rstd = rn_rstd<D>(ss, p.eps);
+            float out[8];
+            rn_scale8(rot, rstd, gm, out);
+            rn_store8<false>(p.y, static_cast<long long>(r) * D + li * 8, out);  // y is dense in walk order
+            if (li == 0) p.rstd[(static_cast<long long>(b) * p.H + h) * p.T + t] = rstd;
         }
     }
+    rn_cp_async_wait<0>();
 }
 
 // one launch takes q and k (n_tensors = 2), one after the other
 template <int D, bool F32>
-__global__ void __launch_bounds__(kRopeNormThreads, 3)
+__global__ void __launch_bounds__(kRopeNormThreads, RN_FWD_BLOCKS)
 rope_norm_fwd_kernel(const __grid_constant__ RopeNormParams p0, const __grid_constant__ RopeNormParams p1,
                      const int n_tensors) {
+    __shared__ RnFwdStage<F32> ring[kFwdDepth<F32>];
     grid_dep_wait();  // launched with programmatic stream serialization: the inputs come from the kernel before
-    rope_norm_fwd_tensor<D, F32>(p0);
-    if (n_tensors > 1) rope_norm_fwd_tensor<D, F32>(p1);
+    rope_norm_fwd_tensor<D, F32>(p0, ring);
+    if (n_tensors > 1) rope_norm_fwd_tensor<D, F32>(p1, ring);
 }
 
+// Shared memory of one backward stage, per thread: cos, sin, x (16 or 32 bytes), dy (16 bytes) and the row's rstd.
+template <bool F32>
+struct RnBwdStage {
+    uint4 cs[kRopeNormThreads], sn[kRopeNormThreads], x0[kRopeNormThreads], x1[kRopeNormThreads], dy[kRopeNormThreads];
+    float rstd[kRopeNormThreads];
+};
+template <>
+struct RnBwdStage<false> {
+    uint4 cs[kRopeNormThreads], sn[kRopeNormThreads], x0[kRopeNormThreads], dy[kRopeNormThreads];
+    float rstd[kRopeNormThreads];
+};
+constexpr int kBwdDepth = 3;  // iterations in flight per lane in the backward
+template <bool F32>
+constexpr int kRopeNormBwdSmemBytes = kBwdDepth * int(sizeof(RnBwdStage<F32>));
+
+__device__ __forceinline__ void rn_cp_async4(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+
+// One tensor's backward; the loads are staged like the forward's (see rope_norm_fwd_tensor).
 template <int D, bool F32>
-__device__ __forceinline__ void rope_norm_bwd_tensor(const RopeNormParams& p, float (*s_part)[D]) {
+__device__ __forceinline__ void rope_norm_bwd_tensor(const RopeNormParams& p, float (*s_part)[D], RnBwdStage<F32>* ring) {
     constexpr int LPR = D / 8;
     constexpr int RPS = 32 / LPR;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -211,61 +293,85 @@ __device__ __forceinline__ void rope_norm_bwd_tensor(const RopeNormParams& p, fl
         gm[e] = p.gamma[li * 8 + e];
         dg[e] = 0.f;
     }
-    for (unsigned long long r0 = static_cast<unsigned long long>(warp0) * (kBwdSteps * RPS); r0 < n_rows;
-         r0 += static_cast<unsigned long long>(n_warps) * (kBwdSteps * RPS)) {
-        float v[kBwdSteps][8], dyv[kBwdSteps][8], rs[kBwdSteps];
-        float4 cs[kBwdSteps], sn[kBwdSteps];
-        int bb[kBwdSteps], tt[kBwdSteps], hh[kBwdSteps];
-        bool live[kBwdSteps];
+    const unsigned long long stride = static_cast<unsigned long long>(n_warps) * RPS;
+    const unsigned long long first = static_cast<unsigned long long>(warp0) * RPS + sub;
+    auto request = [&](unsigned it) {
+        const unsigned long long r = first + it * stride;
+        if (r < n_rows) {
+            int b, t, h;
+            rn_decode_row(p, unsigned(r), b, t, h);
+            RnBwdStage<F32>& st = ring[it % kBwdDepth];
+            const long long xoff = static_cast<long long>(r) * D + li * 8;  // x is dense in walk order
+            if constexpr (F32) {
+                rn_cp_async16(&st.x0[threadIdx.x], static_cast<const float*>(p.x) + xoff);
+                rn_cp_async16(&st.x1[threadIdx.x], static_cast<const float*>(p.x) + xoff + 4);
+            } else {
+                rn_cp_async16(&st.x0[threadIdx.x], static_cast<const uint16_t*>(p.x) + xoff);
+            }
+            rn_cp_async16(&st.dy[threadIdx.x], p.dy + (b * p.y_sb + t * p.y_st + h * p.y_sh + li * 8));
+            rn_cp_async4(&st.rstd[threadIdx.x], p.rstd + ((static_cast<long long>(b) * p.H + h) * p.T + t));
+            rn_cp_async16(&st.cs[threadIdx.x], p.cos_t + static_cast<long long>(t) * (D / 2) + li * 4);
+            rn_cp_async16(&st.sn[threadIdx.x], p.sin_t + static_cast<long long>(t) * (D / 2) + li * 4);
+        }
+        rn_cp_async_commit();
+    };
 #pragma unroll
-        for (int k = 0; k < kBwdSteps; ++k) {
-            const unsigned long long r = r0 + k * RPS + sub;
-            live[k] = r < n_rows;
-            if (live[k]) {
-                rn_decode_row(p, unsigned(r), bb[k], tt[k], hh[k]);
-                rn_load8<F32>(p.x, static_cast<long long>(r) * D + li * 8, v[k]);  // x is dense in walk order
-                rn_load8<false>(p.dy, bb[k] * p.y_sb + tt[k] * p.y_st + hh[k] * p.y_sh + li * 8, dyv[k]);
-                rs[k] = p.rstd[(static_cast<long long>(bb[k]) * p.H + hh[k]) * p.T + tt[k]];
-                cs[k] = *reinterpret_cast<const float4*>(p.cos_t + static_cast<long long>(tt[k]) * (D / 2) + li * 4);
-                sn[k] = *reinterpret_cast<const float4*>(p.sin_t + static_cast<long long>(tt[k]) * (D / 2) + li * 4);
+    for (int i = 0; i < kBwdDepth - 1; ++i) request(i);
+    for (unsigned it = 0; first + it * stride - sub < n_rows; ++it) {
+        request(it + kBwdDepth - 1);
+        rn_cp_async_wait<kBwdDepth - 1>();
+        const unsigned long long r = first + it * stride;
+        const bool live = r < n_rows;
+        float rot[8], g[8];
+        float s = 0.f, rs = 0.f;
+        float c[4] = {0.f, 0.f, 0.f, 0.f}, sv[4] = {0.f, 0.f, 0.f, 0.f};
+        if (live) {
+            const RnBwdStage<F32>& st = ring[it % kBwdDepth];
+            float v[8], dyv[8];
+            if constexpr (F32) {
+                const uint4 a = st.x0[threadIdx.x], q = st.x1[threadIdx.x];
+                v[0] = __uint_as_float(a.x), v[1] = __uint_as_float(a.y), v[2] = __uint_as_float(a.z), v[3] = __uint_as_float(a.w);
+                v[4] = __uint_as_float(q.x), v[5] = __uint_as_float(q.y), v[6] = __uint_as_float(q.z), v[7] = __uint_as_float(q.w);
+            } else {
+                const uint4 a = st.x0[threadIdx.x];
+                v[0] = rn_bf16_lo(a.x), v[1] = rn_bf16_hi(a.x), v[2] = rn_bf16_lo(a.y), v[3] = rn_bf16_hi(a.y);
+                v[4] = rn_bf16_lo(a.z), v[5] = rn_bf16_hi(a.z), v[6] = rn_bf16_lo(a.w), v[7] = rn_bf16_hi(a.w);
+            }
+            const uint4 d = st.dy[threadIdx.x];
+            dyv[0] = rn_bf16_lo(d.x), dyv[1] = rn_bf16_hi(d.x), dyv[2] = rn_bf16_lo(d.y), dyv[3] = rn_bf16_hi(d.y);
+            dyv[4] = rn_bf16_lo(d.z), dyv[5] = rn_bf16_hi(d.z), dyv[6] = rn_bf16_lo(d.w), dyv[7] = rn_bf16_hi(d.w);
+            const uint4 cw = st.cs[threadIdx.x], sw = st.sn[threadIdx.x];
+            c[0] = __uint_as_float(cw.x), c[1] = __uint_as_float(cw.y), c[2] = __uint_as_float(cw.z), c[3] = __uint_as_float(cw.w);
+            sv[0] = __uint_as_float(sw.x), sv[1] = __uint_as_float(sw.y), sv[2] = __uint_as_float(sw.z), sv[3] = __uint_as_float(sw.w);
+            rs = st.rstd[threadIdx.x];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float x0 = v[2 * i], x1 = v[2 * i + 1];
+                rot[2 * i] = x0 * c[i] - x1 * sv[i];
+                rot[2 * i + 1] = x0 * sv[i] + x1 * c[i];
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                g[e] = dyv[e] * gm[e];
+                s += g[e] * rot[e];
+                dg[e] += dyv[e] * rot[e] * rs;
             }
         }
+        s = rn_row_sum<LPR>(s);
+        if (live) {
+            const float coeff = rs * rs * rs * (1.f / float(D)) * s;
+            float dx[8];
 #pragma unroll
-        for (int k = 0; k < kBwdSteps; ++k) {
-            float rot[8], g[8];
-            float s = 0.f;
-            float c[4] = {0.f, 0.f, 0.f, 0.f}, sv[4] = {0.f, 0.f, 0.f, 0.f};
-            if (live[k]) {
-                c[0] = cs[k].x, c[1] = cs[k].y, c[2] = cs[k].z, c[3] = cs[k].w;
-                sv[0] = sn[k].x, sv[1] = sn[k].y, sv[2] = sn[k].z, sv[3] = sn[k].w;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float x0 = v[k][2 * i], x1 = v[k][2 * i + 1];
-                    rot[2 * i] = x0 * c[i] - x1 * sv[i];
-                    rot[2 * i + 1] = x0 * sv[i] + x1 * c[i];
-                }
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    g[e] = dyv[k][e] * gm[e];
-                    s += g[e] * rot[e];
-                    dg[e] += dyv[k][e] * rot[e] * rs[k];
-                }
+            for (int i = 0; i < 4; ++i) {
+                const float d0 = rs * g[2 * i] - coeff * rot[2 * i];
+                const float d1 = rs * g[2 * i + 1] - coeff * rot[2 * i + 1];
+                dx[2 * i] = d0 * c[i] + d1 * sv[i];
+                dx[2 * i + 1] = -d0 * sv[i] + d1 * c[i];
             }
-            s = rn_row_sum<LPR>(s);
-            if (live[k]) {
-                const float coeff = rs[k] * rs[k] * rs[k] * (1.f / float(D)) * s;
-                float dx[8];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float d0 = rs[k] * g[2 * i] - coeff * rot[2 * i];
-                    const float d1 = rs[k] * g[2 * i + 1] - coeff * rot[2 * i + 1];
-                    dx[2 * i] = d0 * c[i] + d1 * sv[i];
-                    dx[2 * i + 1] = -d0 * sv[i] + d1 * c[i];
-                }
-                rn_store8<F32>(p.y, (static_cast<long long>(r0) + k * RPS + sub) * D + li * 8, dx);
-            }
+            rn_store8<F32>(p.y, static_cast<long long>(r) * D + li * 8, dx);
         }
     }
+    rn_cp_async_wait<0>();
     // d_gamma: a lane holds sums for its 8 columns over its rows.  Add the lanes that own the same columns
     // (they differ in `sub`), then the warps of the CTA, both in a fixed order.
 #pragma unroll
@@ -288,13 +394,15 @@ __device__ __forceinline__ void rope_norm_bwd_tensor(const RopeNormParams& p, fl
 }
 
 template <int D, bool F32>
-__global__ void __launch_bounds__(kRopeNormThreads, 2)
+__global__ void __launch_bounds__(kRopeNormThreads, RN_BWD_BLOCKS)
 rope_norm_bwd_kernel(const __grid_constant__ RopeNormParams p0, const __grid_constant__ RopeNormParams p1,
                      const int n_tensors) {
     __shared__ float s_part[kRopeNormThreads / 32][D];
+    extern __shared__ uint4 rn_dyn_smem[];
+    RnBwdStage<F32>* ring = reinterpret_cast<RnBwdStage<F32>*>(rn_dyn_smem);
     grid_dep_wait();
-    rope_norm_bwd_tensor<D, F32>(p0, s_part);
-    if (n_tensors > 1) rope_norm_bwd_tensor<D, F32>(p1, s_part);
+    rope_norm_bwd_tensor<D, F32>(p0, s_part, ring);
+    if (n_tensors > 1) rope_norm_bwd_tensor<D, F32>(p1, s_part, ring);
 }
 
 // d_gamma[d] += sum of the CTAs' partial sums, for one or two tensors.  One warp per column (CTA c takes column

@@ -1,6 +1,7 @@
 // C-ABI launcher for the sm_100a attention kernels (see include/b200attn.h for
 // the contract).  Host side only validates, builds TMA tensor maps and enqueues.
 #include "../../include/b200attn.h"
+#include "b200attn_debug.h"
 
 #include <cuda_runtime.h>
 

@@ -540,33 +540,34 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 }
 
 // ---------------------------------------------------------------------------------------
-// dQ pass, wide variant used for D = 128: 128-key tiles, eight compute warps (thread owns a row
-// and 64 of the 128 score columns), one CTA per SM.  With D = 128 the pass is bound by the
-// tensor pipe, and 128-wide S = Q K^T products keep the shared-memory operand traffic of the
-// SS MMAs at the 128 B/clk the SM can deliver (a 64-wide product needs 192 B/clk).
+// dQ pass for D = 128: one CTA per item (128-row query tile of one (batch, query head)), 128-key tiles, eight
+// compute warps (thread owns a row and 64 of the 128 score columns), one CTA per SM.  As in the D = 64 kernel, Q
+// and dO are copied once from shared memory into tensor memory, so that S = Q K^T, dP = dO V^T and dQ += dS K all
+// take their A operand from there (a 128-wide product with A in shared memory fetches 4 KB of A and 4 KB of B per
+// K step), and the one S buffer is handed back as soon as the scores are in registers: the next tile's Q K^T runs
+// under this tile's exponentials, and the next dP product follows the dQ product that consumes dS out of the dP
+// block.
+// Shared memory: the Q and dO staging tiles (64 KB; re-used as the third K/V ring stage once they have been copied
+// into tensor memory, and at the very end as the staging tile of the dQ store) and two more K/V stages.
+// TMEM (512 columns): S [0,128), dP [128,256) (dS as BF16 over the first 32 columns of each half's range), dQ
+// accumulator [256,384), Q [384,448), dO [448,512).
 // ---------------------------------------------------------------------------------------
 template <int D>
 struct DqWideCfg {
-    static constexpr bool kDoubleS = (D == 64);
-    static constexpr int kStages = kDoubleS ? 3 : 2;
+    static constexpr int kStages = 3;  // K/V tile pairs in flight; the third one lives where Q and dO were staged
     static constexpr int kTileBytes = 128 * D * 2;
     static constexpr int kBoxBytes = 128 * 64 * 2;
     static constexpr int kBoxes = D / 64;
-    static constexpr int kVecBytes = 0;
-    static constexpr int kSmemBytes = (2 + 2 * kStages) * kTileBytes + 256 + 1024;
+    static constexpr int kSmemBytes = 2 * kStages * kTileBytes + 256 + 1024;
     static constexpr int kTmemCols = 512;
-    static constexpr int kColS0 = 0;
-    static constexpr int kColS1 = kDoubleS ? 128 : 0;
-    static constexpr int kColDP = kDoubleS ? 256 : 128;
-    static constexpr int kColAcc0 = kDoubleS ? 384 : 256;
-    __host__ __device__ static constexpr int col_s(int buf) { return buf ? kColS1 : kColS0; }
+    static constexpr int kColS = 0, kColDP = 128, kColAcc = 256, kColQ = 384, kColDO = 448;
 };
 
+// D[tmem] = A[tmem, BF16 pairs] * B[smem, K-major]^T over the head dimension (b_desc describes K step 0)
 template <int D>
-__device__ __forceinline__ void wide_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+__device__ __forceinline__ void wide_ts_headdim(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
 #pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks)
-        umma_ss(d_tmem, a_desc + kmajor_step(ks, 16384), b_desc + kmajor_step(ks, 16384), idesc, ks > 0);
+    for (int ks = 0; ks < D / 16; ++ks) umma_ts(d_tmem, a_tmem + ks * 8, b_desc + kmajor_step(ks, 16384), idesc, ks > 0);
 }
 // A in two 32-column pieces at a_col and a_col + 64 (one per column half)
 template <int D>
@@ -581,20 +582,25 @@ __global__ void __launch_bounds__(320, 1)
 attn_bwd_dq_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                    const __grid_constant__ CUtensorMap tmdQ, const BwdParams p) {
+    static_assert(D == 128, "Q and dO take 2 x 64 tensor-memory columns: D = 128 only");
     using Cfg = DqWideCfg<D>;
     constexpr int NST = Cfg::kStages;
-    constexpr bool DBL = Cfg::kDoubleS;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;
     uint8_t* sdO = sQ + Cfg::kTileBytes;
-    uint8_t* sK = sdO + Cfg::kTileBytes;        // [NST]
-    uint8_t* sV = sK + NST * Cfg::kTileBytes;   // [NST]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + NST * Cfg::kTileBytes + Cfg::kVecBytes);
-    uint64_t* bar_q = bars + 0;
-    uint64_t* bar_s_full = bars + 1;   // [2] one per S buffer
-    uint64_t* bar_dp_full = bars + 3;
-    uint64_t* bar_ds_full = bars + 4;  // [2] by tile parity (a parity wait must never be two phases behind)
+    uint8_t* sK01 = sdO + Cfg::kTileBytes;      // K of ring stages 0 and 1
+    uint8_t* sV01 = sK01 + 2 * Cfg::kTileBytes; // V of ring stages 0 and 1
+    // ring stage 2 re-uses the two tiles Q and dO were staged in (free once they are in tensor memory)
+    auto stage_k = [&](int st) { return st < 2 ? sK01 + st * Cfg::kTileBytes : sQ; };
+    auto stage_v = [&](int st) { return st < 2 ? sV01 + st * Cfg::kTileBytes : sdO; };
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV01 + 2 * Cfg::kTileBytes);
+    uint64_t* bar_q = bars + 0;         // Q and dO have landed in shared memory
+    uint64_t* bar_qt_full = bars + 1;   // Q and dO are in tensor memory
+    uint64_t* bar_s_full = bars + 2;    //                                                     (phase: tile)
+    uint64_t* bar_s_loaded = bars + 3;  // S is in registers: the buffer may be overwritten   (phase: tile)
+    uint64_t* bar_dp_full = bars + 4;   //                                                     (phase: tile)
+    uint64_t* bar_ds_full = bars + 5;   // dS written over dP                                  (phase: tile)
     uint64_t* bar_acc = bars + 6;
     uint64_t* bar_kv_full = bars + 7;          // [NST]
     uint64_t* bar_kv_free = bars + 7 + NST;    // [NST]
@@ -620,11 +626,11 @@ attn_bwd_dq_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 
     if (tid == 0) {
         mbar_init(bar_q, 1);
-        mbar_init(&bar_s_full[0], 1);
-        mbar_init(&bar_s_full[1], 1);
+        mbar_init(bar_qt_full, 256);
+        mbar_init(bar_s_full, 1);
+        mbar_init(bar_s_loaded, 256);
         mbar_init(bar_dp_full, 1);
-        mbar_init(&bar_ds_full[0], 256);
-        mbar_init(&bar_ds_full[1], 256);
+        mbar_init(bar_ds_full, 256);
         mbar_init(bar_acc, 1);
         for (int s = 0; s < NST; ++s) {
             mbar_init(&bar_kv_full[s], 1);
@@ -664,72 +670,65 @@ attn_bwd_dq_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
             if (j >= NST &&
                 !mbar_wait_warp(&bar_kv_free[s], ((j / NST) - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE))
                 break;
+            // the first use of stage 2 overwrites Q and dO in shared memory: they must be in tensor memory by then
+            if (j == 2 && !mbar_wait_warp(bar_qt_full, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_FREE)) break;
             if (elect_one()) {
                 mbar_arrive_expect_tx(&bar_kv_full[s], 2 * Cfg::kTileBytes);
 #pragma unroll
                 for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
-                    tma_load_4d(sK + s * Cfg::kTileBytes + bx * Cfg::kBoxBytes, &tmK, &bar_kv_full[s], bx * 64, j * 128,
-                                hk, b);
-                    tma_load_4d(sV + s * Cfg::kTileBytes + bx * Cfg::kBoxBytes, &tmV, &bar_kv_full[s], bx * 64, j * 128,
-                                hk, b);
+                    tma_load_4d(stage_k(s) + bx * Cfg::kBoxBytes, &tmK, &bar_kv_full[s], bx * 64, j * 128, hk, b);
+                    tma_load_4d(stage_v(s) + bx * Cfg::kBoxBytes, &tmV, &bar_kv_full[s], bx * 64, j * 128, hk, b);
                 }
             }
             __syncwarp();
         }
     } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issuer (whole warp, one lane issues)
-        constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
-        constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
-        const uint64_t q_desc = kmajor_desc<D>(sQ), do_desc = kmajor_desc<D>(sdO);
-        bool ok = mbar_wait_warp(bar_q, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
-        // S(j) = Q K_j^T into S buffer (j & 1 when double-buffered); waits for the tile's loads first
+        constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);   // A in TMEM, B (K or V tile) K-major
+        constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);   // A in TMEM, B (K tile) MN-major
+        bool ok = mbar_wait_warp(bar_qt_full, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+        // S(j) = Q K_j^T; the buffer still holds S(j - 1) until it has been read into registers
         auto issue_s = [&](int j) -> bool {
             const int s = j % NST;
-            if (!mbar_wait_warp(&bar_kv_full[s], (j / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD))
+            if (j > 0 && !mbar_wait_warp(bar_s_loaded, uint32_t(j - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX))
                 return false;
+            if (!mbar_wait_warp(&bar_kv_full[s], (j / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD)) return false;
             tc_fence_after_sync();
-            const int buf = DBL ? (j & 1) : 0;
             if (elect_one()) {
-                wide_ss<D>(tmem + Cfg::col_s(buf), q_desc, kmajor_desc<D>(sK + s * Cfg::kTileBytes), idesc_s);
-                umma_commit(&bar_s_full[buf]);
+                wide_ts_headdim<D>(tmem + Cfg::kColS, tmem + Cfg::kColQ, kmajor_desc<D>(stage_k(s)), idesc_s);
+                umma_commit(bar_s_full);
             }
             __syncwarp();
             return true;
         };
-        auto issue_dp = [&](int j) {  // dP(j) = dO V_j^T; the loads of tile j are known to be complete
+        // dP(j) = dO V_j^T; the tile's loads are known to be complete (S(j) was issued), and the product that read
+        // dS(j - 1) out of this block was issued before
+        auto issue_dp = [&](int j) {
             const int s = j % NST;
             if (elect_one()) {
-                wide_ss<D>(tmem + Cfg::kColDP, do_desc, kmajor_desc<D>(sV + s * Cfg::kTileBytes), idesc_s);
+                wide_ts_headdim<D>(tmem + Cfg::kColDP, tmem + Cfg::kColDO, kmajor_desc<D>(stage_v(s)), idesc_s);
                 umma_commit(bar_dp_full);
             }
             __syncwarp();
         };
         if (ok) ok = issue_s(0);
         if (ok) issue_dp(0);
-        if (ok && DBL && n_kv > 1) ok = issue_s(1);
         for (int j = 0; j < n_kv && ok; ++j) {
             const int s = j % NST;
-            ok = mbar_wait_warp(&bar_ds_full[j & 1], uint32_t(j >> 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+            if (j + 1 < n_kv) {
+                ok = issue_s(j + 1);  // as soon as S(j) is in registers
+                if (!ok) break;
+            }
+            ok = mbar_wait_warp(bar_ds_full, uint32_t(j) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
             if (!ok) break;
             tc_fence_after_sync();
             if (elect_one()) {
                 // dQ += dS K_j
-                wide_ts<D>(tmem + Cfg::kColAcc0, tmem + Cfg::kColDP, mnmajor_desc<D>(sK + s * Cfg::kTileBytes),
-                                      idesc_acc, j > 0);
+                wide_ts<D>(tmem + Cfg::kColAcc, tmem + Cfg::kColDP, mnmajor_desc<D>(stage_k(s)), idesc_acc, j > 0);
                 umma_commit(&bar_kv_free[s]);
             }
             __syncwarp();
-            if (j + 1 < n_kv) {
-                if (!DBL) {
-                    ok = issue_s(j + 1);
-                    if (!ok) break;
-                }
-                issue_dp(j + 1);  // S(j+1) was issued earlier, so its loads have landed
-            }
-            if (DBL && j + 2 < n_kv) {
-                ok = issue_s(j + 2);
-                if (!ok) break;
-            }
+            if (j + 1 < n_kv) issue_dp(j + 1);
         }
         if (elect_one()) umma_commit(bar_acc);
         __syncwarp();
@@ -772,30 +771,47 @@ attn_bwd_dq_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
                 p.dvec_w[vrow] = dv;
             }
         }
-        bool ok = true;
-        for (int j = 0; j < n_kv; ++j) {
-            const int buf = DBL ? (j & 1) : 0;
-            const uint32_t s_par = DBL ? ((j >> 1) & 1) : (j & 1);
-            ok = mbar_wait_warp(&bar_s_full[buf], s_par, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+        // this row of Q (half 0) or dO (half 1) from the swizzled tile in shared memory into tensor memory: the 256
+        // bytes of the row are the 64 BF16-pair columns of lane `row` as they stand
+        bool ok = mbar_wait_warp(bar_q, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+        if (ok) {
+            const uint8_t* tile = half == 0 ? sQ : sdO;
+#pragma unroll
+            for (int bx = 0; bx < Cfg::kBoxes; ++bx) {
+                uint32_t tw[32];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 w = *reinterpret_cast<const uint4*>(tile + bx * Cfg::kBoxBytes + row * 128 + ((c ^ (row & 7)) << 4));
+                    tw[4 * c] = w.x, tw[4 * c + 1] = w.y, tw[4 * c + 2] = w.z, tw[4 * c + 3] = w.w;
+                }
+                tmem_st_x32(tmem + lane_base + (half == 0 ? Cfg::kColQ : Cfg::kColDO) + bx * 32, tw);
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(bar_qt_full);
+        }
+        for (int j = 0; j < n_kv && ok; ++j) {
+            ok = mbar_wait_warp(bar_s_full, uint32_t(j) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
             if (!ok) break;
             tc_fence_after_sync();
-            // phase A: P from S
+            // phase A: P from S (the scores leave tensor memory in one go)
             float pr[64];
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t sv[32];
-                tmem_ld_x32(tmem + lane_base + Cfg::col_s(buf) + c0 + c * 32, sv);
+            {
+                uint32_t sv[64];
+                tmem_ld_x32(tmem + lane_base + Cfg::kColS + c0, sv);
+                tmem_ld_x32(tmem + lane_base + Cfg::kColS + c0 + 32, sv + 32);
                 tmem_wait_ld();
+                tc_fence_before_sync();
+                mbar_arrive(bar_s_loaded);
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    pr[c * 32 + i] = ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse2));
+                for (int i = 0; i < 64; ++i) pr[i] = ex2_approx(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse2));
             }
             if (j == qt) {
 #pragma unroll
                 for (int i = 0; i < 64; ++i)
                     if (c0 + i > row) pr[i] = 0.f;  // key above the diagonal
             }
-            ok = mbar_wait_warp(bar_dp_full, j & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
+            ok = mbar_wait_warp(bar_dp_full, uint32_t(j) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
             if (!ok) break;
             tc_fence_after_sync();
             // phase B: dS = P (dP - D), written over dP as BF16
@@ -812,7 +828,7 @@ attn_bwd_dq_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
             }
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(&bar_ds_full[j & 1]);
+            mbar_arrive(bar_ds_full);
         }
         if (ok) ok = mbar_wait(bar_acc, 0, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
         ok = __all_sync(0xffffffffu, ok);
@@ -822,7 +838,7 @@ attn_bwd_dq_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
             for (int c = 0; c < D / 64; ++c) {
                 uint32_t v[32];
                 const int col = half * (D / 2) + c * 32;
-                tmem_ld_x32(tmem + lane_base + Cfg::kColAcc0 + col, v);
+                tmem_ld_x32(tmem + lane_base + Cfg::kColAcc + col, v);
                 tmem_wait_ld();
                 stage_row_chunk<D>(sQ, row, col, v, p.scale);
             }
@@ -886,6 +902,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     uint64_t* bar_acc_free = bars + 11; // accumulators read by the epilogue                     (phase: item)
     uint64_t* bar_full = bars + 12;        // [NST] Q, dO and the two row vectors of a unit have landed
     uint64_t* bar_free = bars + 12 + NST;  // [NST]
+    uint64_t* bar_s_loaded = bars + 22;  // one S buffer (D = 128): S^T is in registers, the buffer is free (phase: unit)
     uint64_t* bar_out_free = bars + 20;  // the TMA store of the previous item has read the staging tiles (phase: item)
     uint64_t* bar_out_full = bars + 21;  // every compute thread has staged its part of dV / dK        (phase: item)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
@@ -925,6 +942,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         mbar_init(bar_acc_free, Cfg::kComputeThreads);
         mbar_init(bar_out_free, 1);
         mbar_init(bar_out_full, Cfg::kComputeThreads);
+        mbar_init(bar_s_loaded, Cfg::kComputeThreads);
         for (int s = 0; s < NST; ++s) {
             mbar_init(&bar_full[s], 1);
             mbar_init(&bar_free[s], 1);
@@ -1036,7 +1054,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         };
         auto issue_s = [&](const Cursor& c) {  // S^T(u) = K Q^T
             const int s = c.u % NST, kb = c.n % NKV;
-            if (c.it == 0) ok = mbar_wait_warp(&bar_kv[kb], uint32_t(c.n / NKV) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
+            // one S buffer: it still holds S^T of the unit before until the compute warps have read it into registers
+            if (!DBL && c.u > 0) ok = mbar_wait_warp(bar_s_loaded, uint32_t(c.u - 1) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
+            if (ok && c.it == 0) ok = mbar_wait_warp(&bar_kv[kb], uint32_t(c.n / NKV) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
             if (ok) ok = mbar_wait_warp(&bar_full[s], uint32_t(c.u / NST) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_LOAD);
             if (!ok) return;
             tc_fence_after_sync();
@@ -1082,6 +1102,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             // (dS^T is written next to P^T inside the S buffer, so the dP block is free): the MMA round trip
             // runs under their arithmetic.  (With a single S buffer, D = 128, the loads of the next unit
             // may still be in flight: there dP^T follows S^T below instead.)
+            if (!DBL && cs.n_it > 0 && cs.it != 0) {
+                // one S buffer (D = 128): S^T of the next unit as soon as this unit's scores are in registers, so that
+                // it runs under this unit's exponentials.  (Not across an item boundary: the next item's K and V are
+                // only loaded once this item's last dP^T product has run; that S^T follows the products below.)
+                issue_s(cs);
+                cursor_next(cs, true);
+                if (!ok) break;
+            }
             if (DBL && cd.n_it > 0) {
                 ok = mbar_wait_warp(bar_dp_free, uint32_t(ca.u) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_SOFTMAX);
                 if (!ok) break;
@@ -1099,21 +1127,25 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             }
             tc_fence_after_sync();
             if (elect_one()) {
-                // dV += P^T dO ; dK += dS^T Q   (P^T and dS^T sit side by side in S buffer `buf`)
-                issue_ts_over_rows<D>(tmem + Cfg::kColAcc0, tmem + Cfg::col_s(buf),
-                                      mnmajor_desc<D>(sdO + s * Cfg::kTileBytes), idesc_acc, ca.it > 0);
-                issue_ts_over_rows<D>(tmem + Cfg::kColAcc1, tmem + Cfg::col_s(buf) + Cfg::kPartCols / 2,
-                                      mnmajor_desc<D>(sQ + s * Cfg::kTileBytes), idesc_acc, ca.it > 0);
+                // dV += P^T dO ; dK += dS^T Q   (P^T and dS^T sit side by side: in S buffer `buf`, or, with one S
+                // buffer, over the dP block, which the compute warps have read by then)
+                const uint32_t a_pds = tmem + (DBL ? Cfg::col_s(buf) : Cfg::kColDP);
+                issue_ts_over_rows<D>(tmem + Cfg::kColAcc0, a_pds, mnmajor_desc<D>(sdO + s * Cfg::kTileBytes), idesc_acc, ca.it > 0);
+                issue_ts_over_rows<D>(tmem + Cfg::kColAcc1, a_pds + Cfg::kPartCols / 2, mnmajor_desc<D>(sQ + s * Cfg::kTileBytes),
+                                      idesc_acc, ca.it > 0);
                 umma_commit(&bar_free[s]);
                 if (ca.it + 1 == ca.n_it) umma_commit(bar_acc);
             }
             __syncwarp();
             B200ATTN_STAMP(lane == 0, 16 + 8 * ca.u + 5);
             if (ca.it + 1 == ca.n_it) ++n_done;
-            if (!DBL && cs.n_it > 0) {
+            if (!DBL && cs.n_it > 0 && cs.u == ca.u + 1) {  // S^T of the next unit is still to come (item boundary)
                 issue_s(cs);
                 cursor_next(cs, true);
                 if (!ok) break;
+            }
+            if (!DBL && cd.n_it > 0) {
+                // dP^T of the next unit overwrites P^T and dS^T of this one: behind the two products just issued
                 issue_dp(cd);
                 cursor_next(cd, false);
             }
@@ -1235,8 +1267,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                 tc_fence_after_sync();
                 const float4* lse4 = reinterpret_cast<const float4*>(sLse + s * 128 + c0);
                 const float4* dv4 = reinterpret_cast<const float4*>(sDv + s * 128 + c0);
-                // phase A: P^T from S^T (kept in registers and stored over S^T as BF16), 16 columns at a time
                 float pr[32];
+                if constexpr (DBL) {
+                // phase A: P^T from S^T (kept in registers and stored over S^T as BF16), 16 columns at a time
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
                     uint32_t sv[16], pk[8];
@@ -1260,11 +1293,38 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                     for (int i = 0; i < 8; ++i) pk[i] = pack_bf16x2(pr[hh * 16 + 2 * i], pr[hh * 16 + 2 * i + 1]);
                     tmem_st_x8(tmem + lane_base + Cfg::col_s(buf) + c0 + hh * 8, pk);
                 }
+                } else {
+                // phase A with one S buffer: the scores leave tensor memory in one go and the buffer goes back to the
+                // MMA warp at once; P^T stays in registers until phase B
+                {
+                    uint32_t sv[32];
+                    tmem_ld_x16(tmem + lane_base + Cfg::kColS0 + c0, sv);
+                    tmem_ld_x16(tmem + lane_base + Cfg::kColS0 + c0 + 16, sv + 16);
+                    tmem_wait_ld();
+                    tc_fence_before_sync();
+                    mbar_arrive(bar_s_loaded);
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        const float4 l4 = lse4[g];
+                        float* q = &pr[g * 4];
+                        q[0] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 0]), p.scale_log2, -l4.x));
+                        q[1] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 1]), p.scale_log2, -l4.y));
+                        q[2] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 2]), p.scale_log2, -l4.z));
+                        q[3] = ex2_approx(fmaf(__uint_as_float(sv[g * 4 + 3]), p.scale_log2, -l4.w));
+                    }
+                }
+                if (diag) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (c0 + i < row) pr[i] = 0.f;  // query above the key: masked
+                }
+                }
                 B200ATTN_STAMP(tid == 0, 16 + 8 * u + 1);
                 ok = mbar_wait_warp(bar_dp_full, uint32_t(u) & 1, abort_flag, p.status, DEV_WAIT_TIMEOUT_MMA);
                 if (!ok) break;
                 B200ATTN_STAMP(tid == 0, 16 + 8 * u + 2);
                 tc_fence_after_sync();
+                if constexpr (DBL) {
                 // phase B: dS^T = P^T (dP^T - D), stored as BF16 next to P^T in the S buffer
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
@@ -1285,6 +1345,30 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                                                     q[3] * (__uint_as_float(dp[g * 4 + 3]) - d4.w));
                     }
                     tmem_st_x8(tmem + lane_base + Cfg::col_s(buf) + c0 + Cfg::kPartCols / 2 + hh * 8, pk);
+                }
+                } else {
+                // phase B with one S buffer: all of this thread's dP^T into registers, then P^T and dS^T as BF16 side by
+                // side over the part's own 32 columns of the dP block (P^T in the first 16, dS^T in the second 16)
+                {
+                    uint32_t dp[32], pp[16], pd[16];
+                    const uint32_t t_dp = tmem + lane_base + Cfg::kColDP + c0;
+                    tmem_ld_x16(t_dp, dp);
+                    tmem_ld_x16(t_dp + 16, dp + 16);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        const float4 d4 = dv4[g];
+                        const float* q = &pr[g * 4];
+                        pp[g * 2 + 0] = pack_bf16x2(q[0], q[1]);
+                        pp[g * 2 + 1] = pack_bf16x2(q[2], q[3]);
+                        pd[g * 2 + 0] = pack_bf16x2(q[0] * (__uint_as_float(dp[g * 4 + 0]) - d4.x),
+                                                    q[1] * (__uint_as_float(dp[g * 4 + 1]) - d4.y));
+                        pd[g * 2 + 1] = pack_bf16x2(q[2] * (__uint_as_float(dp[g * 4 + 2]) - d4.z),
+                                                    q[3] * (__uint_as_float(dp[g * 4 + 3]) - d4.w));
+                    }
+                    tmem_st_x16(t_dp, pp);
+                    tmem_st_x16(t_dp + 16, pd);
+                }
                 }
                 tmem_wait_st();
                 tc_fence_before_sync();

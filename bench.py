@@ -41,7 +41,11 @@ NCU_TRAFFIC_BYTES = {"c2_50m_train": {"attn_fwd_kernel": 21035776, "attn_bwd_dq_
                                       "attn_bwd_dkdv_kernel": 34405376},
                      # profiles/attn_fwd_bwd_c3_300m_class.md
                      "c3_300m_class": {"attn_fwd_kernel": 53327616, "attn_bwd_dq_kernel": 132612096,
-                                       "attn_bwd_dkdv_kernel": 95487488}}
+                                       "attn_bwd_dkdv_kernel": 95487488},
+                     # profiles/attn_fwd_bwd_c4_long_context.md (the dK/dV pass streams Q and dO once per key tile: the
+                     # re-reads hit L2 at 78 %, the rest comes from DRAM again)
+                     "c4_long_context": {"attn_fwd_kernel": 473484288, "attn_bwd_dq_kernel": 1000673280,
+                                         "attn_bwd_dkdv_kernel": 1197408512}}
 
 
 def load_peaks():
@@ -648,7 +652,7 @@ def run_qkprep(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier)
                 "note": "bound by the host link: every tensor crosses it once per step"},
         "roofline": {"bound": "hbm", "kernel": "rope_norm_fwd_kernel + rope_norm_bwd_kernel", "achieved": gbs / world,
                      "peak": peak, "unit": "GB/s", "frac": gbs / world / peak,
-                     "traffic": 799593216 if cfg.name == "c4_long_context" else None,  # profiles/rope_norm_c4_long_context.md
+                     "traffic": 794041344 if cfg.name == "c4_long_context" else None,  # profiles/rope_norm_c4_long_context.md
                      "peak_source": f"hbm_gbs of {peaks['_source']}", "bytes_per_step": nbytes,
                      "note": "3 launches per step: q and k together, forward, backward, d_gamma sums"},
     }

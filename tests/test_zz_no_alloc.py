@@ -56,12 +56,38 @@ def _both_backwards(lib, B, T, Hq, Hkv, D, seed):
 
 
 def test_static_scratch_backward_matches_workspace_backward_twice_in_a_row(lib):
-    # first call: 2*6*384 = 4608 rows of the array; second call: 1*4*(200 -> 256) = 1024 rows
-    for B, T, Hq, Hkv, D, seed in ((2, 384, 6, 2, 64, 1), (1, 200, 4, 2, 128, 2)):
+    # first call: 2*6*384 = 4608 rows of the array; second call: 1*4*(200 -> 256) = 1024 rows; third call: a ragged
+    # last tile at D = 64, 1*6*(77 -> 128) = 768 rows
+    for B, T, Hq, Hkv, D, seed in ((2, 384, 6, 2, 64, 1), (1, 200, 4, 2, 128, 2), (1, 77, 6, 2, 64, 3)):
         got, want = _both_backwards(lib, B, T, Hq, Hkv, D, seed)
         for name, a, b in zip(("dq", "dk", "dv"), got, want):
             assert torch.isfinite(a.float()).all(), name
             assert torch.equal(a, b), f"{name}: static-scratch backward differs from the workspace backward"
+
+
+def test_static_scratch_backward_leaves_free_device_memory_unchanged(lib):
+    # what the entry point promises: after a first call (which loads the kernels) a call takes no device memory
+    B, T, Hq, Hkv, D = 2, 256, 6, 2, 64
+    q, k, v, do = _inputs(B, T, Hq, Hkv, D, 4)
+    o, lse = torch.empty_like(q), torch.empty(B, Hq, T, device="cuda")
+    m.flash_attn_forward_gqa(q, k, v, o, lse, B, T, Hq, Hkv, D)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        rc = lib.b200attn_bwd_static(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                     do.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, T, Hq, Hkv, D,
+                                     _lib.LAYOUT_BHTD, 0.0, stream)
+        assert rc == _lib.OK, _lib.strerror(rc)
+        torch.cuda.synchronize()
+
+    call()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        call()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert m.device_status() == 0
 
 
 def test_problems_beyond_the_fixed_scratch_are_refused(lib):

@@ -1101,12 +1101,20 @@ def measure_strong(m, full, rank, world, device, steps, barrier, t_full_ms, full
             "tflops_per_gpu": flops / (ms * 1e-3) / 1e12 / world, "one_gpu_ms_per_step": t_full_ms,
             "speedup": t_full_ms / ms, "efficiency": t_full_ms / ms / world,
             "units_per_gpu": hi - lo, "query_tiles_per_gpu": (hi - lo) * g * ((T + 127) // 128),
-            "limiter": ("per-kernel start-up and tail (about 6 us each of three kernels) do not shrink with the work, and "
-                        f"{(hi - lo) * g * ((T + 127) // 128)} forward items do not fill the 296 CTA slots of a GPU"
-                        if (hi - lo) * g * ((T + 127) // 128) < 296 * 2 else
-                        "per-kernel start-up and tail (about 6 us each of three kernels) do not shrink with the work"),
+            "limiter": strong_limiter((hi - lo) * g * ((T + 127) // 128)),
             "parity_ok": bool(ok) if rank == 0 else None, "parity_max_abs_diff": worst,
             "parity": "O, dQ, dK, dV of every unit gathered over NCCL == the whole configuration run on rank 0, bit for bit"}
+
+
+def strong_limiter(items):
+    """Names what keeps a strong-scaling split below linear, from the forward / dQ-pass items left per GPU."""
+    base = "per-kernel start-up and tail (about 6 us each of three kernels) do not shrink with the work"
+    if items < 296:
+        return f"{base}, and {items} forward items do not fill the 296 CTA slots of a GPU"
+    if items < 4 * 296:
+        return (f"{base}, and {items} forward items are {items / 296:.1f} per CTA slot: lists of one to three items "
+                "cannot be balanced as evenly as the whole configuration's")
+    return base
 
 
 def reference_gpu_paths(m, cfg, s):

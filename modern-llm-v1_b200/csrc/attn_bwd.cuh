@@ -425,6 +425,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     tw[4 * c] = gq.x, tw[4 * c + 1] = gq.y, tw[4 * c + 2] = gq.z, tw[4 * c + 3] = gq.w;
                 }
             }
+            // The tiles were read with ordinary loads and will be overwritten by TMA, which works through the async
+            // proxy: without this fence the producer's next load, issued the moment the last thread has arrived, may
+            // overtake reads that are still in flight (the producer is parked at the barrier whenever the item before
+            // was short; dQ rows of whole warps, sometimes of single lanes, then came out wrong once in a few launches).
+            fence_proxy_async_smem();
             mbar_arrive(bar_qs_free);  // the three tiles may be overwritten by the next item's loads
             tmem_st_x32(tmem + lane_base + (part == 0 ? Cfg::kColQ : Cfg::kColDO), tw);
             // exp2(x - inf) = 0: padding query rows contribute nothing
@@ -788,6 +793,9 @@ attn_bwd_dq_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
             }
             tmem_wait_st();
             tc_fence_before_sync();
+            // the producer re-uses the two tiles as a K/V stage once this barrier completes: the ordinary reads
+            // above are ordered before the async proxy's (TMA) writes
+            fence_proxy_async_smem();
             mbar_arrive(bar_qt_full);
         }
         for (int j = 0; j < n_kv && ok; ++j) {
@@ -1372,6 +1380,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                 }
                 tmem_wait_st();
                 tc_fence_before_sync();
+                // the unit's two row vectors were read from shared memory with ordinary loads; the stage goes back
+                // to TMA (async proxy) through the products this arrival lets go
+                fence_proxy_async_smem();
                 mbar_arrive(&bar_pds_full[u & 1]);
                 B200ATTN_STAMP(tid == 0, 16 + 8 * u + 3);
                 if (pending) {  // first unit of this item: now the previous item's epilogue

@@ -250,6 +250,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
                 mma_bf16_16816(o[2 * dp + 1], ap[kk], b2, b3);
             }
         }
+        // ordinary (ldmatrix) reads of a stage that TMA will overwrite: ordered before the async proxy's write
+        fence_proxy_async_smem();
         mbar_arrive(&bar_free[s]);
     }
     // ---- merge the four warps' states and write the split's partial (un-normalised O, m, l)

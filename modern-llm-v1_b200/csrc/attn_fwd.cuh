@@ -390,6 +390,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 qw[4 * c] = w.x, qw[4 * c + 1] = w.y, qw[4 * c + 2] = w.z, qw[4 * c + 3] = w.w;
             }
             tmem_st_x32(tmem + lane_base + Cfg::kColQ + qb * 32, qw);
+            fence_proxy_async_smem();  // ordinary reads before the async proxy (TMA) overwrites the tile
             mbar_arrive(&bar_qs_free[qb]);  // the values are in registers: the tile in shared memory may be reloaded
             tmem_wait_st();
             tc_fence_before_sync();

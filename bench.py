@@ -37,11 +37,11 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 # DRAM traffic of the dominant kernel per launch at the default workload, from the committed ncu
 # summary (profiles/); None until a capture exists for the current kernel.
 # (dram read + write per launch of each kernel, profiles/attn_fwd_bwd_c2_50m_train.md)
-NCU_TRAFFIC_BYTES = {"c2_50m_train": {"attn_fwd_kernel": 21035776, "attn_bwd_dq_kernel": 46745344,
-                                      "attn_bwd_dkdv_kernel": 34405376},
+NCU_TRAFFIC_BYTES = {"c2_50m_train": {"attn_fwd_kernel": 21033728, "attn_bwd_dq_kernel": 46777088,
+                                      "attn_bwd_dkdv_kernel": 34416896},
                      # profiles/attn_fwd_bwd_c3_300m_class.md
-                     "c3_300m_class": {"attn_fwd_kernel": 53327616, "attn_bwd_dq_kernel": 132612096,
-                                       "attn_bwd_dkdv_kernel": 95487488},
+                     "c3_300m_class": {"attn_fwd_kernel": 53215488, "attn_bwd_dq_kernel": 132836864,
+                                       "attn_bwd_dkdv_kernel": 96702208},
                      # profiles/attn_fwd_bwd_c4_long_context.md (the dK/dV pass streams Q and dO once per key tile: the
                      # re-reads hit L2 at 78 %, the rest comes from DRAM again)
                      "c4_long_context": {"attn_fwd_kernel": 473484288, "attn_bwd_dq_kernel": 1000673280,
@@ -540,7 +540,7 @@ def run_decode(m, cfg, args, rank, world, device, peaks, warmup, steps, barrier)
                             "on the device, as it does between the tokens of a sampling loop"},
             "roofline": {"bound": "hbm", "kernel": "attn_decode_kernel", "achieved": gbs / world, "peak": peak,
                          "unit": "GB/s", "frac": gbs / world / peak,
-                         "traffic": 273645568 if cfg.name == "c5_decode" else None,  # profiles/attn_decode_c5_decode.md
+                         "traffic": 273341184 if cfg.name == "c5_decode" else None,  # profiles/attn_decode_c5_decode.md
                          "peak_source": f"hbm_gbs of {peaks['_source']}", "bytes_per_launch": nbytes,
                          "note": "time includes the combine kernel (2 launches per step)"},
         }), flush=True)
